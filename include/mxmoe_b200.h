@@ -1,0 +1,194 @@
+/* mxmoe_b200 - C ABI of the B200 (sm_100a) mixed-precision MoE grouped GEMM.
+ *
+ * Plain C: pointers, sizes, CUDA stream handles (passed as void*).  Every entry
+ * point returns an mxmoe_status (0 = ok); mxmoe_last_error() gives the text of
+ * the last failure on the calling thread.  Nothing here terminates the process
+ * (the reference's `checkCudaErrors` -> exit(1), mxmoe/kernels/src/include/helper.h:186-198,
+ * becomes a status code) and nothing on the launch path allocates memory.
+ *
+ * "reference" paths below are relative to the MxMoE checkout.
+ */
+#ifndef MXMOE_B200_H_
+#define MXMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mxmoe_status {
+  MXMOE_OK              = 0,
+  MXMOE_ERR_INVALID     = 1, /* bad argument (null pointer, misaligned buffer, bad shape) */
+  MXMOE_ERR_UNSUPPORTED = 2, /* quantisation scheme not built into this library */
+  MXMOE_ERR_CUDA        = 3, /* a CUDA runtime / driver call failed */
+  MXMOE_ERR_WORKSPACE   = 4, /* workspace too small or not prepared */
+  MXMOE_ERR_DEVICE      = 5, /* the kernel reported an error (bounded wait ran out, ...) */
+  MXMOE_ERR_NO_DEVICE   = 6  /* no CUDA device / not an sm_100 device */
+} mxmoe_status;
+
+/* Per-problem quantisation descriptor.  Same 16-byte layout as the reference's
+ * `mxmoe::QParams {int2 qbits(a_bits, w_bits); int gsize; bool sym;}`
+ * (mxmoe/kernels/src/include/quantize.cuh:14-25). */
+typedef struct mxmoe_qparams {
+  int32_t a_bits;
+  int32_t w_bits;
+  int32_t gsize;
+  uint8_t sym;
+  uint8_t pad_[3];
+} mxmoe_qparams;
+
+/* One problem C[M,N] = A[M,K] x B[N,K]^T of a grouped launch; all pointers are
+ * device pointers.  Layouts are the reference's (mxmoe/kernels/src/include/layout.cuh:26-31,
+ * packed operands mxmoe/kernels/src/include/quantize.cuh:299-475):
+ *   fp16   (16,16)          A fp16 [M,K],            B fp16 [N,K]
+ *   w8a8   (8,8,-1,sym)     A u16 [M,K/2],           B u16 [N,K/2]   scale_a fp16 [M], scale_b fp16 [N]
+ *   w4a4   (4,4,-1,sym)     A u16 [M,K/4],           B u16 [N,K/4]   scale_a fp16 [M], scale_b fp16 [N]
+ *   w4a16  (16,4,128,asym)  A fp16 [M,K],            B u16 [N/4,K]   scale_b fp16 [K/128][N][2] (scale, zero)
+ * C is fp16 [M,N] (row pitch ldc elements, 0 = N).  With out_mode 1 the raw
+ * accumulators are stored instead (int32 for w8a8/w4a4, fp32 otherwise).
+ *
+ * Rows: the problem covers rows [row0, row0 + M) of A, scale_a and C.  `a_rows`
+ * is the number of rows the A buffer holds (0 = row0 + M); it bounds what the
+ * TMA unit may touch.  If `m_dev` is set, the live row count is read on the
+ * device from *m_dev (clamped to M); if `row0_dev` is set, row0 is read from
+ * *row0_dev.  Both let a launch follow a routing result that never visits the host. */
+typedef struct mxmoe_gg_problem {
+  const void* A;
+  const void* B;
+  const void* scale_a;
+  const void* scale_b;
+  void* C;
+  const int32_t* m_dev;
+  const int32_t* row0_dev;
+  int32_t M, N, K;
+  int32_t a_rows;
+  int32_t row0;
+  int32_t ldc;
+  mxmoe_qparams q;
+  int32_t out_mode;
+  int32_t reserved_;
+} mxmoe_gg_problem;
+
+/* ---- library ---------------------------------------------------------------- */
+const char* mxmoe_last_error(void);
+int mxmoe_version(void);
+/* Number of SMs of the current device, or a negative mxmoe_status. */
+int mxmoe_device_sm_count(void);
+
+/* ---- grouped GEMM ------------------------------------------------------------
+ * Replaces the generated host launcher `groupgemm_hz_fused_<i>` and its kernel
+ * (reference: mxmoe/kernels/kernel_sketch.py:82-145, mxmoe/kernels/compose_kernel.py:150-295).
+ * The per-call cudaMalloc / cudaMemcpy / cudaFree of the reference launcher is
+ * replaced by a caller-owned workspace. */
+
+/* Bytes of device workspace needed for `problem_count` problems. */
+size_t mxmoe_gg_workspace_bytes(int problem_count);
+
+/* Host-side record of what mxmoe_gg_prepare put into a workspace. */
+typedef struct mxmoe_gg_plan {
+  int32_t count;     /* problems kept (empty ones are dropped) */
+  int32_t needs_cvt; /* 1 if any problem has 4-bit operands (selects the kernel variant) */
+} mxmoe_gg_plan;
+
+/* Validate the problem list, encode the TMA descriptors on the host and copy the
+ * device-side problem list into `workspace` (asynchronously on `stream`).
+ * Problems with M == 0 (and no m_dev) are dropped.  `plan` receives what
+ * mxmoe_gg_run needs to know about the prepared workspace. */
+int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,
+                     void* stream, mxmoe_gg_plan* plan);
+
+/* Launch the persistent kernel over a prepared workspace.  `num_ctas` <= 0 uses
+ * one CTA per SM.  May be called any number of times after one prepare. */
+int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream);
+
+/* prepare + run */
+int mxmoe_gg_launch(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Synchronise `stream` and read the device status block of the workspace:
+ * MXMOE_OK, or MXMOE_ERR_DEVICE with the detail in mxmoe_last_error(). */
+int mxmoe_gg_check(void* workspace, void* stream);
+
+/* Drop-in for the reference's function-pointer ABI `mxmoe::FuncType`
+ * (mxmoe/kernels/src/include/registry.cuh:28-39): device arrays of device
+ * pointers, host + device copies of the dim3 sizes (x=M, y=N, z=K) and QParams.
+ * ld* are ignored as in the reference (mxmoe/kernels/src/ref_bind.cu:413 passes
+ * nullptr); runs on the default stream and returns after the kernel finished. */
+int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, void** ptr_scale_b, void** ptr_Cs,
+                             void** ptr_Ds, int64_t* ldas, int64_t* ldbs, int64_t* ldcs, int64_t* ldds,
+                             const uint32_t* device_problem_sizes, const uint32_t* host_problem_sizes,
+                             const mxmoe_qparams* device_qparams, const mxmoe_qparams* host_qparams,
+                             int problem_count);
+
+/* ---- activation prologues ----------------------------------------------------
+ * Arguments common to both kernels.  Rows [0, rows_routed) are expert-sorted
+ * routed rows, rows [rows_routed, rows_total) belong to the shared expert
+ * (pseudo-expert `num_experts`).  The four per-expert device tables are the ones
+ * the reference builds on the host at mxmoe/kernels/src/ref_bind.cu:475-505:
+ * quantisation tag (0 fp16 copy, 1 int8 per token, 2 int4 per token), first row,
+ * write offset of the packed rows and of the scales (both in fp16 elements). */
+typedef struct mxmoe_act_args {
+  const void* in;             /* fp16 */
+  const void* in_shared;      /* fp16, silu_mul_then_quant only */
+  void* q_store;              /* packed activations */
+  void* s_store;              /* fp16 per-token scales */
+  const int32_t* row_expert;  /* [rows_routed] */
+  const int64_t* row_token;   /* [rows_routed], quant_inp_act only */
+  const int32_t* exp_qtag;
+  const int32_t* exp_row_start;
+  const int32_t* exp_q_off;
+  const int32_t* exp_s_off;
+  const int8_t* signs;        /* optional +-1 diagonal of the Hadamard rotation, length k */
+  int32_t k;
+  int32_t k_shared;
+  int32_t rows_routed;
+  int32_t rows_total;
+  int32_t num_experts;
+  int32_t rotate;             /* quant_inp_act only: rotate rows by diag(signs) H_k / sqrt(k) first */
+} mxmoe_act_args;
+
+/* Gather rows of `in` ([T,k] fp16) by expert, optionally rotate, quantise per
+ * token and pack.  Replaces `quant_act_kernel` (launched at
+ * mxmoe/kernels/src/ref_bind.cu:531-544). */
+int mxmoe_quant_act(const mxmoe_act_args* args, void* stream);
+
+/* h = silu(gate) * up over gate_up rows ([rows, 2k] fp16, gate first), then
+ * quantise per token and pack for the down projection.  Replaces
+ * `silu_mul_then_quant_kernel` (launched at mxmoe/kernels/src/ref_bind.cu:701-716). */
+int mxmoe_silu_mul_then_quant(const mxmoe_act_args* args, void* stream);
+
+/* ---- device-side routing and combine -------------------------------------------
+ * Stable counting sort of the (token, slot) pairs by expert, entirely on the
+ * device.  Produces what the reference gets from torch::sort / floor_divide /
+ * bincount(...).cpu() (mxmoe/kernels/src/ref_bind.cu:47-64, :449-453) without the
+ * host round trip: counts[E], row_start[E+1] (exclusive prefix; row_start[E] is
+ * the number of routed rows), row_expert / row_token per sorted row (the
+ * reference's dst_exp_sorted / perm_indices) and slot_row, the inverse map. */
+typedef struct mxmoe_route_args {
+  const int32_t* topk_ids; /* [T, topk] */
+  int32_t* counts;         /* [E] */
+  int32_t* row_start;      /* [E + 1] */
+  int32_t* row_expert;     /* [T * topk] */
+  int64_t* row_token;      /* [T * topk] */
+  int32_t* slot_row;       /* [T * topk]; -1 where the expert id is out of range */
+  int32_t* workspace;      /* mxmoe_route_workspace_bytes() bytes */
+  size_t workspace_bytes;
+  int32_t num_tokens, topk, num_experts, reserved_;
+} mxmoe_route_args;
+
+size_t mxmoe_route_workspace_bytes(int num_tokens, int topk, int num_experts);
+int mxmoe_route_topk(const mxmoe_route_args* args, void* stream);
+
+/* out[t] = sum_j topk_weights[t,j] * y[slot_row[t,j]] (+ y_shared[t]); y is the
+ * fp16 [rows, hidden] output of the down projection, accumulation in fp32.  The
+ * reference leaves this step unimplemented (`gg_unpermute_out(){}`,
+ * mxmoe/kernels/src/ref_bind.cu:66); topk_weights may be NULL (all ones). */
+int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk_weights, const void* y_shared,
+                       void* out, int num_tokens, int topk, int hidden, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXMOE_B200_H_ */

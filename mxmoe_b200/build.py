@@ -1,0 +1,57 @@
+"""Build ``libmxmoe_b200.so`` in-tree with nvcc for sm_100a.
+
+``python -m mxmoe_b200.build`` (or :func:`build`) compiles the CUDA sources under
+``mxmoe_b200/csrc`` into ``mxmoe_b200/libmxmoe_b200.so``.  nvcc cross-compiles
+without a GPU; the CUDA runtime is linked statically so the library loads on a
+machine without a driver (the first call that needs a device then fails with
+``MXMOE_ERR_NO_DEVICE``).
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libmxmoe_b200.so")
+SOURCES = ["capi.cu", "gg_kernel.cu", "act_kernels.cu", "route_kernels.cu"]
+HEADERS = ["ptx.cuh", "gg_types.h", "act_kernels.h", "route_kernels.h", os.path.join("..", "..", "include", "mxmoe_b200.h")]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC=/path/to/nvcc")
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library if it is missing or older than its sources; return its path."""
+    if not force and not is_stale():
+        return LIB
+    cmd = [
+        _nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+        "-shared", "-Xcompiler", "-fPIC",
+        "-Xptxas", "-v" if verbose else "-warn-spills",
+        "-o", LIB,
+    ] + [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed building libmxmoe_b200.so (see stderr)")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,37 @@
+// Arguments of the activation prologue kernels (act_kernels.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace mxb {
+
+// Rows [0, rows_routed) are expert-sorted routed rows; rows [rows_routed,
+// rows_total) belong to the shared expert (pseudo-expert index num_experts) and
+// map one-to-one onto tokens.  The four per-expert tables have num_experts (+1
+// with a shared expert) entries and mirror the host tables of
+// mxmoe/kernels/src/ref_bind.cu:475-505.
+struct ActArgs {
+  const __half* in;          // quant_act: hidden [T, k]; silu_mul_quant: gate_up rows [rows_routed, 2k]
+  const __half* in_shared;   // silu_mul_quant only: shared-expert gate_up rows [T, 2 k_shared]
+  __half* q_store;           // packed activations (offsets in halfs)
+  __half* s_store;           // per-token scales
+  const int* row_expert;     // [rows_routed] expert of each sorted row
+  const int64_t* row_token;  // [rows_routed] source token of each sorted row (quant_act only)
+  const int* exp_qtag;       // 0 fp16 copy, 1 int8/token, 2 int4/token
+  const int* exp_row_start;  // first row of each expert
+  const int* exp_q_off;      // write offset into q_store (halfs)
+  const int* exp_s_off;      // write offset into s_store (halfs)
+  const int8_t* signs;       // optional +-1 diagonal of the rotation (length k), or nullptr
+  int k;                     // row length of routed rows
+  int k_shared;              // row length of shared-expert rows
+  int rows_routed;
+  int rows_total;
+  int num_experts;
+  int rotate;                // 1: apply y = (x .* signs) H / sqrt(k) before quantising
+};
+
+cudaError_t launch_quant_act(const ActArgs& a, cudaStream_t stream);
+cudaError_t launch_silu_mul_quant(const ActArgs& a, cudaStream_t stream);
+
+}  // namespace mxb

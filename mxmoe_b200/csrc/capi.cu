@@ -1,0 +1,397 @@
+// C ABI of libmxmoe_b200.so (declarations: include/mxmoe_b200.h).
+//
+// Host side of the grouped GEMM: validates a problem list, encodes one TMA
+// descriptor per operand on the host (cuTensorMapEncodeTiled, looked up through
+// the runtime so that the library has no link-time dependency on libcuda),
+// uploads the device-side problem list into the caller's workspace and launches
+// the persistent kernel.  No allocation happens on the launch path.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/mxmoe_b200.h"
+#include "act_kernels.h"
+#include "gg_types.h"
+#include "route_kernels.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                              \
+  do {                                                                                              \
+    cudaError_t e__ = (expr);                                                                       \
+    if (e__ != cudaSuccess)                                                                         \
+      return fail(MXMOE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+                  __LINE__);                                                                        \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready          = false;
+  int sm_count        = 0;
+  EncodeTiledFn encode = nullptr;
+};
+std::mutex g_mu;
+DeviceState g_dev[64];
+
+// Once per device: check the architecture, raise the dynamic shared-memory limit
+// of the kernels and fetch the descriptor encoder.
+int device_state(DeviceState** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(MXMOE_ERR_NO_DEVICE, "no CUDA device available");
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10) return fail(MXMOE_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+    st.sm_count = prop.multiProcessorCount;
+    void* fn    = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return fail(MXMOE_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+    st.encode = reinterpret_cast<EncodeTiledFn>(fn);
+    CUDA_TRY(mxb::gg_configure_kernels());
+    st.ready = true;
+  }
+  *out = &st;
+  return MXMOE_OK;
+}
+
+int scheme_of(const mxmoe_qparams& q, int* scheme) {
+  if (q.a_bits >= 16 && q.w_bits >= 16) { *scheme = mxb::SCH_FP16; return MXMOE_OK; }
+  if (q.a_bits == 8 && q.w_bits == 8 && q.gsize == -1 && q.sym) { *scheme = mxb::SCH_W8A8; return MXMOE_OK; }
+  if (q.a_bits == 4 && q.w_bits == 4 && q.gsize == -1 && q.sym) { *scheme = mxb::SCH_W4A4; return MXMOE_OK; }
+  if (q.a_bits >= 16 && q.w_bits == 4 && q.gsize == 128 && !q.sym) { *scheme = mxb::SCH_W4A16G128; return MXMOE_OK; }
+  return fail(MXMOE_ERR_UNSUPPORTED, "unsupported scheme w%da%d_g%d_%s (built: fp16, w8a8_g-1_sym, w4a4_g-1_sym, w4a16_g128_asym)",
+              q.w_bits, q.a_bits, q.gsize, q.sym ? "sym" : "asym");
+}
+
+// 2-D row-major byte/half matrix [rows, row_bytes] -> tiled tensor map with a box of (box_inner x box_rows)
+int encode_2d(EncodeTiledFn enc, CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+              uint64_t inner_elems, uint64_t rows, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw,
+              const char* what, int idx) {
+  if (rows == 0 || inner_elems == 0) return fail(MXMOE_ERR_INVALID, "problem %d: empty %s operand", idx, what);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+    return fail(MXMOE_ERR_INVALID, "problem %d: %s pointer %p is not 16-byte aligned", idx, what, base);
+  const uint64_t pitch = inner_elems * (uint64_t)elem_bytes;
+  if (pitch % 16 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: %s row pitch %llu B is not a multiple of 16", idx, what, (unsigned long long)pitch);
+  cuuint64_t gdim[2]    = {inner_elems, rows};
+  cuuint64_t gstride[1] = {pitch};
+  cuuint32_t box[2]     = {box_inner, box_rows};
+  cuuint32_t estr[2]    = {1, 1};
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MXMOE_ERR_CUDA, "problem %d: cuTensorMapEncodeTiled(%s) failed with CUresult %d", idx, what, (int)r);
+  return MXMOE_OK;
+}
+
+int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GGProblemDev* d) {
+  int scheme = 0;
+  int rc     = scheme_of(p.q, &scheme);
+  if (rc) return rc;
+  if (!p.A || !p.B || !p.C) return fail(MXMOE_ERR_INVALID, "problem %d: null A/B/C pointer", idx);
+  if (p.M < 0 || p.N <= 0 || p.K <= 0) return fail(MXMOE_ERR_INVALID, "problem %d: bad shape M=%d N=%d K=%d", idx, p.M, p.N, p.K);
+  if (p.N % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: N=%d must be a multiple of 8", idx, p.N);
+  if (p.row0 < 0) return fail(MXMOE_ERR_INVALID, "problem %d: negative row0", idx);
+  const int ldc = p.ldc > 0 ? p.ldc : p.N;
+  if (ldc < p.N || ldc % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: ldc=%d must be >= N and a multiple of 8", idx, ldc);
+  if ((reinterpret_cast<uintptr_t>(p.C) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: C is not 16-byte aligned", idx);
+  const bool wxax = scheme == mxb::SCH_W8A8 || scheme == mxb::SCH_W4A4;
+  if (wxax && p.out_mode == mxb::OUT_FP16) {
+    if (!p.scale_a || !p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w%da%d needs scale_a and scale_b", idx, p.q.w_bits, p.q.a_bits);
+    if ((reinterpret_cast<uintptr_t>(p.scale_b) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 16-byte aligned", idx);
+  }
+  if (p.out_mode != mxb::OUT_FP16 && p.out_mode != mxb::OUT_ACC) return fail(MXMOE_ERR_INVALID, "problem %d: bad out_mode %d", idx, p.out_mode);
+  const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
+  if (!p.row0_dev && a_rows < (uint64_t)p.row0 + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
+
+  const uint64_t K = (uint64_t)p.K, N = (uint64_t)p.N;
+  switch (scheme) {
+    case mxb::SCH_FP16:
+      if (p.K % 8) return fail(MXMOE_ERR_INVALID, "problem %d: fp16 needs K %% 8 == 0 (K=%d)", idx, p.K);
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, N, 64, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W8A8:
+      if (p.K % 16) return fail(MXMOE_ERR_INVALID, "problem %d: w8a8 needs K %% 16 == 0 (K=%d)", idx, p.K);
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, a_rows, 128, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, 128, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W4A4:
+      if (p.K % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a4 needs K %% 32 == 0 (K=%d)", idx, p.K);
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W4A16G128:
+      if (p.K % 128) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs K %% 128 == 0 (K=%d)", idx, p.K);
+      if (p.N % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs N %% 32 == 0 (N=%d)", idx, p.N);
+      if (!p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs scale_b (scale, zero) pairs", idx);
+      if ((reinterpret_cast<uintptr_t>(p.scale_b) & 3) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 4-byte aligned", idx);
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx))) return rc;
+      // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, 64 packed rows = 256 n
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K * 2, N / 4, 128, mxb::kBN / 4, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
+      break;
+  }
+  d->scale_a  = static_cast<const __half*>(p.scale_a);
+  d->scale_b  = static_cast<const __half*>(p.scale_b);
+  d->C        = p.C;
+  d->m_dev    = p.m_dev;
+  d->row0_dev = p.row0_dev;
+  d->M        = p.M;
+  d->N        = p.N;
+  d->K        = p.K;
+  d->row0     = p.row0;
+  d->scheme   = scheme;
+  d->out_mode = p.out_mode;
+  d->ldc      = ldc;
+  d->reserved = 0;
+  return MXMOE_OK;
+}
+
+struct ShimScratch {
+  void* ws        = nullptr;
+  size_t ws_bytes = 0;
+};
+ShimScratch g_shim[64];
+
+}  // namespace
+
+extern "C" {
+
+const char* mxmoe_last_error(void) { return g_err; }
+int mxmoe_version(void) { return 100; }
+
+int mxmoe_device_sm_count(void) {
+  DeviceState* st = nullptr;
+  int rc          = device_state(&st);
+  if (rc) return -rc;
+  return st->sm_count;
+}
+
+size_t mxmoe_gg_workspace_bytes(int problem_count) {
+  if (problem_count < 0) problem_count = 0;
+  return sizeof(mxb::GGStatus) + sizeof(mxb::GGProblemDev) * (size_t)problem_count;
+}
+
+int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,
+                     void* stream, mxmoe_gg_plan* plan) {
+  if (problem_count < 0 || (problem_count > 0 && !problems)) return fail(MXMOE_ERR_INVALID, "bad problem list");
+  if (problem_count > mxb::kMaxProblems) return fail(MXMOE_ERR_INVALID, "%d problems exceed the limit of %d per launch", problem_count, mxb::kMaxProblems);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return fail(MXMOE_ERR_WORKSPACE, "workspace must be a 256-byte aligned device pointer");
+  if (workspace_bytes < mxmoe_gg_workspace_bytes(problem_count)) return fail(MXMOE_ERR_WORKSPACE, "workspace of %zu B is smaller than the %zu B needed", workspace_bytes, mxmoe_gg_workspace_bytes(problem_count));
+  DeviceState* st = nullptr;
+  int rc          = device_state(&st);
+  if (rc) return rc;
+
+  std::vector<unsigned char> host(mxmoe_gg_workspace_bytes(problem_count));
+  std::memset(host.data(), 0, host.size());
+  auto* status = reinterpret_cast<mxb::GGStatus*>(host.data());
+  auto* dev    = reinterpret_cast<mxb::GGProblemDev*>(host.data() + sizeof(mxb::GGStatus));
+  int kept = 0, needs_cvt = 0;
+  for (int i = 0; i < problem_count; ++i) {
+    if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
+    rc = build_problem(st->encode, problems[i], i, dev + kept);
+    if (rc) return rc;
+    if (dev[kept].scheme == mxb::SCH_W4A4 || dev[kept].scheme == mxb::SCH_W4A16G128) needs_cvt = 1;
+    ++kept;
+  }
+  status->count     = kept;
+  status->needs_cvt = needs_cvt;
+  // pageable source: the runtime stages the bytes before returning, so `host` may go out of scope
+  CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), sizeof(mxb::GGStatus) + sizeof(mxb::GGProblemDev) * (size_t)kept,
+                           cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  if (plan) {
+    plan->count     = kept;
+    plan->needs_cvt = needs_cvt;
+  }
+  return MXMOE_OK;
+}
+
+int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream) {
+  if (!workspace || !plan) return fail(MXMOE_ERR_WORKSPACE, "null workspace or plan");
+  DeviceState* st = nullptr;
+  int rc          = device_state(&st);
+  if (rc) return rc;
+  const int count = plan->count, needs_cvt = plan->needs_cvt;
+  if (count < 0 || count > mxb::kMaxProblems) return fail(MXMOE_ERR_WORKSPACE, "plan holds an invalid problem count %d", count);
+  if (count == 0) return MXMOE_OK;
+  if (num_ctas <= 0 || num_ctas > st->sm_count) num_ctas = st->sm_count;
+  auto* status = static_cast<mxb::GGStatus*>(workspace);
+  auto* probs  = reinterpret_cast<const mxb::GGProblemDev*>(static_cast<unsigned char*>(workspace) + sizeof(mxb::GGStatus));
+  mxb::gg_launch_kernel(probs, count, status, needs_cvt != 0, num_ctas, static_cast<cudaStream_t>(stream));
+  CUDA_TRY(cudaGetLastError());
+  return MXMOE_OK;
+}
+
+int mxmoe_gg_launch(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  mxmoe_gg_plan plan;
+  int rc = mxmoe_gg_prepare(problems, problem_count, workspace, workspace_bytes, stream, &plan);
+  if (rc) return rc;
+  return mxmoe_gg_run(workspace, &plan, 0, stream);
+}
+
+int mxmoe_gg_check(void* workspace, void* stream) {
+  if (!workspace) return fail(MXMOE_ERR_WORKSPACE, "null workspace");
+  int words[2] = {0, 0};
+  CUDA_TRY(cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (words[0] != 0) {
+    static const char* roles[] = {"?", "producer", "mma(accumulator)", "mma(operands)", "epilogue", "converter"};
+    const int role = (words[1] >> 24) & 0xff;
+    return fail(MXMOE_ERR_DEVICE, "kernel reported error %d (%s) in role %s at tile %d", words[0],
+                words[0] == mxb::kDevErrTimeout ? "bounded wait ran out" : "too many problems",
+                role < 6 ? roles[role] : "?", words[1] & 0xffffff);
+  }
+  return MXMOE_OK;
+}
+
+int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, void** ptr_scale_b, void** ptr_Cs,
+                             void** ptr_Ds, int64_t*, int64_t*, int64_t*, int64_t*, const uint32_t*,
+                             const uint32_t* host_problem_sizes, const mxmoe_qparams*,
+                             const mxmoe_qparams* host_qparams, int problem_count) {
+  (void)ptr_Ds;  // aliases ptr_Cs in every reference call site
+  if (problem_count <= 0) return MXMOE_OK;
+  if (!ptr_As || !ptr_Bs || !ptr_Cs || !host_problem_sizes || !host_qparams) return fail(MXMOE_ERR_INVALID, "null argument");
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  const size_t n = (size_t)problem_count;
+  std::vector<void*> hA(n), hB(n), hSa(n, nullptr), hSb(n, nullptr), hC(n);
+  CUDA_TRY(cudaMemcpy(hA.data(), ptr_As, n * sizeof(void*), cudaMemcpyDeviceToHost));
+  CUDA_TRY(cudaMemcpy(hB.data(), ptr_Bs, n * sizeof(void*), cudaMemcpyDeviceToHost));
+  CUDA_TRY(cudaMemcpy(hC.data(), ptr_Cs, n * sizeof(void*), cudaMemcpyDeviceToHost));
+  if (ptr_scale_a) CUDA_TRY(cudaMemcpy(hSa.data(), ptr_scale_a, n * sizeof(void*), cudaMemcpyDeviceToHost));
+  if (ptr_scale_b) CUDA_TRY(cudaMemcpy(hSb.data(), ptr_scale_b, n * sizeof(void*), cudaMemcpyDeviceToHost));
+  std::vector<mxmoe_gg_problem> probs(n);
+  std::memset(probs.data(), 0, n * sizeof(mxmoe_gg_problem));
+  for (size_t i = 0; i < n; ++i) {
+    probs[i].A = hA[i]; probs[i].B = hB[i]; probs[i].C = hC[i];
+    probs[i].scale_a = hSa[i]; probs[i].scale_b = hSb[i];
+    probs[i].M = (int)host_problem_sizes[3 * i + 0];
+    probs[i].N = (int)host_problem_sizes[3 * i + 1];
+    probs[i].K = (int)host_problem_sizes[3 * i + 2];
+    probs[i].q = host_qparams[i];
+  }
+  // grow-only scratch owned by the shim (the reference launcher allocates and frees per call)
+  ShimScratch& sc = g_shim[dev & 63];
+  const size_t need = mxmoe_gg_workspace_bytes(problem_count);
+  if (sc.ws_bytes < need) {
+    if (sc.ws) cudaFree(sc.ws);
+    sc.ws = nullptr; sc.ws_bytes = 0;
+    CUDA_TRY(cudaMalloc(&sc.ws, need));
+    sc.ws_bytes = need;
+  }
+  int rc = mxmoe_gg_launch(probs.data(), problem_count, sc.ws, sc.ws_bytes, nullptr);
+  if (rc) return rc;
+  return mxmoe_gg_check(sc.ws, nullptr);
+}
+
+static int to_act_args(const mxmoe_act_args* a, mxb::ActArgs* o, bool silu) {
+  if (!a) return fail(MXMOE_ERR_INVALID, "null args");
+  if (!a->in || !a->q_store || !a->exp_qtag || !a->exp_row_start || !a->exp_q_off || !a->exp_s_off)
+    return fail(MXMOE_ERR_INVALID, "null pointer in activation arguments");
+  if (a->rows_routed > 0 && !a->row_expert) return fail(MXMOE_ERR_INVALID, "row_expert is required for routed rows");
+  if (!silu && a->rows_routed > 0 && !a->row_token) return fail(MXMOE_ERR_INVALID, "row_token is required for routed rows");
+  if (a->rows_routed < 0 || a->rows_total < a->rows_routed) return fail(MXMOE_ERR_INVALID, "bad row counts");
+  const bool has_shared = a->rows_total > a->rows_routed;
+  const int ks = has_shared ? a->k_shared : a->k;
+  if (a->k <= 0 || a->k % 8 || ks <= 0 || ks % 8) return fail(MXMOE_ERR_INVALID, "row length must be a positive multiple of 8 (k=%d, k_shared=%d)", a->k, ks);
+  if (a->k > 16384 || ks > 16384) return fail(MXMOE_ERR_UNSUPPORTED, "row length above 16384 is not supported");
+  if (silu && has_shared && !a->in_shared) return fail(MXMOE_ERR_INVALID, "in_shared is required for shared-expert rows");
+  if (!silu && a->rotate) {
+    if ((a->k & (a->k - 1)) != 0 || a->k < 256) return fail(MXMOE_ERR_UNSUPPORTED, "rotation needs a power-of-two row length >= 256 (k=%d)", a->k);
+    if (has_shared && ks != a->k) return fail(MXMOE_ERR_INVALID, "rotation needs k_shared == k");
+  }
+  o->in = static_cast<const __half*>(a->in);
+  o->in_shared = static_cast<const __half*>(a->in_shared);
+  o->q_store = static_cast<__half*>(a->q_store);
+  o->s_store = static_cast<__half*>(a->s_store);
+  o->row_expert = a->row_expert;
+  o->row_token = a->row_token;
+  o->exp_qtag = a->exp_qtag;
+  o->exp_row_start = a->exp_row_start;
+  o->exp_q_off = a->exp_q_off;
+  o->exp_s_off = a->exp_s_off;
+  o->signs = a->signs;
+  o->k = a->k;
+  o->k_shared = ks;
+  o->rows_routed = a->rows_routed;
+  o->rows_total = a->rows_total;
+  o->num_experts = a->num_experts;
+  o->rotate = silu ? 0 : a->rotate;
+  return MXMOE_OK;
+}
+
+int mxmoe_quant_act(const mxmoe_act_args* args, void* stream) {
+  mxb::ActArgs a;
+  int rc = to_act_args(args, &a, false);
+  if (rc) return rc;
+  CUDA_TRY(mxb::launch_quant_act(a, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+int mxmoe_silu_mul_then_quant(const mxmoe_act_args* args, void* stream) {
+  mxb::ActArgs a;
+  int rc = to_act_args(args, &a, true);
+  if (rc) return rc;
+  CUDA_TRY(mxb::launch_silu_mul_quant(a, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+
+size_t mxmoe_route_workspace_bytes(int num_tokens, int topk, int num_experts) {
+  if (num_tokens < 0 || topk <= 0 || num_experts <= 0) return 0;
+  return mxb::route_workspace_bytes(num_tokens, topk, num_experts);
+}
+
+int mxmoe_route_topk(const mxmoe_route_args* a, void* stream) {
+  if (!a) return fail(MXMOE_ERR_INVALID, "null args");
+  if (a->num_tokens < 0 || a->topk <= 0 || a->num_experts <= 0 || a->num_experts > 512)
+    return fail(MXMOE_ERR_INVALID, "bad routing shape T=%d topk=%d E=%d (E <= 512)", a->num_tokens, a->topk, a->num_experts);
+  if ((long long)a->num_tokens * a->topk > 0x3fffffffLL) return fail(MXMOE_ERR_INVALID, "too many (token, slot) pairs");
+  if (!a->counts || !a->row_start || !a->workspace) return fail(MXMOE_ERR_INVALID, "null output or workspace pointer");
+  if (a->num_tokens > 0 && (!a->topk_ids || !a->row_expert || !a->row_token || !a->slot_row))
+    return fail(MXMOE_ERR_INVALID, "null pointer in routing arguments");
+  if (a->workspace_bytes < mxb::route_workspace_bytes(a->num_tokens, a->topk, a->num_experts))
+    return fail(MXMOE_ERR_WORKSPACE, "routing workspace of %zu B is too small", a->workspace_bytes);
+  mxb::RouteArgs r;
+  r.topk_ids = a->topk_ids; r.counts = a->counts; r.row_start = a->row_start; r.row_expert = a->row_expert;
+  r.row_token = a->row_token; r.slot_row = a->slot_row; r.workspace = a->workspace;
+  r.workspace_bytes = a->workspace_bytes;
+  r.num_tokens = a->num_tokens; r.topk = a->topk; r.num_experts = a->num_experts; r.reserved = 0;
+  CUDA_TRY(mxb::launch_route(r, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk_weights, const void* y_shared,
+                       void* out, int num_tokens, int topk, int hidden, void* stream) {
+  if (!y || !slot_row || !out) return fail(MXMOE_ERR_INVALID, "null pointer in combine arguments");
+  if (num_tokens < 0 || topk <= 0 || hidden <= 0 || hidden % 8) return fail(MXMOE_ERR_INVALID, "bad combine shape T=%d topk=%d H=%d (H %% 8 == 0)", num_tokens, topk, hidden);
+  CUDA_TRY(mxb::launch_combine(y, slot_row, topk_weights, y_shared, out, num_tokens, topk, hidden,
+                               static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+}  // extern "C"

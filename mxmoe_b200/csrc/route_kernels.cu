@@ -1,0 +1,179 @@
+// Device-side routing for the MoE grouped GEMM: a stable counting sort of the
+// (token, slot) pairs by expert, and the weighted un-permute of expert outputs.
+//
+// The reference does the permutation with torch::sort / bincount and copies the
+// per-expert counts to the host (mxmoe/kernels/src/ref_bind.cu:47-64, :449-453),
+// which costs a host synchronisation per layer; its un-permute is an empty stub
+// (`gg_unpermute_out(){}`, ref_bind.cu:66).  Here the counts, the row offsets and
+// the permutation stay on the device and feed the grouped GEMM's problem list
+// directly.  Rows of one expert keep the order of the flattened (token, slot)
+// index, i.e. the result equals a stable sort.
+#include "route_kernels.h"
+
+#include <cuda_fp16.h>
+
+namespace mxb {
+namespace {
+
+constexpr int kChunk   = 1024;  // (token, slot) pairs per block
+constexpr int kThreads = 256;
+constexpr int kMaxE    = 512;
+
+__global__ void __launch_bounds__(kThreads) route_count_kernel(RouteArgs a) {
+  __shared__ int hist[kMaxE];
+  const int n = a.num_tokens * a.topk;
+  for (int e = threadIdx.x; e < a.num_experts; e += kThreads) hist[e] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kChunk;
+  for (int i = threadIdx.x; i < kChunk; i += kThreads) {
+    const int idx = base + i;
+    if (idx < n) {
+      const int e = a.topk_ids[idx];
+      if (e >= 0 && e < a.num_experts) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < a.num_experts; e += kThreads) a.workspace[blockIdx.x * a.num_experts + e] = hist[e];
+}
+
+// one block: per-expert exclusive prefix over blocks, then exclusive prefix over experts
+__global__ void __launch_bounds__(kThreads) route_scan_kernel(RouteArgs a, int nblocks) {
+  __shared__ int total[kMaxE];
+  __shared__ int start[kMaxE + 1];
+  const int E = a.num_experts;
+  for (int e = threadIdx.x; e < E; e += kThreads) {
+    int run = 0;
+    for (int b = 0; b < nblocks; ++b) {
+      const int c = a.workspace[b * E + e];
+      a.workspace[b * E + e] = run;
+      run += c;
+    }
+    total[e] = run;
+    a.counts[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) { start[e] = run; run += total[e]; }
+    start[E] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += kThreads) a.row_start[e] = start[e];
+  for (int i = threadIdx.x; i < nblocks * E; i += kThreads) a.workspace[i] += start[i % E];
+}
+
+__global__ void __launch_bounds__(kThreads) route_scatter_kernel(RouteArgs a) {
+  __shared__ int wbase[kThreads / 32][kMaxE];
+  const int n    = a.num_tokens * a.topk;
+  const int E    = a.num_experts;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kWarps   = kThreads / 32;
+  constexpr int kPerWarp = kChunk / kWarps;  // contiguous pairs per warp
+  for (int i = threadIdx.x; i < kWarps * kMaxE; i += kThreads) (&wbase[0][0])[i] = 0;
+  __syncthreads();
+  const int wstart = blockIdx.x * kChunk + warp * kPerWarp;
+  // pass 1: per-warp histogram
+  for (int p = 0; p < kPerWarp; p += 32) {
+    const int idx = wstart + p + lane;
+    int e = -1;
+    if (idx < n) { e = a.topk_ids[idx]; if (e < 0 || e >= E) e = -1; }
+    const unsigned m = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (m & ((1u << lane) - 1)) == 0) wbase[warp][e] += __popc(m);
+    __syncwarp();
+  }
+  __syncthreads();
+  // exclusive prefix over the warps of the block, on top of the block's base
+  for (int e = threadIdx.x; e < E; e += kThreads) {
+    int run = a.workspace[blockIdx.x * E + e];
+    for (int w = 0; w < kWarps; ++w) { const int c = wbase[w][e]; wbase[w][e] = run; run += c; }
+  }
+  __syncthreads();
+  // pass 2: place
+  for (int p = 0; p < kPerWarp; p += 32) {
+    const int idx = wstart + p + lane;
+    int e = -1;
+    if (idx < n) { e = a.topk_ids[idx]; if (e < 0 || e >= E) e = -1; }
+    const unsigned m  = __match_any_sync(0xffffffffu, e);
+    const unsigned lt = m & ((1u << lane) - 1);
+    if (e >= 0) {
+      const int dst = wbase[warp][e] + __popc(lt);
+      a.row_expert[dst] = e;
+      a.row_token[dst]  = idx / a.topk;
+      a.slot_row[idx]   = dst;
+    } else if (idx < n) {
+      a.slot_row[idx] = -1;
+    }
+    __syncwarp();
+    if (e >= 0 && lt == 0) wbase[warp][e] += __popc(m);
+    __syncwarp();
+  }
+}
+
+// out[t] = sum_j w[t,j] * y[slot_row[t,j]] (+ y_shared[t]); fp32 accumulation, fp16 result
+__global__ void __launch_bounds__(kThreads) combine_kernel(const __half* __restrict__ y, const int* __restrict__ slot_row,
+                                                           const float* __restrict__ w, const __half* __restrict__ ysh,
+                                                           __half* __restrict__ out, int topk, int hidden) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden / 8; c += kThreads) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      const int r = slot_row[t * topk + j];
+      if (r < 0) continue;
+      const float wt = w ? w[t * topk + j] : 1.f;
+      const uint4 v  = __ldg(reinterpret_cast<const uint4*>(y + (int64_t)r * hidden) + c);
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        acc[2 * e] += wt * f.x;
+        acc[2 * e + 1] += wt * f.y;
+      }
+    }
+    if (ysh) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(ysh + (int64_t)t * hidden) + c);
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+    reinterpret_cast<uint4*>(out + (int64_t)t * hidden)[c] = o;
+  }
+}
+
+}  // namespace
+
+size_t route_workspace_bytes(int num_tokens, int topk, int num_experts) {
+  const long long n = (long long)num_tokens * topk;
+  const long long nblocks = (n + kChunk - 1) / kChunk;
+  return (size_t)(nblocks > 0 ? nblocks : 1) * (size_t)num_experts * sizeof(int);
+}
+
+cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream) {
+  const int n = a.num_tokens * a.topk;
+  const int nblocks = (n + kChunk - 1) / kChunk;
+  if (a.num_experts > kMaxE) return cudaErrorInvalidValue;
+  if (nblocks > 0) route_count_kernel<<<nblocks, kThreads, 0, stream>>>(a);
+  route_scan_kernel<<<1, kThreads, 0, stream>>>(a, nblocks);
+  if (nblocks > 0) route_scatter_kernel<<<nblocks, kThreads, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const void* y, const int* slot_row, const float* topk_w, const void* y_shared, void* out,
+                           int num_tokens, int topk, int hidden, cudaStream_t stream) {
+  if (num_tokens <= 0) return cudaSuccess;
+  combine_kernel<<<num_tokens, kThreads, 0, stream>>>(static_cast<const __half*>(y), slot_row, topk_w,
+                                                      static_cast<const __half*>(y_shared), static_cast<__half*>(out),
+                                                      topk, hidden);
+  return cudaGetLastError();
+}
+
+}  // namespace mxb

@@ -1,0 +1,26 @@
+// Device-side routing (token -> expert permutation) and weighted combine.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace mxb {
+
+struct RouteArgs {
+  const int* topk_ids;   // [T, topk] expert of every (token, slot)
+  int* counts;           // [E]      rows per expert
+  int* row_start;        // [E + 1]  exclusive prefix of counts; row_start[E] = routed rows
+  int* row_expert;       // [T*topk] expert of every sorted row
+  int64_t* row_token;    // [T*topk] source token of every sorted row
+  int* slot_row;         // [T*topk] sorted row of every (token, slot); -1 for an invalid expert id
+  int* workspace;        // per-block histograms
+  size_t workspace_bytes;
+  int num_tokens, topk, num_experts, reserved;
+};
+
+size_t route_workspace_bytes(int num_tokens, int topk, int num_experts);
+cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream);
+cudaError_t launch_combine(const void* y, const int* slot_row, const float* topk_w, const void* y_shared, void* out,
+                           int num_tokens, int topk, int hidden, cudaStream_t stream);
+
+}  // namespace mxb
