@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the mixed-precision MoE layer (routing -> quantise -> grouped GEMM gate_up ->
+silu*mul+quantise -> grouped GEMM down -> combine) on synthetic data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One step = one pass of the layer over one batch.  Prints ONE JSON line (rank 0).
+Metric: effective TFLOP/s = sum over problems of 2*M*N*K / step time (the reference's definition,
+mxmoe/kernels/src/test.cu:109-116), whole job; tokens/s is reported beside it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_grouped_gemm_effective_tflops"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["source"] = "fallback"
+    return p
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8)),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40)),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20)),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)),
+        }
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                if get_reasons:
+                    r = get_reasons(self.h)
+                    for k, bit in names.items():
+                        if r & bit:
+                            self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr:
+            self._thr.join(timeout=1)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_expert_loop(spec, budget_s: float, threads: int, repeats: int = 1):
+    """Time the oracle's restatement of the reference's torch CPU path (fake-quant dequant-then-matmul
+    expert loop) on a bounded sample of the workload.  Returns (tflops, seconds, sample description)."""
+    from oracle import quant as oq
+    from oracle import hadamard as oh
+    from mxmoe_b200 import workload
+    torch.set_num_threads(threads)
+    ids, _ = workload.make_routing(spec)
+    gu_s, dn_s = workload.draw_schemes(spec)
+    signs = workload.rotation_signs(spec)
+    srt, order = torch.sort(ids.reshape(-1).long(), stable=True)
+    tok = order // spec.topk
+    counts = torch.bincount(srt, minlength=spec.num_experts).tolist()
+    hidden = workload.make_hidden(spec)
+    x = oh.hadamard_rows(hidden.float() * signs.float()).half() if signs is not None else hidden
+
+    def run_expert(e, rows):
+        wgu, wdn = workload.expert_weights_fp16(spec, e)
+        if signs is not None:
+            wgu = workload.rotate_rows(wgu, signs)
+        xe = x[rows]
+        t0 = time.perf_counter()
+        y1 = oq.fake_quant_expert_loop([xe], [wgu], [gu_s[e]])[0]
+        i = wdn.shape[1]
+        h = torch.nn.functional.silu(y1[:, :i].float()).half() * y1[:, i:]
+        oq.fake_quant_expert_loop([h], [wdn], [dn_s[e]])
+        dt = time.perf_counter() - t0
+        return dt, 2 * len(rows) * (wgu.numel() + wdn.numel())
+
+    # coldest experts first: many small problems, like the tail of the real workload, then hotter ones
+    order_e = sorted(range(spec.num_experts), key=lambda e: counts[e])
+    starts = [0]
+    for c in counts:
+        starts.append(starts[-1] + c)
+    total_t, total_f, used, rows_used = 0.0, 0, [], 0
+    run_expert(order_e[0], tok[starts[order_e[0]]:starts[order_e[0]] + max(1, counts[order_e[0]])])  # warm-up
+    for e in order_e:
+        if counts[e] == 0:
+            continue
+        dt, fl = run_expert(e, tok[starts[e]:starts[e] + counts[e]])
+        total_t += dt
+        total_f += fl
+        used.append(e)
+        rows_used += counts[e]
+        if total_t >= budget_s:
+            break
+    desc = (f"{len(used)} of {spec.num_experts} experts ({rows_used} of {sum(counts)} routed rows, coldest first), "
+            f"gate_up + silu*mul + down, weights generated outside the timed region")
+    return total_f / total_t / 1e12, total_t, desc
+
+
+def run_reference_arm(args, spec):
+    """`--impl reference`: the reference's CPU implementation of the path on the host cores.
+
+    The reference's torch code cannot travel to the GPU box, so the arm runs the oracle's port of it
+    (oracle/quant.py: fake-quant dequant-then-matmul expert loop), with all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals = []
+    for i in range(args.warmup + args.steps):
+        tf, secs, desc = cpu_expert_loop(spec, budget_s=max(1.0, 60.0 / max(1, args.steps + args.warmup)), threads=threads)
+        if i >= args.warmup:
+            vals.append((tf, secs))
+    tf = sum(v[0] for v in vals) / len(vals)
+    ms = sum(v[1] for v in vals) / len(vals) * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": spec.name, "tokens": spec.tokens, "note": "CPU port of the reference torch path"},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="qwen15-w4a4-8192")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for cpu_baseline")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    from mxmoe_b200 import workload
+    spec = workload.CONFIGS[args.workload]
+    if args.impl == "reference":
+        return run_reference_arm(args, spec)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the kernels)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from mxmoe_b200 import _lib
+    from mxmoe_b200.layer import MoELayer
+    _lib.lib()  # fail loudly if the CUDA library is missing
+    peaks = load_peaks()
+
+    T = spec.tokens                       # tokens per rank (weak scaling: the global batch is T * world)
+    ids, wts = workload.make_routing(spec, seed=2 + rank)
+    hidden_host = workload.make_hidden(spec, seed=1 + rank).pin_memory()
+    ids_host, wts_host = ids.pin_memory(), wts.pin_memory()
+    out_host = torch.empty((T, spec.hidden), dtype=torch.float16).pin_memory()
+
+    if world > 1:
+        from mxmoe_b200.ep import EPMoELayer
+        layer = EPMoELayer(spec, dev, gen_device=dev)
+    else:
+        gate_up, down, signs, _ = workload.build_layer_weights(spec, gen_device=dev, device=dev)
+        layer = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, T,
+                         shared_inter=spec.shared_inter, signs=signs, rotate=spec.rotate, device=dev)
+    hidden = hidden_host.to(dev, non_blocking=True)
+    ids_d, wts_d = ids_host.to(dev, non_blocking=True), wts_host.to(dev, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        return layer.forward(hidden, ids_d, wts_d)
+
+    # ---- warm-up, correctness guard
+    for _ in range(args.warmup):
+        step_resident()
+    layer.check()
+
+    # ---- per-launch timing of the dominant kernel (grouped GEMM), events on the launching stream
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    if world == 1:
+        gg1_run, gg2_run = layer.gg1.run, layer.gg2.run
+        state = {"i": 0}
+
+        def timed_gg1():
+            e = ev[state["i"]]
+            e[0].record(); gg1_run(); e[1].record()
+
+        def timed_gg2():
+            e = ev[state["i"]]
+            e[2].record(); gg2_run(); e[3].record()
+        layer.gg1.run, layer.gg2.run = timed_gg1, timed_gg2
+
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.steps):
+        if world == 1:
+            state["i"] = i
+        step_resident()
+    t1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_total = t0.elapsed_time(t1)
+    layer.check()
+    if world == 1:
+        layer.gg1.run, layer.gg2.run = gg1_run, gg2_run
+
+    # ---- end-to-end through the public API with host buffers (H2D of inputs + D2H of the result inside)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 50))
+    for _ in range(2):
+        out_host.copy_(layer.forward(hidden_host.to(dev, non_blocking=True), ids_host.to(dev, non_blocking=True),
+                                     wts_host.to(dev, non_blocking=True)), non_blocking=True)
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        h = hidden_host.to(dev, non_blocking=True)
+        i_ = ids_host.to(dev, non_blocking=True)
+        w_ = wts_host.to(dev, non_blocking=True)
+        out_host.copy_(layer.forward(h, i_, w_), non_blocking=True)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    # ---- aggregate over ranks (max time)
+    counts = layer.counts_host() if world > 1 else layer.counts.cpu().tolist()
+    flops_rank = spec.flops()             # every rank contributes T tokens worth of routed + shared work
+    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = times.tolist()
+    ms_step = ms_total / args.steps
+    value = flops_rank * world / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_rank * world / (ms_e2e / e2e_steps * 1e-3) / 1e12
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "i8" if "a4" in spec.scheme or "a8" in spec.scheme else ("f16" if spec.scheme != "mixed5" else "i8+f16"),
+        "data": "synthetic",
+        "tokens_per_s": T * world / (ms_step * 1e-3),
+        "config": {"workload": spec.name, "tokens_per_gpu": T, "experts": spec.num_experts, "topk": spec.topk,
+                   "hidden": spec.hidden, "inter": spec.inter, "shared_inter": spec.shared_inter,
+                   "scheme": spec.scheme, "parallelism": f"ep{world}" if world > 1 else "single",
+                   "l2": "operands+outputs per step (>700 MB) exceed the 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hidden_host.numel() * 2 + ids_host.numel() * 4 + wts_host.numel() * 4,
+                "d2h_bytes_per_step": out_host.numel() * 2, "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
+        "gpu_launches": args.steps * (8 if world == 1 else layer.launches_per_step),
+    }
+
+    if world == 1:
+        # dominant kernel: the persistent grouped GEMM (2 launches per step)
+        torch.cuda.synchronize()
+        d1 = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+        d2 = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
+        gemm_ms = (d1 + d2) / 2
+        flops_launch = flops_rank / 2
+        int_kind = spec.scheme in ("w4a4_g-1_sym", "w8a8_g-1_sym", "mixed_w8w4")
+        peak = peaks["bf16_tflops"] * (2.0 if int_kind else 1.0)
+        achieved = flops_launch / (gemm_ms * 1e-3) / 1e12
+        bytes_launch = layer.gemm_bytes(counts) / 2
+        line["roofline"] = {
+            "bound": "tensor", "kernel": "gg_persistent_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "traffic": None,
+            "peak_source": f"{peaks['source']} cuBLAS bf16 burst x{2 if int_kind else 1} (tcgen05 kind::i8 issues at twice the bf16 rate)",
+            "launch_ms": {"gate_up": d1, "down": d2},
+            "algorithmic_flops_per_launch": flops_launch,
+            "algorithmic_bytes_per_launch": bytes_launch,
+            "hbm_gbs_at_algorithmic_bytes": bytes_launch / (gemm_ms * 1e-3) / 1e9,
+            "hbm_peak_gbs": peaks["hbm_gbs"],
+        }
+        line["gemm_only_tflops"] = flops_rank / ((d1 + d2) * 1e-3) / 1e12
+        if not args.no_cpu and rank == 0:
+            threads = os.cpu_count() or 1
+            tf, secs, desc = cpu_expert_loop(spec, args.cpu_budget, threads)
+            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc,
+                                    "seconds": secs}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -53,7 +53,10 @@ typedef struct mxmoe_qparams {
  * is the number of rows the A buffer holds (0 = row0 + M); it bounds what the
  * TMA unit may touch.  If `m_dev` is set, the live row count is read on the
  * device from *m_dev (clamped to M); if `row0_dev` is set, row0 is read from
- * *row0_dev.  Both let a launch follow a routing result that never visits the host. */
+ * *row0_dev.  Both let a launch follow a routing result that never visits the host.
+ * `a_row_mul` scales the row shift of A only: an activation store that reserves
+ * one fp16-sized slot per row holds a_row_mul packed rows per slot, so expert
+ * rows that start at slot r start at packed row r * a_row_mul. */
 typedef struct mxmoe_gg_problem {
   const void* A;
   const void* B;
@@ -68,7 +71,7 @@ typedef struct mxmoe_gg_problem {
   int32_t ldc;
   mxmoe_qparams q;
   int32_t out_mode;
-  int32_t reserved_;
+  int32_t a_row_mul; /* 0 or 1: none; p > 1: rows of A start at row0 * p (A store whose row slots hold p packed rows) */
 } mxmoe_gg_problem;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -128,7 +131,11 @@ int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, v
  * (pseudo-expert `num_experts`).  The four per-expert device tables are the ones
  * the reference builds on the host at mxmoe/kernels/src/ref_bind.cu:475-505:
  * quantisation tag (0 fp16 copy, 1 int8 per token, 2 int4 per token), first row,
- * write offset of the packed rows and of the scales (both in fp16 elements). */
+ * write offset of the packed rows and of the scales (both in fp16 elements).
+ * exp_q_off / exp_s_off may be NULL: then every row owns one slot of k fp16
+ * elements in q_store, expert e's packed rows start at slot exp_row_start[e] and
+ * follow each other at their own packed pitch, and its scales start at
+ * s_store[exp_row_start[e]] - offsets that need no host knowledge of the counts. */
 typedef struct mxmoe_act_args {
   const void* in;             /* fp16 */
   const void* in_shared;      /* fp16, silu_mul_then_quant only */

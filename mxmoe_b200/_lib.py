@@ -39,7 +39,7 @@ class GGProblem(C.Structure):
         ("m_dev", C.c_void_p), ("row0_dev", C.c_void_p),
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
         ("a_rows", C.c_int32), ("row0", C.c_int32), ("ldc", C.c_int32),
-        ("q", QParams), ("out_mode", C.c_int32), ("reserved_", C.c_int32),
+        ("q", QParams), ("out_mode", C.c_int32), ("a_row_mul", C.c_int32),
     ]
 
 

@@ -41,8 +41,12 @@ __device__ __forceinline__ RowInfo locate_row(const ActArgs& a, int row) {
   r.tag  = a.exp_qtag[e];
   r.k    = (e == a.num_experts) ? a.k_shared : a.k;
   const int pack = r.tag == 0 ? 1 : (r.tag == 1 ? 2 : 4);
-  r.q_off = (int64_t)a.exp_q_off[e] + (int64_t)local * (r.k / pack);
-  r.s_off = (int64_t)a.exp_s_off[e] + local;
+  // without explicit offset tables every row owns one fp16-sized slot of `k` halfs: expert e's
+  // packed rows start at slot exp_row_start[e] and are stored back to back at their own pitch
+  const int64_t q0 = a.exp_q_off ? (int64_t)a.exp_q_off[e] : (int64_t)a.exp_row_start[e] * a.k;
+  const int64_t s0 = a.exp_s_off ? (int64_t)a.exp_s_off[e] : (int64_t)a.exp_row_start[e];
+  r.q_off = q0 + (int64_t)local * (r.k / pack);
+  r.s_off = s0 + local;
   return r;
 }
 

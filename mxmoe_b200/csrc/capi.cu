@@ -124,8 +124,9 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
     if ((reinterpret_cast<uintptr_t>(p.scale_b) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 16-byte aligned", idx);
   }
   if (p.out_mode != mxb::OUT_FP16 && p.out_mode != mxb::OUT_ACC) return fail(MXMOE_ERR_INVALID, "problem %d: bad out_mode %d", idx, p.out_mode);
-  const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
-  if (!p.row0_dev && a_rows < (uint64_t)p.row0 + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
+  const uint64_t a_mul  = p.a_row_mul > 1 ? (uint64_t)p.a_row_mul : 1;
+  const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 * a_mul + (uint64_t)p.M;
+  if (!p.row0_dev && a_rows < (uint64_t)p.row0 * a_mul + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
 
   const uint64_t K = (uint64_t)p.K, N = (uint64_t)p.N;
   switch (scheme) {
@@ -166,7 +167,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   d->scheme   = scheme;
   d->out_mode = p.out_mode;
   d->ldc      = ldc;
-  d->reserved = 0;
+  d->a_row_mul = p.a_row_mul > 1 ? p.a_row_mul : 1;
   return MXMOE_OK;
 }
 
@@ -310,7 +311,7 @@ int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, v
 
 static int to_act_args(const mxmoe_act_args* a, mxb::ActArgs* o, bool silu) {
   if (!a) return fail(MXMOE_ERR_INVALID, "null args");
-  if (!a->in || !a->q_store || !a->exp_qtag || !a->exp_row_start || !a->exp_q_off || !a->exp_s_off)
+  if (!a->in || !a->q_store || !a->exp_qtag || !a->exp_row_start)
     return fail(MXMOE_ERR_INVALID, "null pointer in activation arguments");
   if (a->rows_routed > 0 && !a->row_expert) return fail(MXMOE_ERR_INVALID, "row_expert is required for routed rows");
   if (!silu && a->rows_routed > 0 && !a->row_token) return fail(MXMOE_ERR_INVALID, "row_token is required for routed rows");

@@ -45,7 +45,7 @@ struct alignas(128) GGProblemDev {
   int scheme;
   int out_mode;
   int ldc;     // row pitch of C in elements
-  int reserved;
+  int a_row_mul;  // row shift of A = row0 * a_row_mul (>= 1)
 };
 static_assert(sizeof(GGProblemDev) == 384, "GGProblemDev layout");
 

@@ -1,0 +1,110 @@
+"""Grouped-GEMM launcher over torch device tensors.
+
+A :class:`Problem` is one ``C[M,N] = A[M,K] x B[N,K]^T`` with its quantisation
+scheme; :class:`GroupedGemm` turns a list of them into a prepared workspace
+(TMA descriptors encoded once) that can be launched any number of times on the
+current CUDA stream.  Torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+from typing import Sequence
+
+import torch
+
+from . import _lib
+
+OUT_FP16 = 0
+OUT_ACC = 1
+
+
+def _ptr(t) -> int | None:
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def current_stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+@dataclasses.dataclass
+class Problem:
+    """One problem of a grouped launch; tensors are CUDA tensors (or raw device addresses)."""
+    A: object
+    B: object
+    C: object
+    M: int
+    N: int
+    K: int
+    qparams: tuple            # (a_bits, w_bits, gsize, sym) as in the reference's QParams
+    scale_a: object = None
+    scale_b: object = None
+    row0: int = 0
+    a_rows: int = 0
+    ldc: int = 0
+    out_mode: int = OUT_FP16
+    m_dev: object = None      # int32 device scalar: live row count
+    row0_dev: object = None   # int32 device scalar: first row
+    a_row_mul: int = 0
+
+    def fill(self, c: _lib.GGProblem) -> None:
+        a_bits, w_bits, gsize, sym = self.qparams
+        c.A, c.B, c.C = _ptr(self.A), _ptr(self.B), _ptr(self.C)
+        c.scale_a, c.scale_b = _ptr(self.scale_a), _ptr(self.scale_b)
+        c.m_dev, c.row0_dev = _ptr(self.m_dev), _ptr(self.row0_dev)
+        c.M, c.N, c.K = int(self.M), int(self.N), int(self.K)
+        c.a_rows, c.row0, c.ldc = int(self.a_rows), int(self.row0), int(self.ldc)
+        c.q.a_bits, c.q.w_bits, c.q.gsize, c.q.sym = int(a_bits), int(w_bits), int(gsize), 1 if sym else 0
+        c.out_mode = int(self.out_mode)
+        c.a_row_mul = int(self.a_row_mul)
+
+    def flops(self) -> int:
+        return 2 * self.M * self.N * self.K
+
+
+class GroupedGemm:
+    """A prepared grouped launch.  ``run()`` enqueues the persistent kernel on the current stream."""
+
+    def __init__(self, problems: Sequence[Problem], device=None):
+        self.problems = list(problems)   # keeps the operand tensors alive
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        lib = _lib.lib()
+        n = len(self.problems)
+        self._arr = (_lib.GGProblem * max(n, 1))()
+        for i, p in enumerate(self.problems):
+            p.fill(self._arr[i])
+        nbytes = lib.mxmoe_gg_workspace_bytes(n)
+        self.workspace = torch.empty(nbytes + 256, dtype=torch.uint8, device=self.device)
+        base = self.workspace.data_ptr()
+        self._ws = (base + 255) & ~255
+        self._ws_bytes = nbytes
+        self._plan = _lib.GGPlan()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.mxmoe_gg_prepare(C.byref(self._arr), n, self._ws, nbytes, current_stream_ptr(),
+                                            C.byref(self._plan)))
+
+    @property
+    def kept(self) -> int:
+        return self._plan.count
+
+    def run(self, num_ctas: int = 0) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().mxmoe_gg_run(self._ws, C.byref(self._plan), num_ctas, current_stream_ptr()))
+
+    def check(self) -> None:
+        """Synchronise the current stream and raise if the kernel recorded an error."""
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().mxmoe_gg_check(self._ws, current_stream_ptr()))
+
+
+def grouped_gemm(problems: Sequence[Problem], check: bool = True) -> GroupedGemm:
+    """Prepare, launch once and (by default) check."""
+    g = GroupedGemm(problems)
+    g.run()
+    if check:
+        g.check()
+    return g

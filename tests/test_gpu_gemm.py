@@ -1,0 +1,186 @@
+"""Parity of the sm_100a grouped GEMM against the CPU oracle, through the C ABI.
+
+Integer schemes (w8a8, w4a4): int32 accumulators and the scaled fp16 output are
+compared bit for bit.  Floating-point schemes (fp16, w4a16 group-128):
+rel-L2 <= 1e-3 against the oracle (fp64 accumulation rounded once), the bound the
+specification states for fp16 outputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemm as og
+from mxmoe_b200 import gg
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+REL_L2 = 1e-3
+
+# (M, N, K): one tile / one k-block; ragged M; ragged N tile; several k-blocks; layer shapes
+SHAPES_INT = [(128, 256, 128), (1, 256, 128), (17, 256, 256), (129, 512, 384), (300, 2816, 2048), (77, 2048, 1408),
+              (256, 264, 128)]
+SHAPES_FP = [(128, 256, 64), (1, 256, 128), (17, 256, 128), (129, 512, 384), (300, 2816, 2048), (77, 2048, 1408),
+             (64, 264, 64)]
+SHAPES_W4A16 = [(128, 256, 128), (1, 256, 128), (17, 288, 256), (129, 512, 384), (300, 2816, 2048), (77, 2048, 1408)]
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("shape", SHAPES_INT)
+def test_int_accumulators_bit_exact(cuda_device, bits, shape):
+    rng = np.random.default_rng(hash((bits,) + shape) % 2**32)
+    c = util.WxAxCase(rng, *shape, bits)
+    util.run([c.problem(cuda_device, gg.OUT_ACC)])
+    got = c.C.cpu().numpy()
+    assert np.array_equal(got, c.acc), f"{np.count_nonzero(got != c.acc)} of {got.size} accumulators differ"
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("shape", SHAPES_INT)
+def test_int_scaled_output_bit_exact(cuda_device, bits, shape):
+    rng = np.random.default_rng(hash((bits, 1) + shape) % 2**32)
+    c = util.WxAxCase(rng, *shape, bits)
+    util.run([c.problem(cuda_device)])
+    got = c.C.cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), c.ref.view(np.uint16)), \
+        f"{np.count_nonzero(got.view(np.uint16) != c.ref.view(np.uint16))} of {got.size} outputs differ"
+
+
+def test_int_extreme_codes(cuda_device):
+    """All codes at +-max: the largest accumulator magnitude the scheme can produce."""
+    for bits, k in ((8, 2048), (4, 14336)):
+        hi = 2 ** (bits - 1) - 1
+        rng = np.random.default_rng(bits)
+        c = util.WxAxCase(rng, 130, 256, k, bits)
+        c.qa[:] = hi
+        c.qb[:] = -hi
+        c.qb[::2] = hi
+        c.acc = og.int_accumulate(c.qa, c.qb)
+        util.run([c.problem(cuda_device, gg.OUT_ACC)])
+        assert np.array_equal(c.C.cpu().numpy(), c.acc)
+
+
+@pytest.mark.parametrize("shape", SHAPES_FP)
+def test_fp16(cuda_device, shape):
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    c = util.Fp16Case(rng, *shape)
+    util.run([c.problem(cuda_device)])
+    err = og.rel_l2(c.C.cpu().numpy(), c.ref)
+    assert err <= REL_L2, err
+
+
+@pytest.mark.parametrize("shape", SHAPES_W4A16)
+def test_w4a16_g128(cuda_device, shape):
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    c = util.W4A16Case(rng, *shape)
+    util.run([c.problem(cuda_device)])
+    err = og.rel_l2(c.C.cpu().numpy(), c.ref)
+    assert err <= REL_L2, err
+    # fp32 accumulators of the same problem
+    util.run([c.problem(cuda_device, gg.OUT_ACC)])
+    ref32 = c.a.astype(np.float64) @ c.w.astype(np.float64).T
+    assert og.rel_l2(c.C.cpu().numpy(), ref32) <= 1e-4
+
+
+def test_mixed_schemes_one_launch(cuda_device):
+    """Four schemes, ragged and empty problems, in one grouped launch."""
+    rng = np.random.default_rng(7)
+    cases = [util.WxAxCase(rng, 200, 512, 256, 4), util.Fp16Case(rng, 33, 256, 192),
+             util.W4A16Case(rng, 140, 512, 256), util.WxAxCase(rng, 1, 256, 384, 8),
+             util.WxAxCase(rng, 257, 768, 128, 8), util.W4A16Case(rng, 5, 256, 128),
+             util.Fp16Case(rng, 129, 520, 64), util.WxAxCase(rng, 64, 256, 2048, 4)]
+    probs = [c.problem(cuda_device) for c in cases]
+    # an expert without tokens is dropped by the launcher (ref_bind.cu:345)
+    empty = util.Fp16Case(rng, 1, 256, 64).problem(cuda_device)
+    empty.M = 0
+    g = util.run(probs[:3] + [empty] + probs[3:])
+    assert g.kept == len(cases)
+    for c in cases:
+        got = c.C.cpu().numpy()
+        if isinstance(c, util.WxAxCase):
+            assert np.array_equal(got.view(np.uint16), c.ref.view(np.uint16))
+        else:
+            assert og.rel_l2(got, c.ref) <= REL_L2
+
+
+def test_direct_only_launch_uses_no_converter(cuda_device):
+    rng = np.random.default_rng(11)
+    cases = [util.WxAxCase(rng, 150, 512, 512, 8), util.Fp16Case(rng, 150, 512, 512)]
+    g = util.run([c.problem(cuda_device) for c in cases])
+    assert g._plan.needs_cvt == 0
+    assert np.array_equal(cases[0].C.cpu().numpy().view(np.uint16), cases[0].ref.view(np.uint16))
+    assert og.rel_l2(cases[1].C.cpu().numpy(), cases[1].ref) <= REL_L2
+
+
+def test_device_side_rows_and_offsets(cuda_device):
+    """Several experts share one activation buffer; row counts and offsets live in device memory."""
+    rng = np.random.default_rng(5)
+    counts = [130, 0, 1, 300]
+    k, n, bits = 256, 512, 8
+    total = sum(counts)
+    qa = util.rand_codes(rng, total, k, bits)
+    sa = util.rand_scales(rng, total, 0.01, 0.5)
+    from oracle import pack as op
+    A = util.t16(op.pack_k(qa, bits), cuda_device)
+    SA = util.t16(sa, cuda_device)
+    Cbuf = torch.full((total, n), float("nan"), dtype=torch.float16, device=cuda_device)
+    cnt = torch.tensor(counts, dtype=torch.int32, device=cuda_device)
+    starts = torch.tensor(np.concatenate(([0], np.cumsum(counts)[:-1])), dtype=torch.int32, device=cuda_device)
+    probs, refs, keep = [], [], []
+    for e, m in enumerate(counts):
+        qb = util.rand_codes(rng, n, k, bits)
+        sb = util.rand_scales(rng, n)
+        B, SB = util.t16(op.pack_k(qb, bits), cuda_device), util.t16(sb, cuda_device)
+        keep += [B, SB]
+        r0 = int(starts[e])
+        refs.append(og.wxax_epilogue(og.int_accumulate(qa[r0:r0 + m], qb), sa[r0:r0 + m], sb))
+        probs.append(gg.Problem(A=A, B=B, C=Cbuf, M=total, N=n, K=k, qparams=util.Q_W8A8, scale_a=SA, scale_b=SB,
+                                a_rows=total, m_dev=cnt.data_ptr() + 4 * e, row0_dev=starts.data_ptr() + 4 * e))
+    util.run(probs)
+    got = Cbuf.cpu().numpy()
+    r0 = 0
+    for m, ref in zip(counts, refs):
+        assert np.array_equal(got[r0:r0 + m].view(np.uint16), ref.view(np.uint16))
+        r0 += m
+
+
+def test_linearity_at_layer_size(cuda_device):
+    """Size-independent property at a full expert shape: the int32 accumulators are additive in A."""
+    rng = np.random.default_rng(3)
+    m, n, k = 1024, 2816, 2048
+    c1 = util.WxAxCase.__new__(util.WxAxCase)
+    qa1 = rng.integers(-3, 4, (m, k), dtype=np.int32)
+    qa2 = rng.integers(-3, 4, (m, k), dtype=np.int32)
+    qb = util.rand_codes(rng, n, k, 4)
+    outs = []
+    from oracle import pack as op
+    B = util.t16(op.pack_k(qb, 4), cuda_device)
+    for qa in (qa1, qa2, qa1 + qa2):
+        A = util.t16(op.pack_k(qa, 4), cuda_device)
+        Cacc = torch.zeros((m, n), dtype=torch.int32, device=cuda_device)
+        util.run([gg.Problem(A=A, B=B, C=Cacc, M=m, N=n, K=k, qparams=util.Q_W4A4, out_mode=gg.OUT_ACC)])
+        outs.append(Cacc)
+    assert torch.equal(outs[0] + outs[1], outs[2])
+    # and a checksum against the oracle on a row sample
+    rows = rng.choice(m, 16, replace=False)
+    assert np.array_equal(outs[2][rows].cpu().numpy(), og.int_accumulate((qa1 + qa2)[rows], qb))
+
+
+def test_bad_arguments_raise(cuda_device):
+    from mxmoe_b200._lib import MxMoEError
+    rng = np.random.default_rng(1)
+    c = util.Fp16Case(rng, 8, 256, 64)
+    p = c.problem(cuda_device)
+    p.qparams = (16, 3, -1, True)        # unsupported scheme
+    with pytest.raises(MxMoEError) as ei:
+        gg.GroupedGemm([p])
+    assert ei.value.status == 2
+    p = c.problem(cuda_device)
+    p.N = 252                             # N not a multiple of 8
+    with pytest.raises(MxMoEError) as ei:
+        gg.GroupedGemm([p])
+    assert ei.value.status == 1
+    p = c.problem(cuda_device)
+    p.A = c.A.data_ptr() + 2              # misaligned operand
+    with pytest.raises(MxMoEError):
+        gg.GroupedGemm([p])

@@ -1,0 +1,144 @@
+"""CPU tests of the host side: C-ABI exports, weight preparation, workload generation, error paths."""
+import ctypes
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pack as op
+from oracle import quant as oq
+from mxmoe_b200 import _lib, weights, workload
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "mxmoe_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(mxmoe_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = _lib.lib()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared but not exported"
+    assert declared == set(_lib.EXPORTS)
+
+
+def test_struct_layouts_match_header():
+    assert ctypes.sizeof(_lib.QParams) == 16
+    assert ctypes.sizeof(_lib.GGProblem) == 104
+    assert ctypes.sizeof(_lib.GGPlan) == 8
+    assert ctypes.sizeof(_lib.ActArgs) == 11 * 8 + 6 * 4
+    assert ctypes.sizeof(_lib.RouteArgs) == 8 * 8 + 4 * 4
+
+
+def test_no_device_is_an_error_not_a_fallback():
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    lib = _lib.lib()
+    assert lib.mxmoe_device_sm_count() == -6
+    plan = _lib.GGPlan()
+    p = (_lib.GGProblem * 1)()
+    rc = lib.mxmoe_gg_prepare(ctypes.byref(p), 1, 256, 4096, None, ctypes.byref(plan))
+    assert rc == 6 and b"no CUDA device" in lib.mxmoe_last_error()
+    assert lib.mxmoe_gg_workspace_bytes(10) == 256 + 10 * 384
+
+
+def test_argument_validation_without_device():
+    lib = _lib.lib()
+    assert lib.mxmoe_gg_prepare(None, 3, 256, 1 << 20, None, None) == 1
+    assert lib.mxmoe_gg_prepare(None, 0, None, 0, None, None) == 4
+    assert lib.mxmoe_gg_prepare(None, 100000, 256, 1 << 20, None, None) == 1
+    assert lib.mxmoe_quant_act(None, None) == 1
+    a = _lib.ActArgs()
+    assert lib.mxmoe_quant_act(ctypes.byref(a), None) == 1
+    r = _lib.RouteArgs()
+    r.num_tokens, r.topk, r.num_experts = 4, 2, 100000
+    assert lib.mxmoe_route_topk(ctypes.byref(r), None) == 1
+
+
+@pytest.mark.parametrize("scheme", weights.SCHEMES)
+def test_prepare_weight_matches_oracle_layouts(scheme):
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(64, 256, generator=g) * 0.02).half()
+    pw = weights.prepare_weight(w, scheme, keep_codes=True)
+    a, wb, gs, sym = weights.parse_scheme(scheme)
+    assert pw.qparams == (a, wb, gs, sym) == oq.scheme_tuple(scheme)
+    if scheme == "fp16":
+        assert torch.equal(pw.data, w) and pw.scale is None
+        return
+    codes, scale, zero = oq.minmax_quantize(w, wb, gs, sym)
+    assert torch.equal(pw.codes.to(torch.float16), codes)
+    packed = pw.data.numpy().view(np.uint16)
+    if gs == -1:
+        assert np.array_equal(packed, op.pack_k(codes.numpy().astype(np.int32), wb))
+        assert np.array_equal(pw.scale.numpy().view(np.uint16), scale.reshape(-1).numpy().view(np.uint16))
+    else:
+        assert np.array_equal(packed, op.pack_n4(codes.numpy().astype(np.int32)))
+        want = op.group_major_scales(scale.reshape(64, -1).numpy(), zero.reshape(64, -1).numpy())
+        assert np.array_equal(pw.scale.numpy().view(np.uint16), want.view(np.uint16))
+
+
+def test_prepare_weight_rejects_unknown_scheme():
+    w = torch.zeros(32, 128, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        weights.prepare_weight(w, "w3a16_g64_asym")
+    with pytest.raises(ValueError):
+        weights.prepare_weight(w, "bogus")
+    with pytest.raises(ValueError):
+        weights.prepare_weight(torch.zeros(30, 128, dtype=torch.float16), "w4a16_g128_asym")
+
+
+def test_routing_is_seeded_and_valid():
+    spec = workload.CONFIGS["qwen15-w4a4-512"]
+    ids, w = workload.make_routing(spec)
+    ids2, _ = workload.make_routing(spec)
+    assert torch.equal(ids, ids2) and ids.dtype == torch.int32 and ids.shape == (512, 4)
+    assert (ids.sort(dim=1).values.diff(dim=1) != 0).all(), "top-k without replacement"
+    assert torch.allclose(w.sum(1), torch.ones(512))
+    cnt = torch.bincount(ids.reshape(-1).long(), minlength=60)
+    assert cnt[0] > 4 * cnt.float().median(), "Zipf skew"
+    spec5 = workload.CONFIGS["mixtral-mixed-16384"]
+    ids5, _ = workload.make_routing(spec5, tokens=2000)
+    c5 = torch.bincount(ids5.reshape(-1).long(), minlength=8)
+    assert c5[0] == c5.max()
+
+
+def test_mixed_scheme_draw_hits_five_bits():
+    spec = workload.CONFIGS["qwen15-mixed-8192"]
+    gu, dn = workload.draw_schemes(spec)
+    assert len(gu) == len(dn) == 61
+    assert set(gu + dn) == set(weights.SCHEMES)
+    assert abs(workload.mean_weight_bits(spec, gu, dn) - 5.0) <= 0.02
+    assert (gu, dn) == workload.draw_schemes(spec)
+    gu5, dn5 = workload.draw_schemes(workload.CONFIGS["mixtral-mixed-16384"])
+    assert gu5 == dn5 and set(gu5) == {"w8a8_g-1_sym", "w4a4_g-1_sym"}
+
+
+def test_rotation_matches_oracle():
+    from oracle import hadamard as oh
+    spec = workload.CONFIGS["qwen15-w4a4-512"]
+    s = workload.rotation_signs(spec)
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(8, spec.hidden, generator=g) * 0.02).half()
+    got = workload.rotate_rows(w, s)
+    ref = oh.hadamard_rows(w.double() * s.double()).half()
+    assert torch.equal(got, ref)
+
+
+def test_workload_json_schema():
+    spec = workload.CONFIGS["ds2lite-w4a16-32"]
+    gu, dn = workload.draw_schemes(spec)
+    js = json.loads(workload.workload_json(spec, [1] * 64, gu, dn, layer=3))
+    assert js["num_tokens"] == 32
+    blk = js["layer-3"]
+    assert len(blk["gate_up"]) == 65 and len(blk["down"]) == 65
+    assert blk["gate_up"][0] == {"shape": [1, 2816, 2048], "w_bits": 4, "a_bits": 16, "gsize": 128, "sym": False}
+    assert blk["down"][-1]["shape"] == [32, 2048, 2816]
+
+
+def test_flops_formula():
+    spec = workload.CONFIGS["qwen15-w4a4-8192"]
+    assert spec.flops() == 2 * 32768 * (2816 * 2048 + 2048 * 1408)
