@@ -16,7 +16,6 @@
 
 /* codes are int8 (4-bit codes are passed already sign-extended) */
 void oracle_int_gemm(const int8_t* qa, const int8_t* qb, int M, int N, int K, int32_t* acc) {
-#pragma omp parallel for schedule(static)
   for (int m = 0; m < M; ++m) {
     const int8_t* a = qa + (size_t)m * K;
     for (int n = 0; n < N; ++n) {
@@ -42,7 +41,6 @@ static inline uint16_t f2h(float f) {
 
 /* sa, sb, out: IEEE binary16 bit patterns */
 void oracle_wxax_epilogue(const int32_t* acc, const uint16_t* sa, const uint16_t* sb, int M, int N, uint16_t* out) {
-#pragma omp parallel for schedule(static)
   for (int m = 0; m < M; ++m) {
     float fa = h2f(sa[m]);
     for (int n = 0; n < N; ++n) {
