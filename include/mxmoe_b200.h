@@ -188,6 +188,21 @@ typedef struct mxmoe_route_args {
 size_t mxmoe_route_workspace_bytes(int num_tokens, int topk, int num_experts);
 int mxmoe_route_topk(const mxmoe_route_args* args, void* stream);
 
+/* Same routing as mxmoe_route_topk for callers that cannot allocate device memory where they
+ * route (a serving loop whose memory pool is fixed at start-up, a plug-in that only receives
+ * its input and output buffers): `workspace` / `workspace_bytes` of the arguments are ignored
+ * and the per-block histograms go to a 256 KiB array built into the library.  This entry point
+ * has no counterpart in the reference.
+ *   limit     ceil(T * topk / 1024) * num_experts <= 65536, otherwise MXMOE_ERR_WORKSPACE;
+ *   memory    every GPU that loads the library holds the 256 KiB until the process exits;
+ *   set-up    the first call on each device looks up the array's device address (no allocation):
+ *             make that first call outside of any stream capture;
+ *   sharing   all calls on one device use the same array.  Nothing in it has to start at zero
+ *             (each call rewrites every word it later reads), but two calls whose kernels overlap
+ *             on the GPU - different streams without an ordering between them - race on it.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine. */
+int mxmoe_route_topk_static(const mxmoe_route_args* args, void* stream);
+
 /* out[t] = sum_j topk_weights[t,j] * y[slot_row[t,j]] (+ y_shared[t]); y is the
  * fp16 [rows, hidden] output of the down projection, accumulation in fp32.  The
  * reference leaves this step unimplemented (`gg_unpermute_out(){}`,

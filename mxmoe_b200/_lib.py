@@ -16,7 +16,7 @@ EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
     "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_launch", "mxmoe_gg_check",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_silu_mul_then_quant",
-    "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_combine_topk",
+    "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
 )
 
 
@@ -92,6 +92,7 @@ def lib() -> C.CDLL:
         l.mxmoe_route_workspace_bytes.restype = C.c_size_t
         l.mxmoe_route_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         l.mxmoe_route_topk.argtypes = [C.c_void_p, C.c_void_p]
+        l.mxmoe_route_topk_static.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_combine_topk.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int, C.c_int, C.c_int, C.c_void_p]
         _lib = l

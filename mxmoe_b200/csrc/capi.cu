@@ -386,6 +386,31 @@ int mxmoe_route_topk(const mxmoe_route_args* a, void* stream) {
   return MXMOE_OK;
 }
 
+int mxmoe_route_topk_static(const mxmoe_route_args* a, void* stream) {
+  if (!a) return fail(MXMOE_ERR_INVALID, "null args");
+  if (a->num_tokens < 0 || a->topk <= 0 || a->num_experts <= 0 || a->num_experts > 512)
+    return fail(MXMOE_ERR_INVALID, "bad routing shape T=%d topk=%d E=%d (E <= 512)", a->num_tokens, a->topk, a->num_experts);
+  if ((long long)a->num_tokens * a->topk > 0x3fffffffLL) return fail(MXMOE_ERR_INVALID, "too many (token, slot) pairs");
+  if (!a->counts || !a->row_start) return fail(MXMOE_ERR_INVALID, "null output pointer");
+  if (a->num_tokens > 0 && (!a->topk_ids || !a->row_expert || !a->row_token || !a->slot_row))
+    return fail(MXMOE_ERR_INVALID, "null pointer in routing arguments");
+  const size_t need = mxb::route_workspace_bytes(a->num_tokens, a->topk, a->num_experts) / sizeof(int);
+  if (need > mxb::route_static_scratch_ints())
+    return fail(MXMOE_ERR_WORKSPACE,
+                "routing %d x %d pairs over %d experts needs %zu scratch words; the built-in scratch holds %zu "
+                "(ceil(T*topk/1024) * E must not exceed it) - use mxmoe_route_topk with a workspace instead",
+                a->num_tokens, a->topk, a->num_experts, need, mxb::route_static_scratch_ints());
+  int* scratch = nullptr;
+  CUDA_TRY(mxb::route_static_scratch_ptr(&scratch));
+  mxb::RouteArgs r;
+  r.topk_ids = a->topk_ids; r.counts = a->counts; r.row_start = a->row_start; r.row_expert = a->row_expert;
+  r.row_token = a->row_token; r.slot_row = a->slot_row; r.workspace = scratch;
+  r.workspace_bytes = mxb::route_static_scratch_ints() * sizeof(int);
+  r.num_tokens = a->num_tokens; r.topk = a->topk; r.num_experts = a->num_experts; r.reserved = 0;
+  CUDA_TRY(mxb::launch_route(r, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
 int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk_weights, const void* y_shared,
                        void* out, int num_tokens, int topk, int hidden, void* stream) {
   if (!y || !slot_row || !out) return fail(MXMOE_ERR_INVALID, "null pointer in combine arguments");

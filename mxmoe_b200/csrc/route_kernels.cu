@@ -167,6 +167,40 @@ cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------
+// Routing without any caller-provided scratch.
+//
+// Some callers are not allowed to allocate device memory at the point where they
+// route tokens: code running between the nodes of a fixed serving loop whose
+// memory pool was sized at start-up, or a plug-in that is handed input and output
+// buffers by its host application and nothing else.  For them the per-block
+// histograms live in this file-scope device array instead of a workspace argument.
+// Every GPU that loads the library keeps these 256 KiB resident until the process
+// exits.
+constexpr int kStaticScratchInts = 64 * 1024;
+static __device__ __align__(256) int g_route_scratch[kStaticScratchInts];
+
+size_t route_static_scratch_ints() { return kStaticScratchInts; }
+
+// `g_route_scratch` names a host-side handle in host code, not a device address:
+// the address a kernel may use is looked up once per device, with that device current.
+cudaError_t route_static_scratch_ptr(int** out) {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_route_scratch);
+    if (e != cudaSuccess) return e;
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  *out = ptrs[dev];
+  return cudaSuccess;
+}
+
 cudaError_t launch_combine(const void* y, const int* slot_row, const float* topk_w, const void* y_shared, void* out,
                            int num_tokens, int topk, int hidden, cudaStream_t stream) {
   if (num_tokens <= 0) return cudaSuccess;

@@ -20,6 +20,9 @@ struct RouteArgs {
 
 size_t route_workspace_bytes(int num_tokens, int topk, int num_experts);
 cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream);
+// static-scratch variant (see route_kernels.cu)
+size_t route_static_scratch_ints();
+cudaError_t route_static_scratch_ptr(int** out);
 cudaError_t launch_combine(const void* y, const int* slot_row, const float* topk_w, const void* y_shared, void* out,
                            int num_tokens, int topk, int hidden, cudaStream_t stream);
 
