@@ -161,6 +161,30 @@ typedef struct mxmoe_act_args {
  * mxmoe/kernels/src/ref_bind.cu:531-544). */
 int mxmoe_quant_act(const mxmoe_act_args* args, void* stream);
 
+/* Quantise once per token, then copy.  With top-k routing every token feeds topk experts, so the
+ * rotation and the quantiser are evaluated once per token into token-major stores (one per
+ * activation format in use; a NULL store is not produced) and mxmoe_gather_rows copies each routed
+ * row from the store of its expert's format into the expert-sorted activation store.  The result is
+ * bit-identical to mxmoe_quant_act. */
+typedef struct mxmoe_token_quant_args {
+  const void* in;      /* fp16 hidden [T, k] */
+  void* f16;           /* rotated fp16 rows [T, k] (only needed when rotating and a 16-bit expert exists) */
+  void* q8;            /* int8 rows [T, k/2] uint16 words */
+  void* s8;            /* fp16 [T] */
+  void* q4;            /* int4 rows [T, k/4] uint16 words */
+  void* s4;            /* fp16 [T] */
+  const int8_t* signs; /* optional +-1 diagonal, length k */
+  int32_t k;
+  int32_t num_tokens;
+  int32_t rotate;
+  int32_t reserved_;
+} mxmoe_token_quant_args;
+
+int mxmoe_quant_tokens(const mxmoe_token_quant_args* args, void* stream);
+/* `rows` uses the tables of mxmoe_act_args (its `in` is ignored); every format tagged in
+ * rows->exp_qtag must have its store in `stores` (tag 0 reads stores->f16, or stores->in if NULL). */
+int mxmoe_gather_rows(const mxmoe_act_args* rows, const mxmoe_token_quant_args* stores, void* stream);
+
 /* h = silu(gate) * up over gate_up rows ([rows, 2k] fp16, gate first), then
  * quantise per token and pack for the down projection.  Replaces
  * `silu_mul_then_quant_kernel` (launched at mxmoe/kernels/src/ref_bind.cu:701-716). */

@@ -15,7 +15,8 @@ LIB_PATH = os.path.join(_HERE, "libmxmoe_b200.so")
 EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
     "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_launch", "mxmoe_gg_check",
-    "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_silu_mul_then_quant",
+    "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows",
+    "mxmoe_silu_mul_then_quant",
     "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
 )
 
@@ -58,6 +59,14 @@ class ActArgs(C.Structure):
     ]
 
 
+class TokenQuantArgs(C.Structure):
+    _fields_ = [
+        ("inp", C.c_void_p), ("f16", C.c_void_p), ("q8", C.c_void_p), ("s8", C.c_void_p), ("q4", C.c_void_p),
+        ("s4", C.c_void_p), ("signs", C.c_void_p),
+        ("k", C.c_int32), ("num_tokens", C.c_int32), ("rotate", C.c_int32), ("reserved_", C.c_int32),
+    ]
+
+
 class RouteArgs(C.Structure):
     _fields_ = [
         ("topk_ids", C.c_void_p), ("counts", C.c_void_p), ("row_start", C.c_void_p), ("row_expert", C.c_void_p),
@@ -89,6 +98,8 @@ def lib() -> C.CDLL:
         l.mxmoe_groupgemm_hz_fused.argtypes = [C.c_void_p] * 14 + [C.c_int]
         l.mxmoe_quant_act.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_silu_mul_then_quant.argtypes = [C.c_void_p, C.c_void_p]
+        l.mxmoe_quant_tokens.argtypes = [C.c_void_p, C.c_void_p]
+        l.mxmoe_gather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_route_workspace_bytes.restype = C.c_size_t
         l.mxmoe_route_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         l.mxmoe_route_topk.argtypes = [C.c_void_p, C.c_void_p]

@@ -6,8 +6,13 @@
 //                    mxmoe/kernels/src/ref_bind.cu:531-544; its source is not part
 //                    of the reference, so the contract is taken from the call site
 //                    and the quantiser from mxmoe/quant/quant.py:40-84)
-//   silu_mul_quant   h = silu(gate) * up on the gate_up output, then the same
-//                    quantise + pack for the down projection
+//   quant_tokens     the same rotation + quantisation done ONCE PER TOKEN into
+//   + gather_rows    token-major stores (one per activation format in use), then a
+//                    pure copy of each routed row into its expert's slot: with
+//                    top-k routing this does the arithmetic T times instead of
+//                    T*topk times
+//   silu_mul_quant   h = silu(gate) * up on the gate_up output, then quantise + pack
+//                    for the down projection
 //                    (`silu_mul_then_quant_kernel`, ref_bind.cu:701-716)
 //
 // A row is owned by 1, 2, 4 or 8 warps (<= 64 values per thread, kept in
@@ -56,164 +61,110 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// kWarps warps per row, rows_per_block = 8 / kWarps.  kSilu selects the loader.
-template <int kWarps, bool kSilu>
-__global__ void __launch_bounds__(kBlock) act_quant_kernel(ActArgs a) {
-  __shared__ float xch[kWarps > 1 ? kBlock * 8 : 1];   // cross-warp exchange, one chunk at a time
-  __shared__ float red[8];
+// chunk index of register row j of this thread: element index = chunk * 8 + e, bits e | lane | j | w
+template <int kWarps>
+__device__ __forceinline__ int chunk_of(int w, int j, int lane) { return (w * kJ + j) * 32 + lane; }
 
-  const int warp       = threadIdx.x >> 5;
-  const int lane       = threadIdx.x & 31;
-  const int row_in_blk = warp / kWarps;
-  const int w          = warp % kWarps;  // warp index within the row
-  const int row        = blockIdx.x * (8 / kWarps) + row_in_blk;
-  const bool row_ok    = row < a.rows_total;
+__device__ __forceinline__ void unpack8(const uint4& g, float (&x)[8]) {
+  const __half2* gh = reinterpret_cast<const __half2*>(&g);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __half22float2(gh[e]);
+    x[2 * e] = f.x;
+    x[2 * e + 1] = f.y;
+  }
+}
 
-  RowInfo ri{0, 0, 0, 0};
-  if (row_ok) ri = locate_row(a, row);
-  const int nchunk = ri.k >> 3;  // 16-byte chunks in the row
-
-  // ------------------------------------------------------------------ load
-  float x[kJ][8];
-  const __half* src = nullptr;
-  const __half* src_up = nullptr;
-  if (row_ok) {
-    if (kSilu) {
-      // gate_up rows: [gate (k) | up (k)]; routed rows first, shared-expert rows after them
-      if (row < a.rows_routed) src = a.in + (int64_t)row * 2 * a.k;
-      else                     src = a.in_shared + (int64_t)(row - a.rows_routed) * 2 * a.k_shared;
-      src_up = src + ri.k;
-    } else {
-      const int64_t tok = row < a.rows_routed ? a.row_token[row] : (int64_t)(row - a.rows_routed);
-      src = a.in + tok * a.k;
+// y = (x .* signs) H_k / sqrt(k), natural (Sylvester) order: the transform of
+// mxmoe/quant/hadamard_utils.py:62-94, result rounded to fp16 values.
+template <int kWarps>
+__device__ __forceinline__ void rotate_row(float (&x)[kJ][8], const int8_t* signs, int nchunk, int k, int w, int lane,
+                                           bool row_ok, float* xch) {
+  // chunks per lane that hold data (a power of two; equals kJ whenever a row spans several warps)
+  const int jeff = max(1, min(kJ, nchunk / (32 * kWarps)));
+  if (signs) {
+#pragma unroll
+    for (int j = 0; j < kJ; ++j) {
+      const int ci = chunk_of<kWarps>(w, j, lane);
+      if (row_ok && ci < nchunk) {
+        const int2 sg = __ldg(reinterpret_cast<const int2*>(signs) + ci);
+        const signed char* sc = reinterpret_cast<const signed char*>(&sg);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[j][e] *= (float)sc[e];
+      }
     }
   }
+  // bits 0..2: inside a chunk
 #pragma unroll
   for (int j = 0; j < kJ; ++j) {
-    const int ci = (w * kJ + j) * 32 + lane;
-    if (row_ok && ci < nchunk) {
-      const uint4 g = __ldg(reinterpret_cast<const uint4*>(src) + ci);
-      const __half2* gh = reinterpret_cast<const __half2*>(&g);
-      if (kSilu) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(src_up) + ci);
-        const __half2* uh = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 gf = __half22float2(gh[e]);
-          // silu evaluated in fp32 and rounded to fp16, product rounded to fp16 (fp16 module semantics)
-          const __half s0 = __float2half_rn(gf.x / (1.f + expf(-gf.x)));
-          const __half s1 = __float2half_rn(gf.y / (1.f + expf(-gf.y)));
-          const __half2 h = __hmul2(__halves2half2(s0, s1), uh[e]);
-          const float2 hf = __half22float2(h);
-          x[j][2 * e] = hf.x;
-          x[j][2 * e + 1] = hf.y;
-        }
-      } else {
+    for (int s = 1; s < 8; s <<= 1) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __half22float2(gh[e]);
-          x[j][2 * e] = f.x;
-          x[j][2 * e + 1] = f.y;
+      for (int e = 0; e < 8; ++e) {
+        if ((e & s) == 0) {
+          const float p = x[j][e], q = x[j][e | s];
+          x[j][e] = p + q;
+          x[j][e | s] = p - q;
         }
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) x[j][e] = 0.f;
     }
   }
-
-  // ------------------------------------------------- optional Hadamard rotation
-  // y = (x .* signs) H_k / sqrt(k), natural (Sylvester) order: the transform of
-  // mxmoe/quant/hadamard_utils.py:62-94.  Element index = chunk * 8 + e with
-  // chunk = (w * 8 + j) * 32 + lane, so the index bits are e | lane | j | w.
-  if (!kSilu && a.rotate) {
-    // chunks per lane that hold data (a power of two; equals kJ whenever a row spans several warps)
-    const int jeff = max(1, min(kJ, nchunk / (32 * kWarps)));
-    if (a.signs) {
+  // bits 3..7: across lanes; upper lane gets (other - mine), lower lane (mine + other): one FMA each
 #pragma unroll
-      for (int j = 0; j < kJ; ++j) {
-        const int ci = (w * kJ + j) * 32 + lane;
-        if (row_ok && ci < nchunk) {
-          const int2 sg = __ldg(reinterpret_cast<const int2*>(a.signs) + ci);
-          const signed char* sc = reinterpret_cast<const signed char*>(&sg);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) x[j][e] *= (float)sc[e];
-        }
-      }
-    }
-    // bits 0..2: inside a chunk
+  for (int o = 1; o < 32; o <<= 1) {
+    const float sgn = (lane & o) ? -1.f : 1.f;
 #pragma unroll
     for (int j = 0; j < kJ; ++j) {
 #pragma unroll
-      for (int s = 1; s < 8; s <<= 1) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if ((e & s) == 0) {
-            const float p = x[j][e], q = x[j][e | s];
-            x[j][e] = p + q;
-            x[j][e | s] = p - q;
-          }
-        }
+      for (int e = 0; e < 8; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[j][e], o);
+        x[j][e] = fmaf(sgn, x[j][e], other);
       }
     }
-    // bits 3..7: across lanes
+  }
+  // next bits: across the chunks of one lane
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const bool upper = (lane & o) != 0;
+  for (int s = 1; s < kJ; s <<= 1) {
+    if (s < jeff) {
 #pragma unroll
       for (int j = 0; j < kJ; ++j) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float other = __shfl_xor_sync(0xffffffffu, x[j][e], o);
-          x[j][e] = upper ? other - x[j][e] : x[j][e] + other;
-        }
-      }
-    }
-    // next bits: across the chunks of one lane
-#pragma unroll
-    for (int s = 1; s < kJ; s <<= 1) {
-      if (s < jeff) {
-#pragma unroll
-        for (int j = 0; j < kJ; ++j) {
-          if ((j & s) == 0) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float p = x[j][e], q = x[j | s][e];
-              x[j][e] = p + q;
-              x[j | s][e] = p - q;
-            }
-          }
-        }
-      }
-    }
-    // top bits: across the warps of the row, through shared memory
-    if (kWarps > 1) {
-#pragma unroll
-      for (int s = 1; s < kWarps; s <<= 1) {
-        const bool upper = (w & s) != 0;
-#pragma unroll
-        for (int j = 0; j < kJ; ++j) {
-          __syncthreads();
-#pragma unroll
-          for (int e = 0; e < 8; ++e) xch[threadIdx.x * 8 + e] = x[j][e];
-          __syncthreads();
-          const int partner = (threadIdx.x ^ (s * 32)) * 8;
+        if ((j & s) == 0) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float other = xch[partner + e];
-            x[j][e] = upper ? other - x[j][e] : x[j][e] + other;
+            const float p = x[j][e], q = x[j | s][e];
+            x[j][e] = p + q;
+            x[j | s][e] = p - q;
           }
         }
       }
     }
-    const float norm = 1.0f / sqrtf((float)ri.k);
-#pragma unroll
-    for (int j = 0; j < kJ; ++j)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) x[j][e] = __half2float(__float2half_rn(x[j][e] * norm));
   }
+  // top bits: across the warps of the row, through shared memory
+  if (kWarps > 1) {
+#pragma unroll
+    for (int s = 1; s < kWarps; s <<= 1) {
+      const float sgn = (w & s) ? -1.f : 1.f;
+#pragma unroll
+      for (int j = 0; j < kJ; ++j) {
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xch[threadIdx.x * 8 + e] = x[j][e];
+        __syncthreads();
+        const int partner = (threadIdx.x ^ (s * 32)) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[j][e] = fmaf(sgn, x[j][e], xch[partner + e]);
+      }
+    }
+  }
+  const float norm = 1.0f / sqrtf((float)k);
+#pragma unroll
+  for (int j = 0; j < kJ; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[j][e] = __half2float(__float2half_rn(x[j][e] * norm));
+}
 
-  // --------------------------------------------------------- per-token abs max
+template <int kWarps>
+__device__ __forceinline__ float row_amax(const float (&x)[kJ][8], int warp, int row_in_blk, int lane, float* red) {
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < kJ; ++j)
@@ -228,13 +179,61 @@ __global__ void __launch_bounds__(kBlock) act_quant_kernel(ActArgs a) {
 #pragma unroll
     for (int i = 0; i < kWarps; ++i) amax = fmaxf(amax, red[row_in_blk * kWarps + i]);
   }
-  if (!row_ok) return;
+  return amax;
+}
 
-  __half* q_dst = a.q_store + ri.q_off;
-  if (ri.tag == 0) {
+// Quantiser of one row held in registers.  scale = fp16(amax / qmax); code = rint(clamp(fp16(x / scale)))
+// (quant.py:77-82 evaluated in fp16, as the reference does for fp16 activations).  The fp32 quotient is
+// formed by Markstein's sequence (q0 = x*r, residual by FMA, one correction with the correctly rounded
+// reciprocal r), which yields the correctly rounded fp32 quotient; rounding that once to fp16 is the
+// correctly rounded fp16 quotient.  An all-zero row gets scale 0 and codes 0.
+struct RowQuant {
+  float qmax, sc, rcp;
+  __half sc_h;
+  __device__ __forceinline__ RowQuant(float amax, int tag) {
+    qmax = tag == 1 ? 127.f : 7.f;
+    sc_h = __float2half_rn(__fdiv_rn(amax, qmax));
+    sc   = __half2float(sc_h);
+    rcp  = sc != 0.f ? __frcp_rn(sc) : 0.f;
+  }
+  __device__ __forceinline__ int code(float v) const {
+    float q = v * rcp;
+    const float r = fmaf(-q, sc, v);
+    q = fmaf(r, rcp, q);
+    q = __half2float(__float2half_rn(q));
+    q = fminf(fmaxf(q, -qmax), qmax);
+    return __float2int_rn(q);
+  }
+};
+
+// pack 8 consecutive codes of a row and store them as chunk `ci` of the packed row
+__device__ __forceinline__ void store_codes(__half* q_dst, int ci, int tag, const int (&code)[8]) {
+  if (tag == 1) {
+    // uint16 word = code[2i] << 8 | code[2i+1]
+    uint2 o;
+    o.x = ((uint32_t)(code[1] & 0xff)) | ((uint32_t)(code[0] & 0xff) << 8) | ((uint32_t)(code[3] & 0xff) << 16) |
+          ((uint32_t)(code[2] & 0xff) << 24);
+    o.y = ((uint32_t)(code[5] & 0xff)) | ((uint32_t)(code[4] & 0xff) << 8) | ((uint32_t)(code[7] & 0xff) << 16) |
+          ((uint32_t)(code[6] & 0xff) << 24);
+    reinterpret_cast<uint2*>(q_dst)[ci] = o;
+  } else {
+    // uint16 word = c0 << 12 | c1 << 8 | c2 << 4 | c3
+    const uint32_t w0 = ((uint32_t)(code[0] & 0xf) << 12) | ((uint32_t)(code[1] & 0xf) << 8) |
+                        ((uint32_t)(code[2] & 0xf) << 4) | (uint32_t)(code[3] & 0xf);
+    const uint32_t w1 = ((uint32_t)(code[4] & 0xf) << 12) | ((uint32_t)(code[5] & 0xf) << 8) |
+                        ((uint32_t)(code[6] & 0xf) << 4) | (uint32_t)(code[7] & 0xf);
+    reinterpret_cast<uint32_t*>(q_dst)[ci] = w0 | (w1 << 16);
+  }
+}
+
+// write one row in format `tag` (0 fp16 copy, 1 int8, 2 int4) to q_dst / s_dst
+template <int kWarps>
+__device__ __forceinline__ void emit_row(const float (&x)[kJ][8], float amax, int tag, __half* q_dst, __half* s_dst,
+                                         int nchunk, int w, int lane) {
+  if (tag == 0) {
 #pragma unroll
     for (int j = 0; j < kJ; ++j) {
-      const int ci = (w * kJ + j) * 32 + lane;
+      const int ci = chunk_of<kWarps>(w, j, lane);
       if (ci < nchunk) {
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -245,67 +244,215 @@ __global__ void __launch_bounds__(kBlock) act_quant_kernel(ActArgs a) {
     }
     return;
   }
-
-  // scale = fp16(amax / qmax); code = rint(clamp(fp16(x / scale), -qmax, qmax))   (quant.py:77-82,
-  // evaluated in fp16 like the reference does for fp16 activations; IEEE fp32 division followed
-  // by one rounding to fp16 is the correctly rounded fp16 quotient)
-  const float qmax   = ri.tag == 1 ? 127.f : 7.f;
-  const __half sc_h  = __float2half_rn(__fdiv_rn(amax, qmax));
-  const float sc     = __half2float(sc_h);
-  if (w == 0 && lane == 0) a.s_store[ri.s_off] = sc_h;
-
+  const RowQuant rq(amax, tag);
+  if (w == 0 && lane == 0) *s_dst = rq.sc_h;
 #pragma unroll
   for (int j = 0; j < kJ; ++j) {
-    const int ci = (w * kJ + j) * 32 + lane;
+    const int ci = chunk_of<kWarps>(w, j, lane);
     if (ci >= nchunk) continue;
     int code[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float v = 0.f;
-      if (sc != 0.f) {
-        v = __half2float(__float2half_rn(__fdiv_rn(x[j][e], sc)));
-        v = fminf(fmaxf(v, -qmax), qmax);
-      }
-      code[e] = __float2int_rn(v);
-    }
-    if (ri.tag == 1) {
-      // uint16 word = code[2i] << 8 | code[2i+1]
-      uint2 o;
-      o.x = ((uint32_t)(code[1] & 0xff)) | ((uint32_t)(code[0] & 0xff) << 8) | ((uint32_t)(code[3] & 0xff) << 16) |
-            ((uint32_t)(code[2] & 0xff) << 24);
-      o.y = ((uint32_t)(code[5] & 0xff)) | ((uint32_t)(code[4] & 0xff) << 8) | ((uint32_t)(code[7] & 0xff) << 16) |
-            ((uint32_t)(code[6] & 0xff) << 24);
-      reinterpret_cast<uint2*>(q_dst)[ci] = o;
-    } else {
-      // uint16 word = c0 << 12 | c1 << 8 | c2 << 4 | c3
-      const uint32_t w0 = ((uint32_t)(code[0] & 0xf) << 12) | ((uint32_t)(code[1] & 0xf) << 8) |
-                          ((uint32_t)(code[2] & 0xf) << 4) | (uint32_t)(code[3] & 0xf);
-      const uint32_t w1 = ((uint32_t)(code[4] & 0xf) << 12) | ((uint32_t)(code[5] & 0xf) << 8) |
-                          ((uint32_t)(code[6] & 0xf) << 4) | (uint32_t)(code[7] & 0xf);
-      reinterpret_cast<uint32_t*>(q_dst)[ci] = w0 | (w1 << 16);
-    }
+    for (int e = 0; e < 8; ++e) code[e] = rq.code(x[j][e]);
+    store_codes(q_dst, ci, tag, code);
   }
 }
 
-template <bool kSilu>
-cudaError_t launch(const ActArgs& a, cudaStream_t stream) {
-  const int kmax = a.k > a.k_shared ? a.k : a.k_shared;
-  if (a.rows_total <= 0) return cudaSuccess;
-  if (kmax <= 2048) {
-    act_quant_kernel<1, kSilu><<<(a.rows_total + 7) / 8, kBlock, 0, stream>>>(a);
-  } else if (kmax <= 4096) {
-    act_quant_kernel<2, kSilu><<<(a.rows_total + 3) / 4, kBlock, 0, stream>>>(a);
-  } else if (kmax <= 8192) {
-    act_quant_kernel<4, kSilu><<<(a.rows_total + 1) / 2, kBlock, 0, stream>>>(a);
-  } else {
-    act_quant_kernel<8, kSilu><<<a.rows_total, kBlock, 0, stream>>>(a);
+// ---------------------------------------------------------------------------------------------
+// fused gather + (rotate) + quantise, one pass per routed row (operator-API path, any top-k)
+template <int kWarps>
+__global__ void __launch_bounds__(kBlock) quant_act_kernel(ActArgs a) {
+  __shared__ float xch[kWarps > 1 ? kBlock * 8 : 1];
+  __shared__ float red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_in_blk = warp / kWarps, w = warp % kWarps;
+  const int row     = blockIdx.x * (8 / kWarps) + row_in_blk;
+  const bool row_ok = row < a.rows_total;
+
+  RowInfo ri{0, 0, 0, 0};
+  if (row_ok) ri = locate_row(a, row);
+  const int nchunk = ri.k >> 3;
+  const __half* src = nullptr;
+  if (row_ok) {
+    const int64_t tok = row < a.rows_routed ? a.row_token[row] : (int64_t)(row - a.rows_routed);
+    src = a.in + tok * a.k;
   }
-  return cudaGetLastError();
+  float x[kJ][8];
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci = chunk_of<kWarps>(w, j, lane);
+    if (row_ok && ci < nchunk) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(src) + ci), x[j]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[j][e] = 0.f;
+    }
+  }
+  if (a.rotate) rotate_row<kWarps>(x, a.signs, nchunk, ri.k, w, lane, row_ok, xch);
+  const float amax = row_amax<kWarps>(x, warp, row_in_blk, lane, red);
+  if (!row_ok) return;
+  emit_row<kWarps>(x, amax, ri.tag, a.q_store + ri.q_off, a.s_store ? a.s_store + ri.s_off : nullptr, nchunk, w, lane);
 }
+
+// ---------------------------------------------------------------------------------------------
+// (rotate) + quantise once per token into token-major stores, one per activation format in use
+template <int kWarps>
+__global__ void __launch_bounds__(kBlock) quant_tokens_kernel(TokenQuantArgs a) {
+  __shared__ float xch[kWarps > 1 ? kBlock * 8 : 1];
+  __shared__ float red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_in_blk = warp / kWarps, w = warp % kWarps;
+  const int tok     = blockIdx.x * (8 / kWarps) + row_in_blk;
+  const bool row_ok = tok < a.num_tokens;
+  const int nchunk  = a.k >> 3;
+  float x[kJ][8];
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci = chunk_of<kWarps>(w, j, lane);
+    if (row_ok && ci < nchunk) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(a.in + (int64_t)tok * a.k) + ci), x[j]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[j][e] = 0.f;
+    }
+  }
+  if (a.rotate) rotate_row<kWarps>(x, a.signs, nchunk, a.k, w, lane, row_ok, xch);
+  const float amax = row_amax<kWarps>(x, warp, row_in_blk, lane, red);
+  if (!row_ok) return;
+  if (a.f16) emit_row<kWarps>(x, amax, 0, a.f16 + (int64_t)tok * a.k, nullptr, nchunk, w, lane);
+  if (a.q8) emit_row<kWarps>(x, amax, 1, a.q8 + (int64_t)tok * (a.k / 2), a.s8 + tok, nchunk, w, lane);
+  if (a.q4) emit_row<kWarps>(x, amax, 2, a.q4 + (int64_t)tok * (a.k / 4), a.s4 + tok, nchunk, w, lane);
+}
+
+// copy every routed (and shared-expert) row from the token-major store of its expert's format into
+// the expert-sorted activation store; one warp per row, 16-byte chunks
+__global__ void __launch_bounds__(kBlock) gather_rows_kernel(ActArgs a, TokenQuantArgs t) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= a.rows_total) return;
+  const RowInfo ri  = locate_row(a, row);
+  const int64_t tok = row < a.rows_routed ? a.row_token[row] : (int64_t)(row - a.rows_routed);
+  const int pack    = ri.tag == 0 ? 1 : (ri.tag == 1 ? 2 : 4);
+  const __half* src = ri.tag == 0 ? (t.f16 ? t.f16 : t.in) : (ri.tag == 1 ? t.q8 : t.q4);
+  const uint4* s = reinterpret_cast<const uint4*>(src + tok * (a.k / pack));
+  uint4* d       = reinterpret_cast<uint4*>(a.q_store + ri.q_off);
+  const int n16  = (a.k / pack) >> 3;
+  for (int c = lane; c < n16; c += 32) d[c] = __ldg(s + c);
+  if (ri.tag != 0 && lane == 0) a.s_store[ri.s_off] = (ri.tag == 1 ? t.s8 : t.s4)[tok];
+}
+
+// ---------------------------------------------------------------------------------------------
+// h = silu(gate) * up, then quantise; one pass per routed row.  Values are fp16 after the product,
+// so they are kept as half2 (32 registers per thread for 64 values).
+template <int kWarps>
+__global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
+  __shared__ float red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_in_blk = warp / kWarps, w = warp % kWarps;
+  const int row     = blockIdx.x * (8 / kWarps) + row_in_blk;
+  const bool row_ok = row < a.rows_total;
+  RowInfo ri{0, 0, 0, 0};
+  if (row_ok) ri = locate_row(a, row);
+  const int nchunk = ri.k >> 3;
+  const __half* src = nullptr;
+  if (row_ok) {
+    // gate_up rows: [gate (k) | up (k)]; routed rows first, shared-expert rows in their own buffer
+    if (row < a.rows_routed) src = a.in + (int64_t)row * 2 * a.k;
+    else                     src = a.in_shared + (int64_t)(row - a.rows_routed) * 2 * a.k_shared;
+  }
+  __half2 h[kJ][4];
+  __half2 m2 = __float2half2_rn(0.f);
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci = chunk_of<kWarps>(w, j, lane);
+    if (row_ok && ci < nchunk) {
+      const uint4 g = __ldg(reinterpret_cast<const uint4*>(src) + ci);
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + ri.k) + ci);
+      const __half2* gh = reinterpret_cast<const __half2*>(&g);
+      const __half2* uh = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 gf = __half22float2(gh[e]);
+        // silu in fp32, rounded to fp16; product rounded to fp16 (fp16 module semantics)
+        const float s0 = __fdividef(gf.x, 1.f + __expf(-gf.x));
+        const float s1 = __fdividef(gf.y, 1.f + __expf(-gf.y));
+        h[j][e] = __hmul2(__floats2half2_rn(s0, s1), uh[e]);
+        m2 = __hmax2(m2, __habs2(h[j][e]));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[j][e] = __float2half2_rn(0.f);
+    }
+  }
+  float amax = warp_max(fmaxf(__low2float(m2), __high2float(m2)));
+  if (kWarps > 1) {
+    __syncthreads();
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) amax = fmaxf(amax, red[row_in_blk * kWarps + i]);
+  }
+  if (!row_ok) return;
+  __half* q_dst = a.q_store + ri.q_off;
+  if (ri.tag == 0) {
+#pragma unroll
+    for (int j = 0; j < kJ; ++j) {
+      const int ci = chunk_of<kWarps>(w, j, lane);
+      if (ci < nchunk) reinterpret_cast<uint4*>(q_dst)[ci] = *reinterpret_cast<const uint4*>(h[j]);
+    }
+    return;
+  }
+  const RowQuant rq(amax, ri.tag);
+  if (w == 0 && lane == 0) a.s_store[ri.s_off] = rq.sc_h;
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci = chunk_of<kWarps>(w, j, lane);
+    if (ci >= nchunk) continue;
+    int code[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __half22float2(h[j][e]);
+      code[2 * e]     = rq.code(f.x);
+      code[2 * e + 1] = rq.code(f.y);
+    }
+    store_codes(q_dst, ci, ri.tag, code);
+  }
+}
+
+#define MXB_DISPATCH_WARPS(kmax, rows, KERNEL, ...)                                                   \
+  do {                                                                                                \
+    if ((kmax) <= 2048)      KERNEL<1><<<((rows) + 7) / 8, kBlock, 0, stream>>>(__VA_ARGS__);          \
+    else if ((kmax) <= 4096) KERNEL<2><<<((rows) + 3) / 4, kBlock, 0, stream>>>(__VA_ARGS__);          \
+    else if ((kmax) <= 8192) KERNEL<4><<<((rows) + 1) / 2, kBlock, 0, stream>>>(__VA_ARGS__);          \
+    else                     KERNEL<8><<<(rows), kBlock, 0, stream>>>(__VA_ARGS__);                    \
+  } while (0)
 
 }  // namespace
 
-cudaError_t launch_quant_act(const ActArgs& a, cudaStream_t stream) { return launch<false>(a, stream); }
-cudaError_t launch_silu_mul_quant(const ActArgs& a, cudaStream_t stream) { return launch<true>(a, stream); }
+cudaError_t launch_quant_act(const ActArgs& a, cudaStream_t stream) {
+  if (a.rows_total <= 0) return cudaSuccess;
+  const int kmax = a.k > a.k_shared ? a.k : a.k_shared;
+  MXB_DISPATCH_WARPS(kmax, a.rows_total, quant_act_kernel, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul_quant(const ActArgs& a, cudaStream_t stream) {
+  if (a.rows_total <= 0) return cudaSuccess;
+  const int kmax = a.k > a.k_shared ? a.k : a.k_shared;
+  MXB_DISPATCH_WARPS(kmax, a.rows_total, silu_mul_quant_kernel, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quant_tokens(const TokenQuantArgs& t, cudaStream_t stream) {
+  if (t.num_tokens <= 0) return cudaSuccess;
+  MXB_DISPATCH_WARPS(t.k, t.num_tokens, quant_tokens_kernel, t);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const ActArgs& a, const TokenQuantArgs& t, cudaStream_t stream) {
+  if (a.rows_total <= 0) return cudaSuccess;
+  gather_rows_kernel<<<(a.rows_total + 7) / 8, kBlock, 0, stream>>>(a, t);
+  return cudaGetLastError();
+}
 
 }  // namespace mxb

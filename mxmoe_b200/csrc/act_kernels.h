@@ -31,6 +31,24 @@ struct ActArgs {
   int rotate;                // 1: apply y = (x .* signs) H / sqrt(k) before quantising
 };
 
+// Per-token quantisation into token-major stores; a store pointer that is null is not produced.
+struct TokenQuantArgs {
+  const __half* in;     // hidden [T, k]
+  __half* f16;          // rotated fp16 rows [T, k]            (needed only when rotating)
+  __half* q8;           // int8 rows  [T, k/2] uint16 words
+  __half* s8;           // [T]
+  __half* q4;           // int4 rows  [T, k/4] uint16 words
+  __half* s4;           // [T]
+  const int8_t* signs;  // optional +-1 diagonal, length k
+  int k;
+  int num_tokens;
+  int rotate;
+  int reserved;
+};
+
+cudaError_t launch_quant_tokens(const TokenQuantArgs& t, cudaStream_t stream);
+// rows of `a` (tables as for quant_act; a.in unused) are copied from the stores of `t`
+cudaError_t launch_gather_rows(const ActArgs& a, const TokenQuantArgs& t, cudaStream_t stream);
 cudaError_t launch_quant_act(const ActArgs& a, cudaStream_t stream);
 cudaError_t launch_silu_mul_quant(const ActArgs& a, cudaStream_t stream);
 

@@ -353,6 +353,51 @@ int mxmoe_quant_act(const mxmoe_act_args* args, void* stream) {
   return MXMOE_OK;
 }
 
+static int to_token_args(const mxmoe_token_quant_args* t, mxb::TokenQuantArgs* o) {
+  if (!t) return fail(MXMOE_ERR_INVALID, "null args");
+  if (!t->in) return fail(MXMOE_ERR_INVALID, "null input");
+  if (t->k <= 0 || t->k % 8 || t->k > 16384) return fail(MXMOE_ERR_INVALID, "row length must be a multiple of 8 in (0, 16384] (k=%d)", t->k);
+  if (t->num_tokens < 0) return fail(MXMOE_ERR_INVALID, "negative token count");
+  if ((t->q8 && !t->s8) || (t->q4 && !t->s4)) return fail(MXMOE_ERR_INVALID, "a packed store needs its scale store");
+  if (t->rotate && ((t->k & (t->k - 1)) != 0 || t->k < 256)) return fail(MXMOE_ERR_UNSUPPORTED, "rotation needs a power-of-two row length >= 256 (k=%d)", t->k);
+  o->in = static_cast<const __half*>(t->in);
+  o->f16 = static_cast<__half*>(t->f16);
+  o->q8 = static_cast<__half*>(t->q8);
+  o->s8 = static_cast<__half*>(t->s8);
+  o->q4 = static_cast<__half*>(t->q4);
+  o->s4 = static_cast<__half*>(t->s4);
+  o->signs = t->signs;
+  o->k = t->k;
+  o->num_tokens = t->num_tokens;
+  o->rotate = t->rotate;
+  o->reserved = 0;
+  return MXMOE_OK;
+}
+
+int mxmoe_quant_tokens(const mxmoe_token_quant_args* args, void* stream) {
+  mxb::TokenQuantArgs t;
+  int rc = to_token_args(args, &t);
+  if (rc) return rc;
+  CUDA_TRY(mxb::launch_quant_tokens(t, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+int mxmoe_gather_rows(const mxmoe_act_args* rows, const mxmoe_token_quant_args* stores, void* stream) {
+  mxb::TokenQuantArgs t;
+  int rc = to_token_args(stores, &t);
+  if (rc) return rc;
+  if (!rows) return fail(MXMOE_ERR_INVALID, "null args");
+  mxmoe_act_args r = *rows;
+  r.in = stores->in;
+  r.rotate = 0;
+  if (r.rows_total > r.rows_routed) r.k_shared = r.k;
+  mxb::ActArgs a;
+  rc = to_act_args(&r, &a, false);
+  if (rc) return rc;
+  CUDA_TRY(mxb::launch_gather_rows(a, t, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
 int mxmoe_silu_mul_then_quant(const mxmoe_act_args* args, void* stream) {
   mxb::ActArgs a;
   int rc = to_act_args(args, &a, true);

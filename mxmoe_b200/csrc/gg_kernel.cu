@@ -57,6 +57,7 @@ struct Ctrl {
   int m_eff[kMaxProblems];      // rows of each problem
   int row0[kMaxProblems];       // row shift of each problem
   int meta[kMaxProblems];       // n_tiles << 16 | nkb << 4 | scheme   (nkb < 4096)
+  __half sb_stage[4][kBN];      // per epilogue warp: per-channel scales of the current tile
 };
 
 template <bool kCvt>
@@ -302,6 +303,26 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile ti          = find_tile(ctrl, count, t);
       const GGProblemDev* pr = problems + ti.p;
+      // everything that does not depend on the accumulator is fetched before waiting for it
+      const int M        = ctrl->m_eff[ti.p];
+      const int N        = pr->N;
+      const int row      = ti.m_tile * kBM + q * 32 + lane;   // row inside the problem
+      const bool valid   = row < M;
+      const int64_t grow = (int64_t)ctrl->row0[ti.p] + row;   // row inside the buffers
+      const bool is_int  = (ti.scheme == SCH_W8A8 || ti.scheme == SCH_W4A4);
+      const int out_mode = pr->out_mode;
+      const int ldc      = pr->ldc;
+      __half* sbw        = ctrl->sb_stage[warp - 2];
+      __half sa          = __float2half(0.f);
+      if (is_int && out_mode == OUT_FP16) {
+        const int n = ti.n_tile * kBN + lane * 8;
+        uint4 sv    = make_uint4(0, 0, 0, 0);
+        if (n < N) sv = __ldg(reinterpret_cast<const uint4*>(pr->scale_b + n));
+        if (valid) sa = pr->scale_a[grow];
+        __syncwarp();
+        *reinterpret_cast<uint4*>(sbw + lane * 8) = sv;
+        __syncwarp();
+      }
       bool ok = wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag);
       ok      = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -312,17 +333,6 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
         break;
       }
       tc_fence_after_sync();
-      const int M        = ctrl->m_eff[ti.p];
-      const int N        = pr->N;
-      const int row      = ti.m_tile * kBM + q * 32 + lane;   // row inside the problem
-      const bool valid   = row < M;
-      const int64_t grow = (int64_t)ctrl->row0[ti.p] + row;   // row inside the buffers
-      const bool is_int  = (ti.scheme == SCH_W8A8 || ti.scheme == SCH_W4A4);
-      const int out_mode = pr->out_mode;
-      const int ldc      = pr->ldc;
-      const __half* sb   = pr->scale_b;
-      __half sa          = __float2half(0.f);
-      if (valid && is_int && out_mode == OUT_FP16) sa = pr->scale_a[grow];
       const int acc_shift = (ti.scheme == SCH_W4A4) ? 8 : 0;  // 4-bit codes ride in the high nibble of each byte
 #pragma unroll 1
       for (int c = 0; c < kBN / 32; ++c) {
@@ -356,7 +366,7 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
               uint32_t o[4];
               if (is_int) {
                 // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
-                const uint4 sbv   = __ldg(reinterpret_cast<const uint4*>(sb + n0 + j * 8));
+                const uint4 sbv   = *reinterpret_cast<const uint4*>(sbw + c * 32 + j * 8);
                 const __half2* s2 = reinterpret_cast<const __half2*>(&sbv);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {

@@ -56,6 +56,7 @@ class MoELayer:
         self.has_shared = (shared_inter > 0 and num_experts in gate_up) if with_shared is None else with_shared
         self.rows_cap = max_tokens * topk if max_rows is None else max_rows   # routed rows this instance can hold
         self.rotate = rotate
+        self.per_token_quant = True    # quantise once per token, then gather (False: fused per-row kernel)
         self.gate_up, self.down = gate_up, down
         dev = self.device
         i32 = dict(dtype=torch.int32, device=dev)
@@ -93,6 +94,14 @@ class MoELayer:
         self.o2 = torch.zeros(R * H, **f16)                     # down out, routed rows [R, H]
         self.o2s = torch.zeros(Ts * H, **f16) if Ts else None
         self.out = torch.zeros(T * H, **f16)
+
+        # token-major stores of the once-per-token quantiser (one per activation format in use)
+        used = {self._tag1[e] for e in gate_up}
+        self.tq_f16 = torch.zeros(T * H, **f16) if (0 in used and rotate) else None
+        self.tq_q8 = torch.zeros(T * H // 2, **f16) if 1 in used else None
+        self.tq_s8 = torch.zeros(T, **f16) if 1 in used else None
+        self.tq_q4 = torch.zeros(T * H // 4, **f16) if 2 in used else None
+        self.tq_s4 = torch.zeros(T, **f16) if 2 in used else None
 
         self.gg1 = GroupedGemm(self._problems(gate_up, self._tag1, self.q1, self.s1, self.o1, self.o1s,
                                                K=H, N=2 * I, Ks=H, Ns=2 * Is), device=dev)
@@ -152,11 +161,26 @@ class MoELayer:
         # when a shared expert is present (rows between `rows` and R are simply not produced).
         if self.has_shared:
             assert rows == R, "with a shared expert the routed row count must equal the capacity"
-        self._act(lib.mxmoe_quant_act, inp=hidden, in_shared=None, q_store=self.q1, s_store=self.s1,
-                  row_expert=self.row_expert, row_token=self.row_token, exp_qtag=self.tag1,
-                  exp_row_start=self.row_start, exp_q_off=None, exp_s_off=None, signs=self.signs,
-                  k=self.H, k_shared=self.H, rows_routed=rows, rows_total=rows + T, num_experts=self.E,
-                  rotate=1 if self.rotate else 0)
+        if self.per_token_quant:
+            t = _lib.TokenQuantArgs()
+            t.inp, t.k, t.num_tokens, t.rotate = hidden.data_ptr(), self.H, hidden.shape[0], 1 if self.rotate else 0
+            t.signs = None if self.signs is None else self.signs.data_ptr()
+            for name in ("f16", "q8", "s8", "q4", "s4"):
+                buf = getattr(self, "tq_" + name)
+                setattr(t, name, None if buf is None else buf.data_ptr())
+            _lib.check(lib.mxmoe_quant_tokens(C.byref(t), current_stream_ptr()))
+            a = _lib.ActArgs()
+            a.q_store, a.s_store = self.q1.data_ptr(), self.s1.data_ptr()
+            a.row_expert, a.row_token = self.row_expert.data_ptr(), self.row_token.data_ptr()
+            a.exp_qtag, a.exp_row_start = self.tag1.data_ptr(), self.row_start.data_ptr()
+            a.k, a.k_shared, a.rows_routed, a.rows_total, a.num_experts = self.H, self.H, rows, rows + T, self.E
+            _lib.check(lib.mxmoe_gather_rows(C.byref(a), C.byref(t), current_stream_ptr()))
+        else:
+            self._act(lib.mxmoe_quant_act, inp=hidden, in_shared=None, q_store=self.q1, s_store=self.s1,
+                      row_expert=self.row_expert, row_token=self.row_token, exp_qtag=self.tag1,
+                      exp_row_start=self.row_start, exp_q_off=None, exp_s_off=None, signs=self.signs,
+                      k=self.H, k_shared=self.H, rows_routed=rows, rows_total=rows + T, num_experts=self.E,
+                      rotate=1 if self.rotate else 0)
         self.gg1.run()
         self._act(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=self.o1s, q_store=self.q2, s_store=self.s2,
                   row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=self.row_start,

@@ -186,14 +186,16 @@ def _launch_act(fn, dev, **kw) -> None:
 
 def quant_inp_act(hidden: torch.Tensor, topk_ids: torch.Tensor, num_experts: int, N: int, num_shared_experts: int,
                   qparams_per_exp: Sequence[QParamsTuple], verbose: bool = False, *,
-                  rotate: bool = False, signs: torch.Tensor | None = None):
+                  rotate: bool = False, signs: torch.Tensor | None = None, fused: bool = False):
     """Permute tokens by expert and quantise + pack each row with its expert's activation scheme.
 
     Mirrors ``quant_inp_act`` (ref_bind.cu:434-592) including the nine-element return tuple
     ``(inp_list, inp_scale_list, out_list, inp_store, inp_scale_store, out_store,
     recv_tokens_per_exp[CPU int64], perm_indices, dst_exp_sorted)``.  ``rotate`` / ``signs``
     (keyword-only, not in the reference) apply the Hadamard rotation of the hidden
-    dimension before quantising.
+    dimension before quantising.  By default rows are quantised once per token and then
+    copied to their experts; ``fused=True`` runs the single gather+quantise kernel instead
+    (same bits).
     """
     _check(hidden.dim() == 2 and hidden.is_cuda, "hidden must be a 2D cuda tensor")
     _check(hidden.dtype == torch.float16, "hidden must be fp16")
@@ -221,12 +223,39 @@ def quant_inp_act(hidden: torch.Tensor, topk_ids: torch.Tensor, num_experts: int
     if signs is not None:
         signs = signs.to(device=dev, dtype=torch.int8).contiguous()
 
-    _launch_act(_lib.lib().mxmoe_quant_act, dev,
-                inp=hidden, in_shared=None, q_store=inp_store, s_store=inp_scale_store if s_total else None,
-                row_expert=dst_exp_sorted, row_token=perm_indices,
-                exp_qtag=tables[0], exp_row_start=tables[1], exp_q_off=tables[2], exp_s_off=tables[3],
-                signs=signs, k=K, k_shared=K, rows_routed=num_tokens * topk, rows_total=alloc_tokens,
-                num_experts=num_experts, rotate=1 if rotate else 0)
+    common = dict(q_store=inp_store, s_store=inp_scale_store if s_total else None,
+                  row_expert=dst_exp_sorted, row_token=perm_indices,
+                  exp_qtag=tables[0], exp_row_start=tables[1], exp_q_off=tables[2], exp_s_off=tables[3],
+                  k=K, k_shared=K, rows_routed=num_tokens * topk, rows_total=alloc_tokens, num_experts=num_experts)
+    if fused:
+        _launch_act(_lib.lib().mxmoe_quant_act, dev, inp=hidden, in_shared=None, signs=signs,
+                    rotate=1 if rotate else 0, **common)
+    else:
+        used = {tag[e] for e in range(n_all) if (num_tokens if e == num_experts else tokens[e]) > 0}
+        t = _lib.TokenQuantArgs()
+        keep = []
+
+        def store(n):
+            buf = torch.empty(n, dtype=torch.float16, device=dev)
+            keep.append(buf)
+            return buf.data_ptr()
+        t.inp, t.k, t.num_tokens, t.rotate = hidden.data_ptr(), K, num_tokens, 1 if rotate else 0
+        t.signs = None if signs is None else signs.data_ptr()
+        if 0 in used and rotate:
+            t.f16 = store(num_tokens * K)
+        if 1 in used:
+            t.q8, t.s8 = store(num_tokens * K // 2), store(num_tokens)
+        if 2 in used:
+            t.q4, t.s4 = store(num_tokens * K // 4), store(num_tokens)
+        a = _lib.ActArgs()
+        for k_, v in common.items():
+            setattr(a, k_, v.data_ptr() if isinstance(v, torch.Tensor) else v)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mxmoe_quant_tokens(C.byref(t), current_stream_ptr()))
+            _lib.check(_lib.lib().mxmoe_gather_rows(C.byref(a), C.byref(t), current_stream_ptr()))
+        # the token-major stores may be recycled by the allocator once the stream has consumed them
+        for buf in keep:
+            buf.record_stream(torch.cuda.current_stream())
 
     inp_list, inp_scale_list, out_list = [], [], []
     qout_off = 0

@@ -25,8 +25,9 @@ def _unpack_rows(words, tag, k):
     return w.view(np.float16)
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("k", [256, 1408, 2048, 4096, 5632, 14336])
-def test_quant_inp_act_matches_quantiser(cuda_device, k):
+def test_quant_inp_act_matches_quantiser(cuda_device, k, fused):
     """Codes and scales are bit-identical to the fp16 min/max quantiser (quant.py:40-84) for every tag."""
     rng = np.random.default_rng(k)
     t, e, topk = 37, 6, 2
@@ -35,7 +36,7 @@ def test_quant_inp_act_matches_quantiser(cuda_device, k):
     ids = _routing(rng, t, e, topk)
     qp = [(4, 4, -1, True), (8, 8, -1, True), (16, 16, -1, True), (16, 4, 128, False), (4, 4, -1, True),
           (8, 8, -1, True), (4, 4, -1, True)]          # last entry: shared expert
-    out = ops.quant_inp_act(hidden.to(cuda_device), ids.to(cuda_device), e, 64, 1, qp)
+    out = ops.quant_inp_act(hidden.to(cuda_device), ids.to(cuda_device), e, 64, 1, qp, fused=fused)
     inp_list, scale_list, out_list, _, _, _, recv, perm, dst = out
     assert recv.device.type == "cpu" and recv.dtype == torch.int64
     srt, order = torch.sort(ids.reshape(-1), stable=True)
@@ -68,8 +69,9 @@ def test_quant_inp_act_matches_quantiser(cuda_device, k):
     assert pidx == len(inp_list)
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("k", [256, 2048, 4096])
-def test_quant_inp_act_with_rotation(cuda_device, k):
+def test_quant_inp_act_with_rotation(cuda_device, k, fused):
     """Rotated rows match matmul_hadU on (x * signs) to rel-L2 1e-3 after dequantisation of 8-bit codes;
     4-bit codes differ from the oracle's in at most 1 % of positions and never by more than one step."""
     rng = np.random.default_rng(k + 1)
@@ -79,7 +81,7 @@ def test_quant_inp_act_with_rotation(cuda_device, k):
     ids = _routing(rng, t, e, topk)
     qp = [(16, 16, -1, True), (8, 8, -1, True), (4, 4, -1, True), (4, 4, -1, True)]
     out = ops.quant_inp_act(hidden.to(cuda_device), ids.to(cuda_device), e, 64, 0, qp, rotate=True,
-                            signs=signs.to(cuda_device))
+                            signs=signs.to(cuda_device), fused=fused)
     inp_list, scale_list, _, _, _, _, recv, perm, _ = out
     rot = oh.hadamard_rows(hidden.double() * signs.double())
     pidx, row = 0, 0
