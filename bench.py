@@ -241,7 +241,8 @@ def main():
     # ---- per-launch timing of the dominant kernel (grouped GEMM), events on the launching stream
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     if world == 1:
-        gg1_run, gg2_run = layer.gg1.run, layer.gg2.run
+        core = layer._core
+        gg1_run, gg2_run = core.gg1.run, core.gg2.run
         state = {"i": 0}
 
         def timed_gg1():
@@ -251,7 +252,7 @@ def main():
         def timed_gg2():
             e = ev[state["i"]]
             e[2].record(); gg2_run(); e[3].record()
-        layer.gg1.run, layer.gg2.run = timed_gg1, timed_gg2
+        core.gg1.run, core.gg2.run = timed_gg1, timed_gg2
 
     sampler = ClockSampler(local)
     barrier()
@@ -268,7 +269,7 @@ def main():
     ms_total = t0.elapsed_time(t1)
     layer.check()
     if world == 1:
-        layer.gg1.run, layer.gg2.run = gg1_run, gg2_run
+        core.gg1.run, core.gg2.run = gg1_run, gg2_run
 
     # ---- end-to-end through the public API with host buffers (H2D of inputs + D2H of the result inside)
     barrier()
@@ -313,7 +314,7 @@ def main():
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hidden_host.numel() * 2 + ids_host.numel() * 4 + wts_host.numel() * 4,
                 "d2h_bytes_per_step": out_host.numel() * 2, "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
-        "gpu_launches": args.steps * (8 if world == 1 else layer.launches_per_step),
+        "gpu_launches": args.steps * (layer.launches_per_step + (1 if spec.shared_inter else 0)),
     }
 
     if world == 1:

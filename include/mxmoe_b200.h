@@ -54,9 +54,9 @@ typedef struct mxmoe_qparams {
  * TMA unit may touch.  If `m_dev` is set, the live row count is read on the
  * device from *m_dev (clamped to M); if `row0_dev` is set, row0 is read from
  * *row0_dev.  Both let a launch follow a routing result that never visits the host.
- * `a_row_mul` scales the row shift of A only: an activation store that reserves
- * one fp16-sized slot per row holds a_row_mul packed rows per slot, so expert
- * rows that start at slot r start at packed row r * a_row_mul. */
+ * `lda_bytes` / `sa_stride` describe activation stores made of fixed-size records (one per row,
+ * possibly wider than the packed row, possibly carrying the row's scale): rows of different
+ * formats then share one buffer and one row numbering. */
 typedef struct mxmoe_gg_problem {
   const void* A;
   const void* B;
@@ -71,7 +71,9 @@ typedef struct mxmoe_gg_problem {
   int32_t ldc;
   mxmoe_qparams q;
   int32_t out_mode;
-  int32_t a_row_mul; /* 0 or 1: none; p > 1: rows of A start at row0 * p (A store whose row slots hold p packed rows) */
+  int32_t lda_bytes; /* row pitch of A in bytes; 0 = dense rows.  A multiple of 16. */
+  int32_t sa_stride; /* distance between consecutive per-token scales in fp16 elements; 0 or 1 = contiguous */
+  int32_t reserved_;
 } mxmoe_gg_problem;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -132,10 +134,10 @@ int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, v
  * the reference builds on the host at mxmoe/kernels/src/ref_bind.cu:475-505:
  * quantisation tag (0 fp16 copy, 1 int8 per token, 2 int4 per token), first row,
  * write offset of the packed rows and of the scales (both in fp16 elements).
- * exp_q_off / exp_s_off may be NULL: then every row owns one slot of k fp16
- * elements in q_store, expert e's packed rows start at slot exp_row_start[e] and
- * follow each other at their own packed pitch, and its scales start at
- * s_store[exp_row_start[e]] - offsets that need no host knowledge of the counts. */
+ * Record layout (rec_stride > 0): the three offset tables are not read; row r is written to
+ * q_store + r * rec_stride whatever its format, and its scale to the same record at
+ * rec_scale_off (or to s_store[r] if rec_scale_off < 0) - offsets that need no host knowledge
+ * of the per-expert counts, and buffers that can be sent to another GPU as they are. */
 typedef struct mxmoe_act_args {
   const void* in;             /* fp16 */
   const void* in_shared;      /* fp16, silu_mul_then_quant only */
@@ -154,6 +156,8 @@ typedef struct mxmoe_act_args {
   int32_t rows_total;
   int32_t num_experts;
   int32_t rotate;             /* quant_inp_act only: rotate rows by diag(signs) H_k / sqrt(k) first */
+  int32_t rec_stride;         /* > 0: record layout (see below), in fp16 elements */
+  int32_t rec_scale_off;      /* record layout: offset of the scale inside the record, or < 0 for s_store[row] */
 } mxmoe_act_args;
 
 /* Gather rows of `in` ([T,k] fp16) by expert, optionally rotate, quantise per

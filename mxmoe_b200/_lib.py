@@ -40,7 +40,8 @@ class GGProblem(C.Structure):
         ("m_dev", C.c_void_p), ("row0_dev", C.c_void_p),
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
         ("a_rows", C.c_int32), ("row0", C.c_int32), ("ldc", C.c_int32),
-        ("q", QParams), ("out_mode", C.c_int32), ("a_row_mul", C.c_int32),
+        ("q", QParams), ("out_mode", C.c_int32), ("lda_bytes", C.c_int32), ("sa_stride", C.c_int32),
+        ("reserved_", C.c_int32),
     ]
 
 
@@ -55,7 +56,7 @@ class ActArgs(C.Structure):
         ("exp_qtag", C.c_void_p), ("exp_row_start", C.c_void_p), ("exp_q_off", C.c_void_p), ("exp_s_off", C.c_void_p),
         ("signs", C.c_void_p),
         ("k", C.c_int32), ("k_shared", C.c_int32), ("rows_routed", C.c_int32), ("rows_total", C.c_int32),
-        ("num_experts", C.c_int32), ("rotate", C.c_int32),
+        ("num_experts", C.c_int32), ("rotate", C.c_int32), ("rec_stride", C.c_int32), ("rec_scale_off", C.c_int32),
     ]
 
 

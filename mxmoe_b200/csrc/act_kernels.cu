@@ -35,23 +35,29 @@ constexpr int kJ     = 8;    // 16-byte chunks per lane (8 values each)
 struct RowInfo {
   int tag;          // 0 copy fp16, 1 int8 per token, 2 int4 per token
   int k;            // logical row length
-  int64_t q_off;    // write offset of the packed row, in halfs
-  int64_t s_off;    // write offset of the scale, in halfs
+  __half* q_dst;    // where the packed row goes
+  __half* s_dst;    // where the scale goes (may be null for tag 0)
 };
 
 __device__ __forceinline__ RowInfo locate_row(const ActArgs& a, int row) {
-  const int e     = row < a.rows_routed ? a.row_expert[row] : a.num_experts;
-  const int local = row - a.exp_row_start[e];
+  const int e = row < a.rows_routed ? a.row_expert[row] : a.num_experts;
   RowInfo r;
-  r.tag  = a.exp_qtag[e];
-  r.k    = (e == a.num_experts) ? a.k_shared : a.k;
-  const int pack = r.tag == 0 ? 1 : (r.tag == 1 ? 2 : 4);
+  r.tag = a.exp_qtag[e];
+  r.k   = (e == a.num_experts) ? a.k_shared : a.k;
+  if (a.rec_stride > 0) {
+    // record layout: one fixed-size record per row, whatever its format
+    r.q_dst = a.q_store + (int64_t)row * a.rec_stride;
+    r.s_dst = a.rec_scale_off >= 0 ? r.q_dst + a.rec_scale_off : (a.s_store ? a.s_store + row : nullptr);
+    return r;
+  }
+  const int local = row - a.exp_row_start[e];
+  const int pack  = r.tag == 0 ? 1 : (r.tag == 1 ? 2 : 4);
   // without explicit offset tables every row owns one fp16-sized slot of `k` halfs: expert e's
   // packed rows start at slot exp_row_start[e] and are stored back to back at their own pitch
   const int64_t q0 = a.exp_q_off ? (int64_t)a.exp_q_off[e] : (int64_t)a.exp_row_start[e] * a.k;
   const int64_t s0 = a.exp_s_off ? (int64_t)a.exp_s_off[e] : (int64_t)a.exp_row_start[e];
-  r.q_off = q0 + (int64_t)local * (r.k / pack);
-  r.s_off = s0 + local;
+  r.q_dst = a.q_store + q0 + (int64_t)local * (r.k / pack);
+  r.s_dst = a.s_store ? a.s_store + s0 + local : nullptr;
   return r;
 }
 
@@ -268,7 +274,7 @@ __global__ void __launch_bounds__(kBlock) quant_act_kernel(ActArgs a) {
   const int row     = blockIdx.x * (8 / kWarps) + row_in_blk;
   const bool row_ok = row < a.rows_total;
 
-  RowInfo ri{0, 0, 0, 0};
+  RowInfo ri{0, 0, nullptr, nullptr};
   if (row_ok) ri = locate_row(a, row);
   const int nchunk = ri.k >> 3;
   const __half* src = nullptr;
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__(kBlock) quant_act_kernel(ActArgs a) {
   if (a.rotate) rotate_row<kWarps>(x, a.signs, nchunk, ri.k, w, lane, row_ok, xch);
   const float amax = row_amax<kWarps>(x, warp, row_in_blk, lane, red);
   if (!row_ok) return;
-  emit_row<kWarps>(x, amax, ri.tag, a.q_store + ri.q_off, a.s_store ? a.s_store + ri.s_off : nullptr, nchunk, w, lane);
+  emit_row<kWarps>(x, amax, ri.tag, ri.q_dst, ri.s_dst, nchunk, w, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -334,10 +340,10 @@ __global__ void __launch_bounds__(kBlock) gather_rows_kernel(ActArgs a, TokenQua
   const int pack    = ri.tag == 0 ? 1 : (ri.tag == 1 ? 2 : 4);
   const __half* src = ri.tag == 0 ? (t.f16 ? t.f16 : t.in) : (ri.tag == 1 ? t.q8 : t.q4);
   const uint4* s = reinterpret_cast<const uint4*>(src + tok * (a.k / pack));
-  uint4* d       = reinterpret_cast<uint4*>(a.q_store + ri.q_off);
+  uint4* d       = reinterpret_cast<uint4*>(ri.q_dst);
   const int n16  = (a.k / pack) >> 3;
   for (int c = lane; c < n16; c += 32) d[c] = __ldg(s + c);
-  if (ri.tag != 0 && lane == 0) a.s_store[ri.s_off] = (ri.tag == 1 ? t.s8 : t.s4)[tok];
+  if (ri.tag != 0 && lane == 0) *ri.s_dst = (ri.tag == 1 ? t.s8 : t.s4)[tok];
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -350,7 +356,7 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
   const int row_in_blk = warp / kWarps, w = warp % kWarps;
   const int row     = blockIdx.x * (8 / kWarps) + row_in_blk;
   const bool row_ok = row < a.rows_total;
-  RowInfo ri{0, 0, 0, 0};
+  RowInfo ri{0, 0, nullptr, nullptr};
   if (row_ok) ri = locate_row(a, row);
   const int nchunk = ri.k >> 3;
   const __half* src = nullptr;
@@ -393,7 +399,7 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
     for (int i = 0; i < kWarps; ++i) amax = fmaxf(amax, red[row_in_blk * kWarps + i]);
   }
   if (!row_ok) return;
-  __half* q_dst = a.q_store + ri.q_off;
+  __half* q_dst = ri.q_dst;
   if (ri.tag == 0) {
 #pragma unroll
     for (int j = 0; j < kJ; ++j) {
@@ -403,7 +409,7 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
     return;
   }
   const RowQuant rq(amax, ri.tag);
-  if (w == 0 && lane == 0) a.s_store[ri.s_off] = rq.sc_h;
+  if (w == 0 && lane == 0) *ri.s_dst = rq.sc_h;
 #pragma unroll
   for (int j = 0; j < kJ; ++j) {
     const int ci = chunk_of<kWarps>(w, j, lane);

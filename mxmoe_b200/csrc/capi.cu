@@ -91,11 +91,12 @@ int scheme_of(const mxmoe_qparams& q, int* scheme) {
 // 2-D row-major byte/half matrix [rows, row_bytes] -> tiled tensor map with a box of (box_inner x box_rows)
 int encode_2d(EncodeTiledFn enc, CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
               uint64_t inner_elems, uint64_t rows, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw,
-              const char* what, int idx) {
+              const char* what, int idx, uint64_t pitch_bytes = 0) {
   if (rows == 0 || inner_elems == 0) return fail(MXMOE_ERR_INVALID, "problem %d: empty %s operand", idx, what);
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
     return fail(MXMOE_ERR_INVALID, "problem %d: %s pointer %p is not 16-byte aligned", idx, what, base);
-  const uint64_t pitch = inner_elems * (uint64_t)elem_bytes;
+  const uint64_t pitch = pitch_bytes ? pitch_bytes : inner_elems * (uint64_t)elem_bytes;
+  if (pitch < inner_elems * (uint64_t)elem_bytes) return fail(MXMOE_ERR_INVALID, "problem %d: %s row pitch %llu B is smaller than a row", idx, what, (unsigned long long)pitch);
   if (pitch % 16 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: %s row pitch %llu B is not a multiple of 16", idx, what, (unsigned long long)pitch);
   cuuint64_t gdim[2]    = {inner_elems, rows};
   cuuint64_t gstride[1] = {pitch};
@@ -124,25 +125,25 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
     if ((reinterpret_cast<uintptr_t>(p.scale_b) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 16-byte aligned", idx);
   }
   if (p.out_mode != mxb::OUT_FP16 && p.out_mode != mxb::OUT_ACC) return fail(MXMOE_ERR_INVALID, "problem %d: bad out_mode %d", idx, p.out_mode);
-  const uint64_t a_mul  = p.a_row_mul > 1 ? (uint64_t)p.a_row_mul : 1;
-  const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 * a_mul + (uint64_t)p.M;
-  if (!p.row0_dev && a_rows < (uint64_t)p.row0 * a_mul + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
+  const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
+  const uint64_t lda    = p.lda_bytes > 0 ? (uint64_t)p.lda_bytes : 0;
+  if (!p.row0_dev && a_rows < (uint64_t)p.row0 + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
 
   const uint64_t K = (uint64_t)p.K, N = (uint64_t)p.N;
   switch (scheme) {
     case mxb::SCH_FP16:
       if (p.K % 8) return fail(MXMOE_ERR_INVALID, "problem %d: fp16 needs K %% 8 == 0 (K=%d)", idx, p.K);
-      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
       if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, N, 64, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
       break;
     case mxb::SCH_W8A8:
       if (p.K % 16) return fail(MXMOE_ERR_INVALID, "problem %d: w8a8 needs K %% 16 == 0 (K=%d)", idx, p.K);
-      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, a_rows, 128, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, a_rows, 128, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
       if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, 128, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
       break;
     case mxb::SCH_W4A4:
       if (p.K % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a4 needs K %% 32 == 0 (K=%d)", idx, p.K);
-      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx, lda))) return rc;
       if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
       break;
     case mxb::SCH_W4A16G128:
@@ -150,7 +151,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
       if (p.N % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs N %% 32 == 0 (N=%d)", idx, p.N);
       if (!p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs scale_b (scale, zero) pairs", idx);
       if ((reinterpret_cast<uintptr_t>(p.scale_b) & 3) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 4-byte aligned", idx);
-      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
       // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, 64 packed rows = 256 n
       if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K * 2, N / 4, 128, mxb::kBN / 4, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
       break;
@@ -167,7 +168,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   d->scheme   = scheme;
   d->out_mode = p.out_mode;
   d->ldc      = ldc;
-  d->a_row_mul = p.a_row_mul > 1 ? p.a_row_mul : 1;
+  d->sa_stride = p.sa_stride > 1 ? p.sa_stride : 1;
   return MXMOE_OK;
 }
 
@@ -311,7 +312,7 @@ int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, v
 
 static int to_act_args(const mxmoe_act_args* a, mxb::ActArgs* o, bool silu) {
   if (!a) return fail(MXMOE_ERR_INVALID, "null args");
-  if (!a->in || !a->q_store || !a->exp_qtag || !a->exp_row_start)
+  if (!a->in || !a->q_store || !a->exp_qtag || (!a->exp_row_start && a->rec_stride <= 0))
     return fail(MXMOE_ERR_INVALID, "null pointer in activation arguments");
   if (a->rows_routed > 0 && !a->row_expert) return fail(MXMOE_ERR_INVALID, "row_expert is required for routed rows");
   if (!silu && a->rows_routed > 0 && !a->row_token) return fail(MXMOE_ERR_INVALID, "row_token is required for routed rows");
@@ -342,6 +343,14 @@ static int to_act_args(const mxmoe_act_args* a, mxb::ActArgs* o, bool silu) {
   o->rows_total = a->rows_total;
   o->num_experts = a->num_experts;
   o->rotate = silu ? 0 : a->rotate;
+  o->rec_stride = a->rec_stride > 0 ? a->rec_stride : 0;
+  o->rec_scale_off = a->rec_scale_off;
+  if (o->rec_stride > 0) {
+    const int kmax = a->k > ks ? a->k : ks;
+    if (o->rec_stride % 8) return fail(MXMOE_ERR_INVALID, "rec_stride must be a multiple of 8 fp16 elements");
+    if (o->rec_scale_off >= o->rec_stride) return fail(MXMOE_ERR_INVALID, "rec_scale_off lies outside the record");
+    if (o->rec_stride * 4 < kmax) return fail(MXMOE_ERR_INVALID, "rec_stride %d cannot hold a row of %d elements in any format", o->rec_stride, kmax);
+  }
   return MXMOE_OK;
 }
 

@@ -215,7 +215,7 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         const Tile ti          = find_tile(ctrl, count, t);
         const GGProblemDev* pr = problems + ti.p;
-        const int a_row        = ctrl->row0[ti.p] * pr->a_row_mul + ti.m_tile * kBM;
+        const int a_row        = ctrl->row0[ti.p] + ti.m_tile * kBM;
         for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag)) {
             atomicCAS(&status->error, 0, kDevErrTimeout);
@@ -318,7 +318,7 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
         const int n = ti.n_tile * kBN + lane * 8;
         uint4 sv    = make_uint4(0, 0, 0, 0);
         if (n < N) sv = __ldg(reinterpret_cast<const uint4*>(pr->scale_b + n));
-        if (valid) sa = pr->scale_a[grow];
+        if (valid) sa = pr->scale_a[grow * pr->sa_stride];
         __syncwarp();
         *reinterpret_cast<uint4*>(sbw + lane * 8) = sv;
         __syncwarp();

@@ -45,7 +45,7 @@ struct alignas(128) GGProblemDev {
   int scheme;
   int out_mode;
   int ldc;     // row pitch of C in elements
-  int a_row_mul;  // row shift of A = row0 * a_row_mul (>= 1)
+  int sa_stride;  // distance between per-token scales, in elements (>= 1)
 };
 static_assert(sizeof(GGProblemDev) == 384, "GGProblemDev layout");
 

@@ -49,7 +49,8 @@ class Problem:
     out_mode: int = OUT_FP16
     m_dev: object = None      # int32 device scalar: live row count
     row0_dev: object = None   # int32 device scalar: first row
-    a_row_mul: int = 0
+    lda_bytes: int = 0        # row pitch of A in bytes (0 = dense)
+    sa_stride: int = 0        # distance between per-token scales in elements (0 = contiguous)
 
     def fill(self, c: _lib.GGProblem) -> None:
         a_bits, w_bits, gsize, sym = self.qparams
@@ -60,7 +61,8 @@ class Problem:
         c.a_rows, c.row0, c.ldc = int(self.a_rows), int(self.row0), int(self.ldc)
         c.q.a_bits, c.q.w_bits, c.q.gsize, c.q.sym = int(a_bits), int(w_bits), int(gsize), 1 if sym else 0
         c.out_mode = int(self.out_mode)
-        c.a_row_mul = int(self.a_row_mul)
+        c.lda_bytes = int(self.lda_bytes)
+        c.sa_stride = int(self.sa_stride)
 
     def flops(self) -> int:
         return 2 * self.M * self.N * self.K

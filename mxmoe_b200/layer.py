@@ -3,21 +3,24 @@
 Pipeline of one forward (all on the current CUDA stream)::
 
     route_topk            counts / row offsets / permutation on the device
-    quant_act             gather + (Hadamard) + per-token quantise + pack      -> gate_up operands
+    quant_tokens          (Hadamard) + per-token quantise + pack, once per token
+    gather_rows           copy each routed row into the expert-sorted record store
     grouped GEMM          gate_up of every expert (+ shared expert), one launch
-    silu_mul_then_quant   h = silu(gate) * up, quantise + pack                 -> down operands
+    silu_mul_then_quant   h = silu(gate) * up, quantise + pack
     grouped GEMM          down of every expert (+ shared expert), one launch
     combine_topk          weighted un-permute (+ shared expert output)
 
 Both problem lists are prepared once: their row counts and row offsets are read
-by the kernel from the routing result in device memory, so nothing returns to
-the host between layers (the reference synchronises three times per layer:
-``.cpu()`` of the counts, ``cudaMalloc`` and ``cudaFree``; ref_bind.cu:449-453,
-kernel_sketch.py:87-104, :142-143).
+by the kernel from device memory, so nothing returns to the host between layers
+(the reference synchronises three times per layer: ``.cpu()`` of the counts,
+``cudaMalloc`` and ``cudaFree``; ref_bind.cu:449-453, kernel_sketch.py:87-104,
+:142-143).
 
-Activation stores use a slot layout: every row owns one fp16-sized slot of its
-row length; an expert's packed rows start at the slot of its first row and
-follow each other at their own packed pitch.
+Activation stores use a *record layout*: every row owns one record of fixed size
+(the widest packed row among the experts that can appear in the store); row r is
+at ``r * stride`` whatever its format, and each expert's TMA descriptor uses that
+stride as its row pitch.  Offsets therefore never depend on per-expert counts and
+a store can be handed to another GPU as it is.
 """
 from __future__ import annotations
 
@@ -30,39 +33,177 @@ from .gg import GroupedGemm, Problem, current_stream_ptr
 from .weights import PackedWeight
 
 
-def _tag_of(qp) -> int:
+def tag_of(qp) -> int:
+    """Activation format of a scheme: 0 fp16, 1 int8 per token, 2 int4 per token."""
     a_bits = qp[0]
     return 0 if a_bits >= 16 else (1 if a_bits == 8 else 2)
 
 
-def _pack_of(tag: int) -> int:
+def pack_of(tag: int) -> int:
     return (1, 2, 4)[tag]
 
 
-class MoELayer:
-    """Expert weights of one layer plus preallocated activation buffers for up to ``max_tokens`` tokens.
+def record_stride(row_len: int, tags) -> int:
+    """Record size (fp16 elements) that holds a row of ``row_len`` values in the widest of ``tags``."""
+    return max(row_len // pack_of(t) for t in tags)
 
-    ``gate_up`` / ``down`` map expert id -> :class:`PackedWeight`; key ``num_experts`` is the
-    shared expert.  ``local_experts`` (expert parallelism) restricts the routed experts this
-    instance owns: ids outside of it are ignored by the routing kernel's caller.
+
+def _act_call(fn, **kw):
+    a = _lib.ActArgs()
+    for k, v in kw.items():
+        setattr(a, k, v.data_ptr() if isinstance(v, torch.Tensor) else v)
+    _lib.check(fn(C.byref(a), current_stream_ptr()))
+
+
+class ExpertCompute:
+    """gate_up GEMM -> silu*mul+quantise -> down GEMM over rows that already sit in a record store.
+
+    The rows are described by *segments*: segment i holds ``seg_m[i]`` consecutive rows starting at
+    row ``seg_row0[i]`` that all belong to expert ``seg_expert[i]`` (both numbers live in device
+    memory).  On one GPU a segment is an expert; under expert parallelism it is a (source rank,
+    expert) pair.  ``row_expert`` gives the expert of every row (for the format of the second
+    quantiser).  An optional shared expert runs over ``shared["tokens"]`` token-major rows in the
+    same two launches.
+    """
+
+    def __init__(self, num_experts, hidden, inter, gate_up: dict, down: dict, rows_cap: int,
+                 seg_expert, seg_m: torch.Tensor, seg_row0: torch.Tensor, row_expert: torch.Tensor,
+                 q1: torch.Tensor, rec1: int, scale1_ptr: int, scale1_stride: int, device,
+                 shared: dict | None = None, shared_inter: int = 0):
+        self.E, self.H, self.I, self.Is = num_experts, hidden, inter, shared_inter
+        self.R, self.device = rows_cap, device
+        self.gate_up, self.down = gate_up, down
+        self.row_expert, self.seg_expert = row_expert, list(seg_expert)
+        self.shared = shared
+        dev, R, H, I = device, rows_cap, hidden, inter
+        f16 = dict(dtype=torch.float16, device=dev)
+        local = sorted(set(self.seg_expert))
+
+        def tags(block):
+            t = [0] * (num_experts + 1)
+            for e, w in block.items():
+                t[e] = tag_of(w.qparams)
+            return t
+        self._tag1, self._tag2 = tags(gate_up), tags(down)
+        self.tag2 = torch.tensor(self._tag2, dtype=torch.int32, device=dev)
+        self.rec2 = record_stride(I, {self._tag2[e] for e in local}) if local else I
+        self.o1 = torch.zeros(max(R, 1) * 2 * I, **f16)        # gate_up output rows [R, 2I]
+        self.q2 = torch.zeros(max(R, 1) * self.rec2, **f16)    # down input records
+        self.s2 = torch.zeros(max(R, 1), **f16)
+        self.o2 = torch.zeros(max(R, 1) * H, **f16)            # down output rows [R, H]
+
+        p1, p2 = [], []
+        for i, e in enumerate(self.seg_expert):
+            m_ptr, r_ptr = seg_m.data_ptr() + 4 * i, seg_row0.data_ptr() + 4 * i
+            w1: PackedWeight = gate_up[e]
+            w2: PackedWeight = down[e]
+            p1.append(Problem(A=q1, B=w1.data, C=self.o1, M=R, N=2 * I, K=H, qparams=w1.qparams,
+                              scale_a=scale1_ptr if self._tag1[e] else None, scale_b=w1.scale,
+                              a_rows=R, lda_bytes=rec1 * 2, sa_stride=scale1_stride, m_dev=m_ptr, row0_dev=r_ptr))
+            p2.append(Problem(A=self.q2, B=w2.data, C=self.o2, M=R, N=H, K=I, qparams=w2.qparams,
+                              scale_a=self.s2 if self._tag2[e] else None, scale_b=w2.scale,
+                              a_rows=R, lda_bytes=self.rec2 * 2, m_dev=m_ptr, row0_dev=r_ptr))
+        if shared is not None:
+            T, Is, E = shared["tokens"], shared_inter, num_experts
+            w1, w2 = gate_up[E], down[E]
+            t2 = self._tag2[E]
+            self.rec2s = Is // pack_of(t2)
+            self.o1s = torch.zeros(T * 2 * Is, **f16)
+            self.q2s = torch.zeros(T * self.rec2s, **f16)
+            self.s2s = torch.zeros(T, **f16)
+            self.o2s = torch.zeros(T * H, **f16)
+            # the shared expert reads the token-major store of its format directly: no copy
+            p1.append(Problem(A=shared["a_ptr"], B=w1.data, C=self.o1s, M=T, N=2 * Is, K=H, qparams=w1.qparams,
+                              scale_a=shared["sa_ptr"] if self._tag1[E] else None, scale_b=w1.scale))
+            p2.append(Problem(A=self.q2s, B=w2.data, C=self.o2s, M=T, N=H, K=Is, qparams=w2.qparams,
+                              scale_a=self.s2s if t2 else None, scale_b=w2.scale))
+        else:
+            self.o2s = None
+        self.gg1 = GroupedGemm(p1, device=dev)
+        self.gg2 = GroupedGemm(p2, device=dev)
+        self.launches = 3 + (1 if shared is not None else 0)
+
+    def run(self, rows: int) -> None:
+        """``rows``: upper bound of the rows in use this step (sizes the silu launch)."""
+        lib = _lib.lib()
+        self.gg1.run()
+        _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.q2, s_store=self.s2,
+                  row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
+                  exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
+                  rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1)
+        if self.shared is not None:
+            T = self.shared["tokens"]
+            _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1s, in_shared=self.o1s, q_store=self.q2s,
+                      s_store=self.s2s, row_expert=None, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
+                      exp_q_off=None, exp_s_off=None, signs=None, k=self.Is, k_shared=self.Is, rows_routed=0,
+                      rows_total=T, num_experts=self.E, rotate=0, rec_stride=self.rec2s, rec_scale_off=-1)
+        self.gg2.run()
+
+    def check(self) -> None:
+        self.gg1.check()
+        self.gg2.check()
+
+
+class TokenQuant:
+    """Token-major stores of the once-per-token quantiser: one per activation format in use."""
+
+    def __init__(self, tokens: int, hidden: int, tags_used, rotate: bool, signs, device):
+        f16 = dict(dtype=torch.float16, device=device)
+        self.T, self.H, self.rotate = tokens, hidden, rotate
+        self.signs = None if signs is None else signs.to(device=device, dtype=torch.int8).contiguous()
+        self.f16 = torch.zeros(tokens * hidden, **f16) if (0 in tags_used and rotate) else None
+        self.q8 = torch.zeros(tokens * hidden // 2, **f16) if 1 in tags_used else None
+        self.s8 = torch.zeros(tokens, **f16) if 1 in tags_used else None
+        self.q4 = torch.zeros(tokens * hidden // 4, **f16) if 2 in tags_used else None
+        self.s4 = torch.zeros(tokens, **f16) if 2 in tags_used else None
+        self.args = _lib.TokenQuantArgs()
+
+    def fill(self, hidden: torch.Tensor) -> _lib.TokenQuantArgs:
+        t = self.args
+        t.inp, t.k, t.num_tokens, t.rotate = hidden.data_ptr(), self.H, hidden.shape[0], 1 if self.rotate else 0
+        t.signs = None if self.signs is None else self.signs.data_ptr()
+        for name in ("f16", "q8", "s8", "q4", "s4"):
+            buf = getattr(self, name)
+            setattr(t, name, None if buf is None else buf.data_ptr())
+        return t
+
+    def run(self, hidden: torch.Tensor) -> _lib.TokenQuantArgs:
+        t = self.fill(hidden)
+        _lib.check(_lib.lib().mxmoe_quant_tokens(C.byref(t), current_stream_ptr()))
+        return t
+
+    def rows_of(self, tag: int, hidden: torch.Tensor):
+        """(address of the token-major rows in format ``tag``, address of their scales or None)."""
+        if tag == 0:
+            return (self.f16.data_ptr() if self.f16 is not None else hidden.data_ptr()), None
+        if tag == 1:
+            return self.q8.data_ptr(), self.s8.data_ptr()
+        return self.q4.data_ptr(), self.s4.data_ptr()
+
+
+class MoELayer:
+    """Expert weights of one layer plus preallocated activation buffers for ``max_tokens`` tokens.
+
+    ``gate_up`` / ``down`` map expert id -> :class:`PackedWeight`; key ``num_experts`` is the shared
+    expert.  ``forward`` takes a fixed-address hidden tensor per instance size (the shared expert's
+    descriptor is bound to the address of the first ``hidden`` it sees when no rotation or quantiser
+    produces a token-major copy).
     """
 
     def __init__(self, num_experts: int, topk: int, hidden: int, inter: int, gate_up: dict, down: dict,
                  max_tokens: int, shared_inter: int = 0, signs: torch.Tensor | None = None, rotate: bool = False,
-                 device=None, max_rows: int | None = None, with_shared: bool | None = None):
+                 device=None):
         self.E, self.topk, self.H, self.I, self.Is = num_experts, topk, hidden, inter, shared_inter
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.T = max_tokens
-        self.has_shared = (shared_inter > 0 and num_experts in gate_up) if with_shared is None else with_shared
-        self.rows_cap = max_tokens * topk if max_rows is None else max_rows   # routed rows this instance can hold
+        self.has_shared = shared_inter > 0 and num_experts in gate_up
         self.rotate = rotate
-        self.per_token_quant = True    # quantise once per token, then gather (False: fused per-row kernel)
         self.gate_up, self.down = gate_up, down
         dev = self.device
         i32 = dict(dtype=torch.int32, device=dev)
         f16 = dict(dtype=torch.float16, device=dev)
-        R, T, H, I, Is, E = self.rows_cap, self.T, hidden, inter, shared_inter, num_experts
-        Ts = T if self.has_shared else 0
+        R, T, H, E = max_tokens * topk, max_tokens, hidden, num_experts
+        self.R = R
 
         # routing state
         self.counts = torch.zeros(E, **i32)
@@ -72,73 +213,57 @@ class MoELayer:
         self.slot_row = torch.zeros(max(R, 1), **i32)
         ws = _lib.lib().mxmoe_route_workspace_bytes(max(R, 1), 1, E)
         self.route_ws = torch.zeros(ws // 4 + 1, **i32)
-        self.signs = None if signs is None else signs.to(device=dev, dtype=torch.int8).contiguous()
 
-        # per-expert activation tags (static): index E is the shared expert
-        def tags(block):
-            t = [0] * (E + 1)
-            for e, w in block.items():
-                t[e] = _tag_of(w.qparams)
-            return t
-        self._tag1, self._tag2 = tags(gate_up), tags(down)
-        self.tag1 = torch.tensor(self._tag1, **i32)
-        self.tag2 = torch.tensor(self._tag2, **i32)
-
-        # stores (slot layout) and outputs
-        self.q1 = torch.zeros((R + Ts) * H, **f16)
-        self.s1 = torch.zeros(R + Ts, **f16)
-        self.o1 = torch.zeros(R * 2 * I, **f16)                 # gate_up out, routed rows [R, 2I]
-        self.o1s = torch.zeros(Ts * 2 * Is, **f16) if Ts else None
-        self.q2 = torch.zeros(R * I + Ts * Is, **f16)
-        self.s2 = torch.zeros(R + Ts, **f16)
-        self.o2 = torch.zeros(R * H, **f16)                     # down out, routed rows [R, H]
-        self.o2s = torch.zeros(Ts * H, **f16) if Ts else None
+        tag1 = [0] * (E + 1)
+        for e, w in gate_up.items():
+            tag1[e] = tag_of(w.qparams)
+        self._tag1 = tag1
+        self.tag1 = torch.tensor(tag1, **i32)
+        routed = [e for e in sorted(gate_up) if e < E]
+        self.tq = TokenQuant(T, H, {tag1[e] for e in gate_up}, rotate, signs, dev)
+        self.rec1 = record_stride(H, {tag1[e] for e in routed}) if routed else H
+        self.q1 = torch.zeros(max(R, 1) * self.rec1, **f16)
+        self.s1 = torch.zeros(max(R, 1), **f16)
         self.out = torch.zeros(T * H, **f16)
+        self._routed = routed
+        self._core = None   # built on the first forward (needs the address of `hidden` for an fp16 shared expert)
 
-        # token-major stores of the once-per-token quantiser (one per activation format in use)
-        used = {self._tag1[e] for e in gate_up}
-        self.tq_f16 = torch.zeros(T * H, **f16) if (0 in used and rotate) else None
-        self.tq_q8 = torch.zeros(T * H // 2, **f16) if 1 in used else None
-        self.tq_s8 = torch.zeros(T, **f16) if 1 in used else None
-        self.tq_q4 = torch.zeros(T * H // 4, **f16) if 2 in used else None
-        self.tq_s4 = torch.zeros(T, **f16) if 2 in used else None
-
-        self.gg1 = GroupedGemm(self._problems(gate_up, self._tag1, self.q1, self.s1, self.o1, self.o1s,
-                                               K=H, N=2 * I, Ks=H, Ns=2 * Is), device=dev)
-        self.gg2 = GroupedGemm(self._problems(down, self._tag2, self.q2, self.s2, self.o2, self.o2s,
-                                               K=I, N=H, Ks=Is, Ns=H), device=dev)
-
-    # ------------------------------------------------------------------
-    def _problems(self, block: dict, tag: list, q, s, o, o_shared, K, N, Ks, Ns):
-        R, T, E = self.rows_cap, self.T, self.E
-        probs = []
-        esz = 2
-        for e in sorted(k for k in block if k < E):
-            w: PackedWeight = block[e]
-            p = _pack_of(tag[e])
-            probs.append(Problem(
-                A=q, B=w.data, C=o, M=R, N=N, K=K, qparams=w.qparams,
-                scale_a=s if tag[e] else None, scale_b=w.scale,
-                a_rows=R * p, a_row_mul=p,
-                m_dev=self.counts.data_ptr() + 4 * e, row0_dev=self.row_start.data_ptr() + 4 * e))
+    def _build_core(self, hidden: torch.Tensor) -> None:
+        shared = None
         if self.has_shared:
-            w = block[E]
-            # shared rows follow the routed slots; their count (T) and position are static
-            probs.append(Problem(
-                A=q.data_ptr() + R * K * esz, B=w.data, C=o_shared, M=T, N=Ns, K=Ks, qparams=w.qparams,
-                scale_a=(s.data_ptr() + R * esz) if tag[E] else None, scale_b=w.scale))
-        return probs
+            a_ptr, sa_ptr = self.tq.rows_of(self._tag1[self.E], hidden)
+            shared = {"tokens": self.T, "a_ptr": a_ptr, "sa_ptr": sa_ptr}
+        self._hidden_ptr = hidden.data_ptr()
+        # one segment per routed expert: rows [row_start[e], row_start[e] + counts[e])
+        seg_m = self.counts
+        seg_row0 = self.row_start
+        # segments must index seg_m / seg_row0 by position: experts are 0..E-1 in order here
+        assert self._routed == list(range(len(self._routed))), "single-GPU layer owns experts 0..E-1"
+        self._core = ExpertCompute(self.E, self.H, self.I, self.gate_up, self.down, self.R, self._routed, seg_m,
+                                   seg_row0, self.row_expert, self.q1, self.rec1, self.s1.data_ptr(), 1, self.device,
+                                   shared=shared, shared_inter=self.Is)
+        self.gg1, self.gg2 = self._core.gg1, self._core.gg2
 
-    def _act(self, fn, **kw):
-        a = _lib.ActArgs()
-        for k, v in kw.items():
-            setattr(a, k, v.data_ptr() if isinstance(v, torch.Tensor) else v)
-        _lib.check(fn(C.byref(a), current_stream_ptr()))
+    # buffers of the compute core, exposed for tests and benchmarks
+    @property
+    def o1(self):
+        return self._core.o1
 
-    # ------------------------------------------------------------------
+    @property
+    def o2(self):
+        return self._core.o2
+
+    @property
+    def o1s(self):
+        return self._core.o1s
+
+    @property
+    def o2s(self):
+        return self._core.o2s
+
     def route(self, topk_ids: torch.Tensor) -> None:
         T, k = topk_ids.shape
-        assert T * k <= self.rows_cap and topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()
+        assert T * k <= self.R and topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()
         a = _lib.RouteArgs()
         a.topk_ids, a.counts, a.row_start = topk_ids.data_ptr(), self.counts.data_ptr(), self.row_start.data_ptr()
         a.row_expert, a.row_token, a.slot_row = (self.row_expert.data_ptr(), self.row_token.data_ptr(),
@@ -147,68 +272,46 @@ class MoELayer:
         a.num_tokens, a.topk, a.num_experts = T, k, self.E
         _lib.check(_lib.lib().mxmoe_route_topk(C.byref(a), current_stream_ptr()))
 
-    def experts_forward(self, hidden: torch.Tensor, rows: int) -> None:
-        """quant -> gate_up -> silu*mul+quant -> down over the rows already described by the routing state.
-
-        ``rows`` is the number of routed rows (static upper bound of this step: T * topk locally,
-        or the receive capacity under expert parallelism); ``hidden`` is what ``row_token`` indexes.
-        """
-        lib = _lib.lib()
-        T = hidden.shape[0] if self.has_shared else 0
-        R = self.rows_cap
-        assert rows <= R
-        # the shared expert's rows sit right after the R routed slots: describe them by rows_routed = R
-        # when a shared expert is present (rows between `rows` and R are simply not produced).
-        if self.has_shared:
-            assert rows == R, "with a shared expert the routed row count must equal the capacity"
-        if self.per_token_quant:
-            t = _lib.TokenQuantArgs()
-            t.inp, t.k, t.num_tokens, t.rotate = hidden.data_ptr(), self.H, hidden.shape[0], 1 if self.rotate else 0
-            t.signs = None if self.signs is None else self.signs.data_ptr()
-            for name in ("f16", "q8", "s8", "q4", "s4"):
-                buf = getattr(self, "tq_" + name)
-                setattr(t, name, None if buf is None else buf.data_ptr())
-            _lib.check(lib.mxmoe_quant_tokens(C.byref(t), current_stream_ptr()))
-            a = _lib.ActArgs()
-            a.q_store, a.s_store = self.q1.data_ptr(), self.s1.data_ptr()
-            a.row_expert, a.row_token = self.row_expert.data_ptr(), self.row_token.data_ptr()
-            a.exp_qtag, a.exp_row_start = self.tag1.data_ptr(), self.row_start.data_ptr()
-            a.k, a.k_shared, a.rows_routed, a.rows_total, a.num_experts = self.H, self.H, rows, rows + T, self.E
-            _lib.check(lib.mxmoe_gather_rows(C.byref(a), C.byref(t), current_stream_ptr()))
-        else:
-            self._act(lib.mxmoe_quant_act, inp=hidden, in_shared=None, q_store=self.q1, s_store=self.s1,
-                      row_expert=self.row_expert, row_token=self.row_token, exp_qtag=self.tag1,
-                      exp_row_start=self.row_start, exp_q_off=None, exp_s_off=None, signs=self.signs,
-                      k=self.H, k_shared=self.H, rows_routed=rows, rows_total=rows + T, num_experts=self.E,
-                      rotate=1 if self.rotate else 0)
-        self.gg1.run()
-        self._act(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=self.o1s, q_store=self.q2, s_store=self.s2,
-                  row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=self.row_start,
-                  exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.Is if self.has_shared else self.I,
-                  rows_routed=rows, rows_total=rows + T, num_experts=self.E, rotate=0)
-        self.gg2.run()
+    def gather(self, t: _lib.TokenQuantArgs, rows: int, q_store: torch.Tensor, rec_stride: int,
+               s_store: torch.Tensor | None, rec_scale_off: int = -1) -> None:
+        a = _lib.ActArgs()
+        a.q_store = q_store.data_ptr()
+        a.s_store = None if s_store is None else s_store.data_ptr()
+        a.row_expert, a.row_token = self.row_expert.data_ptr(), self.row_token.data_ptr()
+        a.exp_qtag = self.tag1.data_ptr()
+        a.k, a.k_shared, a.rows_routed, a.rows_total, a.num_experts = self.H, self.H, rows, rows, self.E
+        a.rec_stride, a.rec_scale_off = rec_stride, rec_scale_off
+        _lib.check(_lib.lib().mxmoe_gather_rows(C.byref(a), C.byref(t), current_stream_ptr()))
 
     def forward(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor | None = None):
         """``[T, H]`` fp16 hidden states + ``[T, topk]`` int32 expert ids (+ fp32 gate weights) -> ``[T, H]`` fp16."""
         T = hidden.shape[0]
         assert T == self.T, "this layer instance was sized for a fixed token count"
         with torch.cuda.device(self.device):
+            if self._core is None:
+                self._build_core(hidden)
+            if self.has_shared and self._tag1[self.E] == 0 and not self.rotate:
+                assert hidden.data_ptr() == self._hidden_ptr, \
+                    "an fp16 shared expert reads `hidden` in place: pass the same buffer every step"
             self.route(topk_ids)
-            self.experts_forward(hidden, T * self.topk)
+            t = self.tq.run(hidden)
+            self.gather(t, T * self.topk, self.q1, self.rec1, self.s1)
+            self._core.run(T * self.topk)
             out = self.out.view(self.T, self.H)
             _lib.check(_lib.lib().mxmoe_combine_topk(
-                self.o2.data_ptr(), self.slot_row.data_ptr(),
+                self._core.o2.data_ptr(), self.slot_row.data_ptr(),
                 None if topk_weights is None else topk_weights.data_ptr(),
-                self.o2s.data_ptr() if self.has_shared else None, out.data_ptr(), T, self.topk, self.H,
+                self._core.o2s.data_ptr() if self.has_shared else None, out.data_ptr(), T, self.topk, self.H,
                 current_stream_ptr()))
         return out
 
-    def check(self) -> None:
-        self.gg1.check()
-        self.gg2.check()
+    launches_per_step = 9   # route x3, quant_tokens, gather_rows, GEMM, silu, GEMM, combine (+1 with a shared expert)
 
-    # algorithmic traffic of the two grouped GEMMs for given per-expert row counts (bytes)
+    def check(self) -> None:
+        self._core.check()
+
     def gemm_bytes(self, counts: list[int]) -> int:
+        """Algorithmic traffic of the two grouped GEMMs for given per-expert row counts (bytes)."""
         total = 0
         for block, K, N, Ks, Ns in ((self.gate_up, self.H, 2 * self.I, self.H, 2 * self.Is),
                                     (self.down, self.I, self.H, self.Is, self.H)):

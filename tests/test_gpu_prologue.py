@@ -158,7 +158,7 @@ def test_device_routing_matches_stable_sort(cuda_device, t, e, k):
     lay = MoELayer.__new__(MoELayer)
     # only the routing state of a layer is needed here
     dev = cuda_device
-    lay.E, lay.rows_cap = e, t * k
+    lay.E, lay.R = e, t * k
     lay.counts = torch.zeros(e, dtype=torch.int32, device=dev)
     lay.row_start = torch.zeros(e + 1, dtype=torch.int32, device=dev)
     lay.row_expert = torch.zeros(t * k, dtype=torch.int32, device=dev)
