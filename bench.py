@@ -290,7 +290,7 @@ def main():
     ms_e2e = e0.elapsed_time(e1)
 
     # ---- aggregate over ranks (max time)
-    counts = layer.counts_host() if world > 1 else layer.counts.cpu().tolist()
+    counts = layer.counts.cpu().tolist() if world == 1 else None
     flops_rank = spec.flops()             # every rank contributes T tokens worth of routed + shared work
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:

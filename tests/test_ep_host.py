@@ -1,0 +1,78 @@
+"""Host logic of the expert-parallel layer on CPU ranks (gloo, world size 2 and 3): expert ranges,
+split sizes and receive-side segments from the gathered counts, and the two row exchanges."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mxmoe_b200.ep import ExchangePlan, exchange_rows, expert_ranges
+
+
+def test_expert_ranges():
+    assert expert_ranges(60, 8) == [(0, 8), (8, 16), (16, 24), (24, 32), (32, 39), (39, 46), (46, 53), (53, 60)]
+    assert expert_ranges(64, 8)[-1] == (56, 64)
+    assert expert_ranges(8, 8) == [(i, i + 1) for i in range(8)]
+    assert expert_ranges(8, 1) == [(0, 8)]
+
+
+def test_plan_from_counts():
+    counts = [[3, 0, 2, 1], [1, 1, 0, 5]]           # [source][expert]
+    r = expert_ranges(4, 2)
+    p0 = ExchangePlan.build(counts, r, 0)
+    assert p0.send_rows == [3, 3] and p0.recv_rows == [3, 2]
+    assert p0.seg_m == [3, 0, 1, 1] and p0.seg_row0 == [0, 3, 3, 4] and p0.total_recv == 5
+    p1 = ExchangePlan.build(counts, r, 1)
+    assert p1.send_rows == [2, 5] and p1.recv_rows == [3, 5] and p1.total_recv == 8
+    assert p1.seg_m == [2, 1, 0, 5]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, experts):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(100 + rank)
+        rows = 40 + 7 * rank
+        expert_of_row = torch.sort(torch.randint(0, experts, (rows,), generator=g)).values     # sorted = grouped by rank
+        counts = torch.bincount(expert_of_row, minlength=experts).to(torch.int32)
+        gathered = [torch.zeros(experts, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(gathered, counts)
+        counts_all = torch.stack(gathered).tolist()
+        ranges = expert_ranges(experts, world)
+        plan = ExchangePlan.build(counts_all, ranges, rank)
+        assert sum(plan.send_rows) == rows
+        # record = (source rank, row index at the source, expert)
+        send = torch.stack([torch.full((rows,), float(rank)), torch.arange(rows, dtype=torch.float32),
+                            expert_of_row.float()], dim=1)
+        recv = torch.full((plan.total_recv + 3, 3), -1.0)
+        exchange_rows(recv, send, plan.recv_rows, plan.send_rows)
+        lo, hi = ranges[rank]
+        i = 0
+        for s in range(world):
+            for e in range(lo, hi):
+                m, r0 = plan.seg_m[i], plan.seg_row0[i]
+                seg = recv[r0:r0 + m]
+                assert (seg[:, 0] == s).all() and (seg[:, 2] == e).all()
+                assert (seg[1:, 1] > seg[:-1, 1]).all()          # source order is kept inside a segment
+                i += 1
+        assert (recv[plan.total_recv:] == -1).all()
+        # "expert compute": scale every row by (expert + 1), then send the rows home
+        out = recv[: plan.total_recv] * (recv[: plan.total_recv, 2:3] + 1)
+        back = torch.zeros(rows, 3)
+        exchange_rows(back, out, plan.send_rows, plan.recv_rows)
+        assert torch.equal(back, send * (expert_of_row.float()[:, None] + 1))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,experts", [(2, 6), (3, 8)])
+def test_row_exchange_on_cpu_ranks(world, experts):
+    mp.spawn(_worker, args=(world, _free_port(), experts), nprocs=world, join=True)
