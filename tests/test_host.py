@@ -143,3 +143,21 @@ def test_workload_json_schema():
 def test_flops_formula():
     spec = workload.CONFIGS["qwen15-w4a4-8192"]
     assert spec.flops() == 2 * 32768 * (2816 * 2048 + 2048 * 1408)
+
+
+def test_perf_table_schema_matches_the_solver_input():
+    """Keys and fields the reference solver reads (bits_solver.py:518-542): table[scheme]["1"|"3"][repr(tile)]["inc"]."""
+    from mxmoe_b200 import perf_table
+    path = os.path.join(ROOT, "mxmoe_b200", "perf", "performance_table.json")
+    table = json.load(open(path))
+    assert set(table) == set(weights.SCHEMES)
+    for scheme, by_key in table.items():
+        sk = "1" if ("a16" in scheme or scheme == "fp16") else "3"
+        assert list(by_key) == [sk]
+        key = repr(perf_table.b200_tile(scheme))
+        assert key.startswith("TileConfig(BM=128, BN=256, BK=") and key in by_key[sk]
+        cost = by_key[sk][key]
+        assert {"first_iter_cost", "inc", "stderr"} <= set(cost) and cost["inc"] > 0
+    # int8 tiles must be cheaper than fp16 tiles of the same shape, 4-bit weight-only the most expensive
+    inc = {s: next(iter(next(iter(v.values())).values()))["inc"] for s, v in table.items()}
+    assert inc["w8a8_g-1_sym"] < inc["fp16"] < inc["w4a16_g128_asym"]
