@@ -261,11 +261,11 @@ int mxmoe_gg_check(void* workspace, void* stream) {
   CUDA_TRY(cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   if (words[0] != 0) {
-    static const char* roles[] = {"?", "producer", "mma(accumulator)", "mma(operands)", "epilogue", "converter"};
+    static const char* roles[] = {"?", "producer", "mma(accumulator)", "mma(operands)", "epilogue", "converter", "converter(pacing)"};
     const int role = (words[1] >> 24) & 0xff;
     return fail(MXMOE_ERR_DEVICE, "kernel reported error %d (%s) in role %s at tile %d", words[0],
                 words[0] == mxb::kDevErrTimeout ? "bounded wait ran out" : "too many problems",
-                role < 6 ? roles[role] : "?", words[1] & 0xffffff);
+                role < 7 ? roles[role] : "?", words[1] & 0xffffff);
   }
   return MXMOE_OK;
 }

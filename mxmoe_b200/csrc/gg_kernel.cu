@@ -254,6 +254,9 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      // The converter arrives on cvt[s] only for tiles with a 4-bit operand, so those barriers complete
+      // fewer phases than full[s] / empty[s]: their parity is tracked per stage, on use (bit s).
+      uint32_t cvt_parity = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         const Tile ti = find_tile(ctrl, count, t);
@@ -269,7 +272,10 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
         const uint32_t idesc  = is_int ? idesc_i8(kBM, kBN) : idesc_f16(kBM, kBN);
         for (int kb = 0; kb < ti.nkb; ++kb) {
           bool w = wait_bar(smem_u32(&ctrl->full[stage]), phase, abort_flag);
-          if (w && has_cvt) w = wait_bar(smem_u32(&ctrl->cvt[stage]), phase, abort_flag);
+          if (w && has_cvt) {
+            w = wait_bar(smem_u32(&ctrl->cvt[stage]), (cvt_parity >> stage) & 1u, abort_flag);
+            cvt_parity ^= 1u << stage;
+          }
           if (!w) {
             atomicCAS(&status->error, 0, kDevErrTimeout);
             atomicCAS(&status->where, 0, (3 << 24) | t);
@@ -403,10 +409,22 @@ gg_persistent_kernel(const GGProblemDev* __restrict__ problems, int count, GGSta
     for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
       const Tile ti = find_tile(ctrl, count, t);
       if (ti.scheme != SCH_W4A4 && ti.scheme != SCH_W4A16G128) {
-        // nothing to convert: keep the ring position in step with the other roles
-        const int adv = stage + ti.nkb;
-        if ((adv / C::kStages) & 1) phase ^= 1u;
-        stage = adv % C::kStages;
+        // Nothing to convert, but the ring must still be followed stage by stage: a role that ran
+        // more than one ring revolution ahead of the producer would see the parity of an older
+        // phase of full[s] and mistake it for the one it is waiting for.
+        for (int kb = 0; kb < ti.nkb; ++kb) {
+          bool ok = wait_bar(smem_u32(&ctrl->full[stage]), phase, abort_flag);
+          ok      = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) {
+              atomicCAS(&status->error, 0, kDevErrTimeout);
+              atomicCAS(&status->where, 0, (6 << 24) | t);
+            }
+            alive = false;
+            break;
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
         continue;
       }
       const GGProblemDev* pr = problems + ti.p;

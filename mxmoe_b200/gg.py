@@ -103,10 +103,10 @@ class GroupedGemm:
             _lib.check(_lib.lib().mxmoe_gg_check(self._ws, current_stream_ptr()))
 
 
-def grouped_gemm(problems: Sequence[Problem], check: bool = True) -> GroupedGemm:
+def grouped_gemm(problems: Sequence[Problem], check: bool = True, num_ctas: int = 0) -> GroupedGemm:
     """Prepare, launch once and (by default) check."""
     g = GroupedGemm(problems)
-    g.run()
+    g.run(num_ctas)
     if check:
         g.check()
     return g

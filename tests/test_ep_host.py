@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mxmoe_b200.ep import ExchangePlan, exchange_rows, expert_ranges
+from mxmoe_b200.ep import ExchangePlan, exchange_rows, expert_ranges, strided_placement
 
 
 def test_expert_ranges():
@@ -16,6 +16,16 @@ def test_expert_ranges():
     assert expert_ranges(64, 8)[-1] == (56, 64)
     assert expert_ranges(8, 8) == [(i, i + 1) for i in range(8)]
     assert expert_ranges(8, 1) == [(0, 8)]
+
+
+def test_strided_placement():
+    remap, inverse, ranges = strided_placement(10, 4)
+    assert inverse == [0, 4, 8, 1, 5, 9, 2, 6, 3, 7]
+    assert ranges == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert [remap[e] for e in inverse] == list(range(10))
+    for r, (lo, hi) in enumerate(ranges):
+        assert all(inverse[n] % 4 == r for n in range(lo, hi))
+    assert strided_placement(8, 8)[2] == [(i, i + 1) for i in range(8)]
 
 
 def test_plan_from_counts():

@@ -103,6 +103,26 @@ def test_mixed_schemes_one_launch(cuda_device):
             assert og.rel_l2(got, c.ref) <= REL_L2
 
 
+@pytest.mark.parametrize("num_ctas", [1, 2, 3, 7])
+def test_few_ctas_walk_many_tiles_of_alternating_schemes(cuda_device, num_ctas):
+    """With a handful of CTAs every CTA processes a long sequence of tiles whose schemes alternate
+    (direct / converted, int / float): ring positions, barrier parities and TMEM buffers must stay
+    consistent across every kind of transition."""
+    rng = np.random.default_rng(100 + num_ctas)
+    cases = [util.WxAxCase(rng, 300, 512, 384, 8), util.WxAxCase(rng, 200, 768, 256, 4),
+             util.Fp16Case(rng, 140, 512, 192), util.WxAxCase(rng, 129, 256, 640, 8),
+             util.W4A16Case(rng, 260, 512, 256), util.WxAxCase(rng, 64, 1024, 128, 4),
+             util.WxAxCase(rng, 257, 512, 512, 8), util.W4A16Case(rng, 30, 768, 128),
+             util.Fp16Case(rng, 200, 264, 64), util.WxAxCase(rng, 500, 256, 1408, 4)]
+    util.run([c.problem(cuda_device) for c in cases], num_ctas=num_ctas)
+    for i, c in enumerate(cases):
+        got = c.C.cpu().numpy()
+        if isinstance(c, util.WxAxCase):
+            assert np.array_equal(got.view(np.uint16), c.ref.view(np.uint16)), f"problem {i}"
+        else:
+            assert og.rel_l2(got, c.ref) <= REL_L2, f"problem {i}"
+
+
 def test_direct_only_launch_uses_no_converter(cuda_device):
     rng = np.random.default_rng(11)
     cases = [util.WxAxCase(rng, 150, 512, 512, 8), util.Fp16Case(rng, 150, 512, 512)]

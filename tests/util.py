@@ -92,8 +92,8 @@ class W4A16Case:
                           scale_b=self.SB, out_mode=out_mode)
 
 
-def run(problems):
+def run(problems, num_ctas=0):
     g = gg.GroupedGemm(problems)
-    g.run()
+    g.run(num_ctas)
     g.check()
     return g
