@@ -104,8 +104,11 @@ typedef struct mxmoe_gg_plan {
 int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,
                      void* stream, mxmoe_gg_plan* plan);
 
-/* Launch the persistent kernel over a prepared workspace.  `num_ctas` <= 0 uses
- * one CTA per SM.  May be called any number of times after one prepare. */
+/* Launch the persistent kernel over a prepared workspace; may be called any number of times after
+ * one prepare.  `num_ctas` == 0: the default kernel on every SM (CTA pairs, tcgen05 cta_group::2,
+ * 256 x 256 tiles; environment MXMOE_GG_KERNEL=single selects the single-CTA kernel instead);
+ * > 0: the single-CTA kernel (128 x 256 tiles) with that many CTAs; < 0: the CTA-pair kernel with
+ * -num_ctas CTAs (rounded down to even).  All choices give identical results. */
 int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream);
 
 /* prepare + run */

@@ -10,6 +10,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -72,7 +73,8 @@ int device_state(DeviceState** out) {
     if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
       return fail(MXMOE_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
     st.encode = reinterpret_cast<EncodeTiledFn>(fn);
-    CUDA_TRY(mxb::gg_configure_kernels());
+    CUDA_TRY(mxb::gg_configure_single());
+    CUDA_TRY(mxb::gg_configure_pair());
     st.ready = true;
   }
   *out = &st;
@@ -134,17 +136,17 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
     case mxb::SCH_FP16:
       if (p.K % 8) return fail(MXMOE_ERR_INVALID, "problem %d: fp16 needs K %% 8 == 0 (K=%d)", idx, p.K);
       if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
-      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, N, 64, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, N, 64, mxb::kBN / 2, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
       break;
     case mxb::SCH_W8A8:
       if (p.K % 16) return fail(MXMOE_ERR_INVALID, "problem %d: w8a8 needs K %% 16 == 0 (K=%d)", idx, p.K);
       if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, a_rows, 128, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
-      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, 128, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, 128, mxb::kBN / 2, CU_TENSOR_MAP_SWIZZLE_128B, "B", idx))) return rc;
       break;
     case mxb::SCH_W4A4:
       if (p.K % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a4 needs K %% 32 == 0 (K=%d)", idx, p.K);
       if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx, lda))) return rc;
-      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN / 2, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
       break;
     case mxb::SCH_W4A16G128:
       if (p.K % 128) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs K %% 128 == 0 (K=%d)", idx, p.K);
@@ -152,8 +154,8 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
       if (!p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs scale_b (scale, zero) pairs", idx);
       if ((reinterpret_cast<uintptr_t>(p.scale_b) & 3) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 4-byte aligned", idx);
       if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, K, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
-      // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, 64 packed rows = 256 n
-      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K * 2, N / 4, 128, mxb::kBN / 4, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
+      // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, a box of 32 packed rows = 128 n
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K * 2, N / 4, 128, mxb::kBN / 8, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
       break;
   }
   d->scale_a  = static_cast<const __half*>(p.scale_a);
@@ -170,6 +172,16 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   d->ldc      = ldc;
   d->sa_stride = p.sa_stride > 1 ? p.sa_stride : 1;
   return MXMOE_OK;
+}
+
+// MXMOE_GG_KERNEL=single|pair overrides which kernel a launch with num_ctas == 0 uses
+bool default_pair() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MXMOE_GG_KERNEL");
+    v = (e && !strcmp(e, "single")) ? 0 : 1;
+  }
+  return v == 1;
 }
 
 struct ShimScratch {
@@ -239,10 +251,17 @@ int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void*
   const int count = plan->count, needs_cvt = plan->needs_cvt;
   if (count < 0 || count > mxb::kMaxProblems) return fail(MXMOE_ERR_WORKSPACE, "plan holds an invalid problem count %d", count);
   if (count == 0) return MXMOE_OK;
-  if (num_ctas <= 0 || num_ctas > st->sm_count) num_ctas = st->sm_count;
   auto* status = static_cast<mxb::GGStatus*>(workspace);
   auto* probs  = reinterpret_cast<const mxb::GGProblemDev*>(static_cast<unsigned char*>(workspace) + sizeof(mxb::GGStatus));
-  mxb::gg_launch_kernel(probs, count, status, needs_cvt != 0, num_ctas, static_cast<cudaStream_t>(stream));
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  // num_ctas > 0: single-CTA kernel with that many CTAs; < 0: CTA-pair kernel with -num_ctas CTAs;
+  // 0: the library default on every SM
+  bool pair = num_ctas < 0 || (num_ctas == 0 && default_pair());
+  int n     = num_ctas < 0 ? -num_ctas : num_ctas;
+  if (n <= 0 || n > st->sm_count) n = st->sm_count;
+  if (pair && n < 2) pair = false;
+  if (pair) CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt != 0, n & ~1, cs));
+  else      mxb::gg_launch_single(probs, count, status, needs_cvt != 0, n, cs);
   CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;
 }

@@ -1,0 +1,292 @@
+// Device code shared by the single-CTA and the CTA-pair grouped GEMM kernels: bounded waits,
+// tile lookup, the fused epilogue and the 4-bit converters.
+#pragma once
+#include "gg_types.h"
+#include "ptx.cuh"
+
+namespace mxb {
+namespace ggc {
+
+using namespace ptx;
+
+constexpr uint64_t kTimeoutNs = 1000000000ull;
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it       = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kTimeoutNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// per-problem scheduling tables kept in shared memory
+struct Sched {
+  int total_tiles;
+  int pad[3];
+  int tile_end[kMaxProblems];   // inclusive prefix sum of tiles
+  int m_eff[kMaxProblems];      // rows of each problem
+  int row0[kMaxProblems];       // row shift of each problem
+  int meta[kMaxProblems];       // n_tiles << 16 | nkb << 4 | scheme   (nkb < 4096)
+};
+
+struct Tile {
+  int p, m_tile, n_tile, scheme, nkb;
+};
+
+// Fill the tables (all threads of the CTA; contains two __syncthreads).  `rows_per_tile` is 128 for
+// the single-CTA kernel and 256 for the CTA pair.
+__device__ __forceinline__ void build_sched(Sched* sc, const GGProblemDev* problems, int count, int rows_per_tile) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  for (int p = tid; p < count; p += blockDim.x) {
+    const GGProblemDev& pr = problems[p];
+    int m = pr.M;
+    if (pr.m_dev) m = min(max(*pr.m_dev, 0), pr.M);
+    const int r0     = pr.row0_dev ? *pr.row0_dev : pr.row0;
+    const int nt     = (pr.N + kBN - 1) / kBN;
+    const int kelems = (pr.scheme == SCH_W8A8 || pr.scheme == SCH_W4A4) ? 128 : 64;
+    const int nkb    = (pr.K + kelems - 1) / kelems;
+    sc->tile_end[p] = ((m + rows_per_tile - 1) / rows_per_tile) * nt;
+    sc->m_eff[p]    = m;
+    sc->row0[p]     = r0;
+    sc->meta[p]     = (nt << 16) | (nkb << 4) | pr.scheme;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    int carry = 0;
+    for (int base = 0; base < count; base += 32) {
+      const int p = base + lane;
+      int v       = (p < count) ? sc->tile_end[p] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      v += carry;
+      if (p < count) sc->tile_end[p] = v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) sc->total_tiles = carry;
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ Tile find_tile(const Sched* c, int count, int t) {
+  int lo = 0, hi = count - 1;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (t < c->tile_end[mid]) hi = mid; else lo = mid + 1;
+  }
+  const int start = lo ? c->tile_end[lo - 1] : 0;
+  const int meta  = c->meta[lo];
+  const int nt    = meta >> 16;
+  const int idx   = t - start;
+  Tile r;
+  r.p      = lo;
+  r.m_tile = idx / nt;
+  r.n_tile = idx - r.m_tile * nt;
+  r.scheme = meta & 15;
+  r.nkb    = (meta >> 4) & 0xFFF;
+  return r;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// 4-bit code pair (bits [0,4) of each 16-bit half) -> half2, exact (1024 + q) - 1024,
+// then one fp16 FMA with (scale, zero): the arithmetic of quantize.cuh:79-93, :189-190.
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t w, int nib, __half2 s2, __half2 z2) {
+  uint32_t h = ((w >> (4 * nib)) & 0x000f000fu) | 0x64006400u;
+  __half2 q  = __hsub2(*reinterpret_cast<__half2*>(&h), __half2half2(__ushort_as_half((unsigned short)0x6400)));
+  __half2 r  = __hfma2(q, s2, z2);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// ---------------------------------------------------------------------------------- converters
+// w4a4: `rows` packed rows of 64 bytes (128 two's-complement nibbles) at `src` -> rows of 128 int8
+// bytes at `dst` in the 128-byte-swizzled operand layout.  Code q becomes the byte 16*q: both
+// operands carry the factor, the accumulator is 256x the true one and is shifted back in the
+// epilogue.  128 threads, `ct` = thread index in the converter group.
+__device__ __forceinline__ void convert_w4a4(uint32_t src, uint32_t dst, int rows, int ct) {
+  const int iters = rows >> 5;   // rows * 4 chunks / 128 threads
+#pragma unroll 4
+  for (int i = 0; i < iters; ++i) {
+    const int g   = i * 128 + ct;
+    const int row = g >> 2;
+    const int c   = g & 3;
+    const uint4 w = lds128(src + row * 64 + c * 16);
+    uint4 hi, lo;
+    hi.x = w.x & 0xF0F0F0F0u; lo.x = (w.x << 4) & 0xF0F0F0F0u;
+    hi.y = w.y & 0xF0F0F0F0u; lo.y = (w.y << 4) & 0xF0F0F0F0u;
+    hi.z = w.z & 0xF0F0F0F0u; lo.z = (w.z << 4) & 0xF0F0F0F0u;
+    hi.w = w.w & 0xF0F0F0F0u; lo.w = (w.w << 4) & 0xF0F0F0F0u;
+    const uint32_t drow = dst + row * 128;
+    const int sw        = row & 7;
+    sts128(drow + (((2 * c) ^ sw) << 4), hi);
+    sts128(drow + (((2 * c + 1) ^ sw) << 4), lo);
+  }
+}
+
+// w4a16 group-128: which part of the packed weight tile a converter thread owns.  A packed row holds
+// 8 interleaved n-rows x 64 k as 8 chunks of 16 bytes; chunk 2*kb16 + fh carries, for the 16-k block
+// kb16, the rows n_lo = 32*(prow/8) + 16*fh + prow%8 (nibbles 0,1) and n_lo + 8 (nibbles 2,3).
+template <int kPackedRows>   // 64: a 256-row B tile; 32: one CTA's 128-row half
+struct W4A16Lane {
+  int prow, fh, r, n_lo, kb0;
+  static constexpr int kIters = kPackedRows == 64 ? 4 : 2;
+  __device__ __forceinline__ explicit W4A16Lane(int ct) {
+    if (kPackedRows == 64) {
+      prow = ct >> 1; fh = ct & 1; kb0 = 0;
+    } else {
+      const int c2 = ct & 63;
+      prow = c2 >> 1; fh = c2 & 1; kb0 = 2 * (ct >> 6);
+    }
+    r    = prow & 7;
+    n_lo = 32 * (prow >> 3) + 16 * fh + r;
+  }
+  // 16-k block handled in iteration i (rotated per row so that neighbouring threads hit different banks)
+  __device__ __forceinline__ int kb16(int i) const {
+    return kPackedRows == 64 ? ((prow + i) & 3) : (kb0 + ((prow + i) & 1));
+  }
+};
+
+template <int kPackedRows>
+__device__ __forceinline__ void convert_w4a16(const W4A16Lane<kPackedRows>& ln, uint32_t raw_b, uint32_t op_b,
+                                              __half2 sz_lo, __half2 sz_hi) {
+  const uint32_t src = raw_b + ln.prow * 128;
+  const uint32_t dlo = op_b + ln.n_lo * 128;
+  const uint32_t dhi = dlo + 8 * 128;
+  const __half2 s_lo = __half2half2(__low2half(sz_lo)), z_lo = __half2half2(__high2half(sz_lo));
+  const __half2 s_hi = __half2half2(__low2half(sz_hi)), z_hi = __half2half2(__high2half(sz_hi));
+#pragma unroll
+  for (int i = 0; i < W4A16Lane<kPackedRows>::kIters; ++i) {
+    const int kb16 = ln.kb16(i);
+    const uint4 w  = lds128(src + (2 * kb16 + ln.fh) * 16);
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c = cc ^ ln.fh;   // odd threads write the other k-half first (bank spread)
+      const uint32_t phys = (uint32_t)(((2 * kb16 + c) ^ ln.r) << 4);
+      uint4 o;
+      // nibble 2*fl + c of every word: fl = 0 -> row n_lo, fl = 1 -> row n_hi
+      o.x = dequant_pair(w.x, c, s_lo, z_lo); o.y = dequant_pair(w.y, c, s_lo, z_lo);
+      o.z = dequant_pair(w.z, c, s_lo, z_lo); o.w = dequant_pair(w.w, c, s_lo, z_lo);
+      sts128(dlo + phys, o);
+      o.x = dequant_pair(w.x, 2 + c, s_hi, z_hi); o.y = dequant_pair(w.y, 2 + c, s_hi, z_hi);
+      o.z = dequant_pair(w.z, 2 + c, s_hi, z_hi); o.w = dequant_pair(w.w, 2 + c, s_hi, z_hi);
+      sts128(dhi + phys, o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------- epilogue
+// One warp handles 32 rows (TMEM lanes) x 256 columns of a tile.
+struct EpiCtx {
+  int N, ldc, out_mode, acc_shift, n_col0;
+  bool valid, is_int;
+  int64_t grow;   // row inside the buffers (C, scale_a)
+  __half sa;
+};
+
+// Everything that does not depend on the accumulator: fetched before waiting for it.  `row` is the
+// row inside the problem this thread owns; `sbw` is this warp's 256-entry staging area for the
+// per-channel scales of the tile.
+__device__ __forceinline__ EpiCtx epi_prefetch(const GGProblemDev* pr, const Sched* sc, const Tile& ti, int row,
+                                               int lane, __half* sbw) {
+  EpiCtx c;
+  c.N         = pr->N;
+  c.ldc       = pr->ldc;
+  c.out_mode  = pr->out_mode;
+  c.n_col0    = ti.n_tile * kBN;
+  c.valid     = row < sc->m_eff[ti.p];
+  c.grow      = (int64_t)sc->row0[ti.p] + row;
+  c.is_int    = (ti.scheme == SCH_W8A8 || ti.scheme == SCH_W4A4);
+  c.acc_shift = (ti.scheme == SCH_W4A4) ? 8 : 0;   // 4-bit codes ride in the high nibble of each byte
+  c.sa        = __float2half(0.f);
+  if (c.is_int && c.out_mode == OUT_FP16) {
+    const int n = c.n_col0 + lane * 8;
+    uint4 sv    = make_uint4(0, 0, 0, 0);
+    if (n < c.N) sv = __ldg(reinterpret_cast<const uint4*>(pr->scale_b + n));
+    if (c.valid) c.sa = pr->scale_a[c.grow * pr->sa_stride];
+    __syncwarp();
+    *reinterpret_cast<uint4*>(sbw + lane * 8) = sv;
+    __syncwarp();
+  }
+  return c;
+}
+
+// Drain 256 accumulator columns of this warp's 32 TMEM lanes (`taddr`: lane quarter and column base
+// already applied) and store the rows.
+__device__ __forceinline__ void epi_store(const EpiCtx& c, const GGProblemDev* pr, uint32_t taddr, const __half* sbw) {
+#pragma unroll 1
+  for (int ch = 0; ch < kBN / 32; ++ch) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + ch * 32, v);
+    tmem_ld_wait();
+    const int n0 = c.n_col0 + ch * 32;
+    if (!c.valid || n0 >= c.N) continue;
+    if (c.out_mode == OUT_ACC) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(pr->C) + c.grow * c.ldc + n0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (n0 + j * 4 < c.N) {
+          uint4 o;
+          if (c.is_int) {
+            o.x = (uint32_t)((int)v[4 * j + 0] >> c.acc_shift);
+            o.y = (uint32_t)((int)v[4 * j + 1] >> c.acc_shift);
+            o.z = (uint32_t)((int)v[4 * j + 2] >> c.acc_shift);
+            o.w = (uint32_t)((int)v[4 * j + 3] >> c.acc_shift);
+          } else {
+            o = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
+          *reinterpret_cast<uint4*>(dst + j * 4) = o;
+        }
+      }
+    } else {
+      __half* dst = reinterpret_cast<__half*>(pr->C) + c.grow * c.ldc + n0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (n0 + j * 8 < c.N) {
+          uint32_t o[4];
+          if (c.is_int) {
+            // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
+            const uint4 sbv   = *reinterpret_cast<const uint4*>(sbw + ch * 32 + j * 8);
+            const __half2* s2 = reinterpret_cast<const __half2*>(&sbv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float p0 = __half2float(__hmul(c.sa, __low2half(s2[e])));
+              const float p1 = __half2float(__hmul(c.sa, __high2half(s2[e])));
+              const float f0 = (float)((int)v[8 * j + 2 * e] >> c.acc_shift) * p0;
+              const float f1 = (float)((int)v[8 * j + 2 * e + 1] >> c.acc_shift) * p1;
+              __half2 h      = __floats2half2_rn(f0, f1);
+              o[e]           = *reinterpret_cast<uint32_t*>(&h);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __half2 h = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+              o[e]      = *reinterpret_cast<uint32_t*>(&h);
+            }
+          }
+          *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace ggc
+}  // namespace mxb

@@ -62,8 +62,13 @@ static_assert(sizeof(GGStatus) == 256, "GGStatus layout");
 constexpr int kDevErrTimeout = 1;   // a bounded wait ran out
 constexpr int kDevErrTooMany = 2;   // more problems than kMaxProblems
 
-void gg_launch_kernel(const GGProblemDev* problems, int count, GGStatus* status, bool needs_cvt, int num_ctas,
+// single-CTA kernel (gg_kernel.cu): tiles of 128 x 256, any number of CTAs
+void gg_launch_single(const GGProblemDev* problems, int count, GGStatus* status, bool needs_cvt, int num_ctas,
                       cudaStream_t stream);
-cudaError_t gg_configure_kernels();
+cudaError_t gg_configure_single();
+// CTA-pair kernel (gg_pair_kernel.cu): tiles of 256 x 256 on clusters of two CTAs; num_ctas must be even
+cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* status, bool needs_cvt, int num_ctas,
+                           cudaStream_t stream);
+cudaError_t gg_configure_pair();
 
 }  // namespace mxb

@@ -17,6 +17,15 @@ pytestmark = pytest.mark.gpu
 
 REL_L2 = 1e-3
 
+
+@pytest.fixture(autouse=True, params=["pair", "single"])
+def gg_kernel(request):
+    """Every test of this file runs once per kernel: CTA pairs (256 x 256 tiles, cta_group::2) and
+    single CTAs (128 x 256 tiles)."""
+    util.DEFAULT_CTAS = 0 if request.param == "pair" else 1 << 20
+    yield request.param
+    util.DEFAULT_CTAS = 0
+
 # (M, N, K): one tile / one k-block; ragged M; ragged N tile; several k-blocks; layer shapes
 SHAPES_INT = [(128, 256, 128), (1, 256, 128), (17, 256, 256), (129, 512, 384), (300, 2816, 2048), (77, 2048, 1408),
               (256, 264, 128)]
@@ -103,11 +112,11 @@ def test_mixed_schemes_one_launch(cuda_device):
             assert og.rel_l2(got, c.ref) <= REL_L2
 
 
-@pytest.mark.parametrize("num_ctas", [1, 2, 3, 7])
+@pytest.mark.parametrize("num_ctas", [1, 2, 3, 7, -2, -4, -6])
 def test_few_ctas_walk_many_tiles_of_alternating_schemes(cuda_device, num_ctas):
     """With a handful of CTAs every CTA processes a long sequence of tiles whose schemes alternate
     (direct / converted, int / float): ring positions, barrier parities and TMEM buffers must stay
-    consistent across every kind of transition."""
+    consistent across every kind of transition.  Negative counts select the CTA-pair kernel."""
     rng = np.random.default_rng(100 + num_ctas)
     cases = [util.WxAxCase(rng, 300, 512, 384, 8), util.WxAxCase(rng, 200, 768, 256, 4),
              util.Fp16Case(rng, 140, 512, 192), util.WxAxCase(rng, 129, 256, 640, 8),

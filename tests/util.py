@@ -92,8 +92,13 @@ class W4A16Case:
                           scale_b=self.SB, out_mode=out_mode)
 
 
-def run(problems, num_ctas=0):
+# launch geometry used when a test does not ask for one: 0 = library default (CTA-pair kernel on every
+# SM), a large positive number = single-CTA kernel on every SM.  tests/test_gpu_gemm.py runs with both.
+DEFAULT_CTAS = 0
+
+
+def run(problems, num_ctas=None):
     g = gg.GroupedGemm(problems)
-    g.run(num_ctas)
+    g.run(DEFAULT_CTAS if num_ctas is None else num_ctas)
     g.check()
     return g
