@@ -184,6 +184,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -230,15 +231,36 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step_resident():
+    use_graph = world == 1 and not args.no_graph
+
+    def step_eager():
         return layer.forward(hidden, ids_d, wts_d)
+
+    def step_resident():
+        # one CUDA-graph replay per step on a single GPU (the step never returns to the host);
+        # the expert-parallel step needs its split sizes on the host and runs eagerly
+        return layer.forward_graph(hidden, ids_d, wts_d) if use_graph else step_eager()
 
     # ---- warm-up, correctness guard
     for _ in range(args.warmup):
         step_resident()
     layer.check()
 
-    # ---- per-launch timing of the dominant kernel (grouped GEMM), events on the launching stream
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.steps):
+        step_resident()
+    t1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_total = t0.elapsed_time(t1)
+    layer.check()
+
+    # ---- per-launch timing of the dominant kernel (grouped GEMM): the same steps launched eagerly, with
+    # CUDA events on the launching stream around the two GEMM launches of every step
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     if world == 1:
         core = layer._core
@@ -253,38 +275,29 @@ def main():
             e = ev[state["i"]]
             e[2].record(); gg2_run(); e[3].record()
         core.gg1.run, core.gg2.run = timed_gg1, timed_gg2
-
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(args.steps):
-        if world == 1:
+        for i in range(args.steps):
             state["i"] = i
-        step_resident()
-    t1.record()
-    barrier()
-    clocks = sampler.stop()
-    ms_total = t0.elapsed_time(t1)
-    layer.check()
-    if world == 1:
+            step_eager()
+        torch.cuda.synchronize()
         core.gg1.run, core.gg2.run = gg1_run, gg2_run
 
     # ---- end-to-end through the public API with host buffers (H2D of inputs + D2H of the result inside)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = max(3, min(args.steps, 50))
+    def step_e2e():
+        # host -> device copies of this step's inputs into the layer's input buffers, the step, and the
+        # device -> host copy of its result, all on the timed stream
+        hidden.copy_(hidden_host, non_blocking=True)
+        ids_d.copy_(ids_host, non_blocking=True)
+        wts_d.copy_(wts_host, non_blocking=True)
+        out_host.copy_(step_resident(), non_blocking=True)
     for _ in range(2):
-        out_host.copy_(layer.forward(hidden_host.to(dev, non_blocking=True), ids_host.to(dev, non_blocking=True),
-                                     wts_host.to(dev, non_blocking=True)), non_blocking=True)
+        step_e2e()
     barrier()
     e0.record()
     for _ in range(e2e_steps):
-        h = hidden_host.to(dev, non_blocking=True)
-        i_ = ids_host.to(dev, non_blocking=True)
-        w_ = wts_host.to(dev, non_blocking=True)
-        out_host.copy_(layer.forward(h, i_, w_), non_blocking=True)
+        step_e2e()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
@@ -310,7 +323,8 @@ def main():
         "config": {"workload": spec.name, "tokens_per_gpu": T, "experts": spec.num_experts, "topk": spec.topk,
                    "hidden": spec.hidden, "inter": spec.inter, "shared_inter": spec.shared_inter,
                    "scheme": spec.scheme, "parallelism": f"ep{world}" if world > 1 else "single",
-                   "l2": "operands+outputs per step (>700 MB) exceed the 126 MB L2; no explicit flush"},
+                   "l2": "operands+outputs per step (>700 MB) exceed the 126 MB L2; no explicit flush",
+                   "launch": "cuda-graph replay" if use_graph else "eager"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hidden_host.numel() * 2 + ids_host.numel() * 4 + wts_host.numel() * 4,
                 "d2h_bytes_per_step": out_host.numel() * 2, "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},

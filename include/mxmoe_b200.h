@@ -73,7 +73,8 @@ typedef struct mxmoe_gg_problem {
   int32_t out_mode;
   int32_t lda_bytes; /* row pitch of A in bytes; 0 = dense rows.  A multiple of 16. */
   int32_t sa_stride; /* distance between consecutive per-token scales in fp16 elements; 0 or 1 = contiguous */
-  int32_t reserved_;
+  int32_t a_expanded; /* w4a4 only: A holds one byte per code, the byte 16*q, in the order the kernel's own
+                         int4 -> int8 unpacking produces (see mxmoe_token_quant_args.q4x); A is then [M, K] bytes */
 } mxmoe_gg_problem;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -94,7 +95,7 @@ size_t mxmoe_gg_workspace_bytes(int problem_count);
 /* Host-side record of what mxmoe_gg_prepare put into a workspace. */
 typedef struct mxmoe_gg_plan {
   int32_t count;     /* problems kept (empty ones are dropped) */
-  int32_t needs_cvt; /* 1 if any problem has 4-bit operands (selects the kernel variant) */
+  int32_t needs_cvt; /* kernel variant: 0 no 4-bit operand, 1 4-bit weights only, 2 packed 4-bit activations too */
 } mxmoe_gg_plan;
 
 /* Validate the problem list, encode the TMA descriptors on the host and copy the
@@ -105,9 +106,9 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
                      void* stream, mxmoe_gg_plan* plan);
 
 /* Launch the persistent kernel over a prepared workspace; may be called any number of times after
- * one prepare.  `num_ctas` == 0: the default kernel on every SM (CTA pairs, tcgen05 cta_group::2,
- * 256 x 256 tiles; environment MXMOE_GG_KERNEL=single selects the single-CTA kernel instead);
- * > 0: the single-CTA kernel (128 x 256 tiles) with that many CTAs; < 0: the CTA-pair kernel with
+ * one prepare.  `num_ctas` == 0: the default kernel on every SM (single CTAs, 128 x 256 tiles;
+ * environment MXMOE_GG_KERNEL=pair selects the CTA-pair kernel instead); > 0: the single-CTA kernel
+ * with that many CTAs; < 0: the CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles) with
  * -num_ctas CTAs (rounded down to even).  All choices give identical results. */
 int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream);
 
@@ -118,6 +119,13 @@ int mxmoe_gg_launch(const mxmoe_gg_problem* problems, int problem_count, void* w
 /* Synchronise `stream` and read the device status block of the workspace:
  * MXMOE_OK, or MXMOE_ERR_DEVICE with the detail in mxmoe_last_error(). */
 int mxmoe_gg_check(void* workspace, void* stream);
+
+/* Built-in tracing: cycle counters (clock64 deltas) that CTA 0 recorded during the last launch over
+ * `workspace`.  counters[16]: 0 kernel body, 1 producer waiting for a free stage, 2 MMA issuer waiting
+ * for operands, 3 MMA issuer waiting for a drained accumulator, 4 MMA issue, 5 epilogue waiting,
+ * 6 epilogue draining + storing, 7 converter waiting, 8 converter working, 9 tiles, 10 stages.
+ * Synchronises `stream`. */
+int mxmoe_gg_profile(void* workspace, uint64_t* counters, void* stream);
 
 /* Drop-in for the reference's function-pointer ABI `mxmoe::FuncType`
  * (mxmoe/kernels/src/include/registry.cuh:28-39): device arrays of device
@@ -135,7 +143,8 @@ int mxmoe_groupgemm_hz_fused(void** ptr_As, void** ptr_Bs, void** ptr_scale_a, v
  * routed rows, rows [rows_routed, rows_total) belong to the shared expert
  * (pseudo-expert `num_experts`).  The four per-expert device tables are the ones
  * the reference builds on the host at mxmoe/kernels/src/ref_bind.cu:475-505:
- * quantisation tag (0 fp16 copy, 1 int8 per token, 2 int4 per token), first row,
+ * quantisation tag (0 fp16 copy, 1 int8 per token, 2 int4 per token, 3 int4 per token expanded to
+ * one byte 16*q per code - an internal format of this library), first row,
  * write offset of the packed rows and of the scales (both in fp16 elements).
  * Record layout (rec_stride > 0): the three offset tables are not read; row r is written to
  * q_store + r * rec_stride whatever its format, and its scale to the same record at
@@ -179,7 +188,9 @@ typedef struct mxmoe_token_quant_args {
   void* q8;            /* int8 rows [T, k/2] uint16 words */
   void* s8;            /* fp16 [T] */
   void* q4;            /* int4 rows [T, k/4] uint16 words */
-  void* s4;            /* fp16 [T] */
+  void* s4;            /* fp16 [T], shared by q4 and q4x */
+  void* q4x;           /* int4 rows expanded to one byte 16*q per code, [T, k] bytes: the a_expanded operand
+                          format of the grouped GEMM (tag 3 in exp_qtag); needs k % 32 == 0 */
   const int8_t* signs; /* optional +-1 diagonal, length k */
   int32_t k;
   int32_t num_tokens;

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libmxmoe_b200.so")
 # every symbol include/mxmoe_b200.h declares
 EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
-    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_launch", "mxmoe_gg_check",
+    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows",
     "mxmoe_silu_mul_then_quant",
     "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
@@ -41,7 +41,7 @@ class GGProblem(C.Structure):
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
         ("a_rows", C.c_int32), ("row0", C.c_int32), ("ldc", C.c_int32),
         ("q", QParams), ("out_mode", C.c_int32), ("lda_bytes", C.c_int32), ("sa_stride", C.c_int32),
-        ("reserved_", C.c_int32),
+        ("a_expanded", C.c_int32),
     ]
 
 
@@ -63,7 +63,7 @@ class ActArgs(C.Structure):
 class TokenQuantArgs(C.Structure):
     _fields_ = [
         ("inp", C.c_void_p), ("f16", C.c_void_p), ("q8", C.c_void_p), ("s8", C.c_void_p), ("q4", C.c_void_p),
-        ("s4", C.c_void_p), ("signs", C.c_void_p),
+        ("s4", C.c_void_p), ("q4x", C.c_void_p), ("signs", C.c_void_p),
         ("k", C.c_int32), ("num_tokens", C.c_int32), ("rotate", C.c_int32), ("reserved_", C.c_int32),
     ]
 
@@ -96,6 +96,7 @@ def lib() -> C.CDLL:
         l.mxmoe_gg_run.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         l.mxmoe_gg_launch.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
         l.mxmoe_gg_check.argtypes = [C.c_void_p, C.c_void_p]
+        l.mxmoe_gg_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_groupgemm_hz_fused.argtypes = [C.c_void_p] * 14 + [C.c_int]
         l.mxmoe_quant_act.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_silu_mul_then_quant.argtypes = [C.c_void_p, C.c_void_p]

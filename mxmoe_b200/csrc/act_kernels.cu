@@ -33,7 +33,7 @@ constexpr int kBlock = 256;  // 8 warps
 constexpr int kJ     = 8;    // 16-byte chunks per lane (8 values each)
 
 struct RowInfo {
-  int tag;          // 0 copy fp16, 1 int8 per token, 2 int4 per token
+  int tag;          // 0 copy fp16, 1 int8 per token, 2 int4 per token, 3 int4 per token expanded to bytes
   int k;            // logical row length
   __half* q_dst;    // where the packed row goes
   __half* s_dst;    // where the scale goes (may be null for tag 0)
@@ -51,7 +51,7 @@ __device__ __forceinline__ RowInfo locate_row(const ActArgs& a, int row) {
     return r;
   }
   const int local = row - a.exp_row_start[e];
-  const int pack  = r.tag == 0 ? 1 : (r.tag == 1 ? 2 : 4);
+  const int pack  = r.tag == 0 ? 1 : (r.tag == 2 ? 4 : 2);
   // without explicit offset tables every row owns one fp16-sized slot of `k` halfs: expert e's
   // packed rows start at slot exp_row_start[e] and are stored back to back at their own pitch
   const int64_t q0 = a.exp_q_off ? (int64_t)a.exp_q_off[e] : (int64_t)a.exp_row_start[e] * a.k;
@@ -197,7 +197,7 @@ struct RowQuant {
   float qmax, sc, rcp;
   __half sc_h;
   __device__ __forceinline__ RowQuant(float amax, int tag) {
-    qmax = tag == 1 ? 127.f : 7.f;
+    qmax = tag == 1 ? 127.f : 7.f;   // tags 2 and 3 are both 4-bit
     sc_h = __float2half_rn(__fdiv_rn(amax, qmax));
     sc   = __half2float(sc_h);
     rcp  = sc != 0.f ? __frcp_rn(sc) : 0.f;
@@ -228,11 +228,21 @@ __device__ __forceinline__ void store_codes(__half* q_dst, int ci, int tag, cons
                         ((uint32_t)(code[2] & 0xf) << 4) | (uint32_t)(code[3] & 0xf);
     const uint32_t w1 = ((uint32_t)(code[4] & 0xf) << 12) | ((uint32_t)(code[5] & 0xf) << 8) |
                         ((uint32_t)(code[6] & 0xf) << 4) | (uint32_t)(code[7] & 0xf);
-    reinterpret_cast<uint32_t*>(q_dst)[ci] = w0 | (w1 << 16);
+    const uint32_t w  = w0 | (w1 << 16);
+    if (tag == 2) {
+      reinterpret_cast<uint32_t*>(q_dst)[ci] = w;
+    } else {
+      // tag 3: the bytes the GEMM's own int4 -> int8 unpacking would produce from the packed row: every
+      // 16 packed bytes become 16 bytes of high nibbles then 16 bytes of low nibbles, each nibble moved
+      // to the top of its byte (the byte 16*q).  These 4 packed bytes are bytes 4*(ci%4).. of chunk ci/4.
+      uint32_t* d = reinterpret_cast<uint32_t*>(q_dst) + 8 * (ci >> 2) + (ci & 3);
+      d[0] = w & 0xF0F0F0F0u;
+      d[4] = (w << 4) & 0xF0F0F0F0u;
+    }
   }
 }
 
-// write one row in format `tag` (0 fp16 copy, 1 int8, 2 int4) to q_dst / s_dst
+// write one row in format `tag` (0 fp16 copy, 1 int8, 2 int4 packed, 3 int4 expanded) to q_dst / s_dst
 template <int kWarps>
 __device__ __forceinline__ void emit_row(const float (&x)[kJ][8], float amax, int tag, __half* q_dst, __half* s_dst,
                                          int nchunk, int w, int lane) {
@@ -327,6 +337,7 @@ __global__ void __launch_bounds__(kBlock) quant_tokens_kernel(TokenQuantArgs a) 
   if (a.f16) emit_row<kWarps>(x, amax, 0, a.f16 + (int64_t)tok * a.k, nullptr, nchunk, w, lane);
   if (a.q8) emit_row<kWarps>(x, amax, 1, a.q8 + (int64_t)tok * (a.k / 2), a.s8 + tok, nchunk, w, lane);
   if (a.q4) emit_row<kWarps>(x, amax, 2, a.q4 + (int64_t)tok * (a.k / 4), a.s4 + tok, nchunk, w, lane);
+  if (a.q4x) emit_row<kWarps>(x, amax, 3, a.q4x + (int64_t)tok * (a.k / 2), a.s4 + tok, nchunk, w, lane);
 }
 
 // copy every routed (and shared-expert) row from the token-major store of its expert's format into
@@ -337,8 +348,8 @@ __global__ void __launch_bounds__(kBlock) gather_rows_kernel(ActArgs a, TokenQua
   if (row >= a.rows_total) return;
   const RowInfo ri  = locate_row(a, row);
   const int64_t tok = row < a.rows_routed ? a.row_token[row] : (int64_t)(row - a.rows_routed);
-  const int pack    = ri.tag == 0 ? 1 : (ri.tag == 1 ? 2 : 4);
-  const __half* src = ri.tag == 0 ? (t.f16 ? t.f16 : t.in) : (ri.tag == 1 ? t.q8 : t.q4);
+  const int pack    = ri.tag == 0 ? 1 : (ri.tag == 2 ? 4 : 2);
+  const __half* src = ri.tag == 0 ? (t.f16 ? t.f16 : t.in) : (ri.tag == 1 ? t.q8 : (ri.tag == 2 ? t.q4 : t.q4x));
   const uint4* s = reinterpret_cast<const uint4*>(src + tok * (a.k / pack));
   uint4* d       = reinterpret_cast<uint4*>(ri.q_dst);
   const int n16  = (a.k / pack) >> 3;

@@ -18,7 +18,7 @@ struct ActArgs {
   __half* s_store;           // per-token scales
   const int* row_expert;     // [rows_routed] expert of each sorted row
   const int64_t* row_token;  // [rows_routed] source token of each sorted row (quant_act only)
-  const int* exp_qtag;       // 0 fp16 copy, 1 int8/token, 2 int4/token
+  const int* exp_qtag;       // 0 fp16 copy, 1 int8/token, 2 int4/token packed, 3 int4/token expanded to bytes
   const int* exp_row_start;  // first row of each expert
   const int* exp_q_off;      // write offset into q_store (halfs)
   const int* exp_s_off;      // write offset into s_store (halfs)
@@ -40,7 +40,8 @@ struct TokenQuantArgs {
   __half* q8;           // int8 rows  [T, k/2] uint16 words
   __half* s8;           // [T]
   __half* q4;           // int4 rows  [T, k/4] uint16 words
-  __half* s4;           // [T]
+  __half* s4;           // [T]  (shared by q4 and q4x)
+  __half* q4x;          // int4 rows expanded to one byte 16*q per code [T, k/2] (the GEMM's a_expanded format)
   const int8_t* signs;  // optional +-1 diagonal, length k
   int k;
   int num_tokens;

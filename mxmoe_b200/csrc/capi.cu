@@ -114,6 +114,10 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   int scheme = 0;
   int rc     = scheme_of(p.q, &scheme);
   if (rc) return rc;
+  if (p.a_expanded) {
+    if (scheme != mxb::SCH_W4A4) return fail(MXMOE_ERR_INVALID, "problem %d: a_expanded is only defined for w4a4", idx);
+    scheme = mxb::SCH_W4A4_XA;
+  }
   if (!p.A || !p.B || !p.C) return fail(MXMOE_ERR_INVALID, "problem %d: null A/B/C pointer", idx);
   if (p.M < 0 || p.N <= 0 || p.K <= 0) return fail(MXMOE_ERR_INVALID, "problem %d: bad shape M=%d N=%d K=%d", idx, p.M, p.N, p.K);
   if (p.N % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: N=%d must be a multiple of 8", idx, p.N);
@@ -121,7 +125,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   const int ldc = p.ldc > 0 ? p.ldc : p.N;
   if (ldc < p.N || ldc % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: ldc=%d must be >= N and a multiple of 8", idx, ldc);
   if ((reinterpret_cast<uintptr_t>(p.C) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: C is not 16-byte aligned", idx);
-  const bool wxax = scheme == mxb::SCH_W8A8 || scheme == mxb::SCH_W4A4;
+  const bool wxax = scheme == mxb::SCH_W8A8 || scheme == mxb::SCH_W4A4 || scheme == mxb::SCH_W4A4_XA;
   if (wxax && p.out_mode == mxb::OUT_FP16) {
     if (!p.scale_a || !p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w%da%d needs scale_a and scale_b", idx, p.q.w_bits, p.q.a_bits);
     if ((reinterpret_cast<uintptr_t>(p.scale_b) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 16-byte aligned", idx);
@@ -146,6 +150,11 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
     case mxb::SCH_W4A4:
       if (p.K % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a4 needs K %% 32 == 0 (K=%d)", idx, p.K);
       if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, a_rows, 64, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx, lda))) return rc;
+      if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN / 2, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W4A4_XA:
+      if (p.K % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a4 needs K %% 32 == 0 (K=%d)", idx, p.K);
+      if ((rc = encode_2d(enc, &d->tmA, p.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, a_rows, 128, mxb::kBM, CU_TENSOR_MAP_SWIZZLE_128B, "A", idx, lda))) return rc;
       if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN / 2, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
       break;
     case mxb::SCH_W4A16G128:
@@ -174,12 +183,12 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   return MXMOE_OK;
 }
 
-// MXMOE_GG_KERNEL=single|pair overrides which kernel a launch with num_ctas == 0 uses
+// which kernel a launch with num_ctas == 0 uses: the single-CTA kernel unless MXMOE_GG_KERNEL=pair
 bool default_pair() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("MXMOE_GG_KERNEL");
-    v = (e && !strcmp(e, "single")) ? 0 : 1;
+    v = (e && !strcmp(e, "pair")) ? 1 : 0;
   }
   return v == 1;
 }
@@ -228,7 +237,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
     rc = build_problem(st->encode, problems[i], i, dev + kept);
     if (rc) return rc;
-    if (dev[kept].scheme == mxb::SCH_W4A4 || dev[kept].scheme == mxb::SCH_W4A16G128) needs_cvt = 1;
+    if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
+    else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
     ++kept;
   }
   status->count     = kept;
@@ -260,8 +270,8 @@ int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void*
   int n     = num_ctas < 0 ? -num_ctas : num_ctas;
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
   if (pair && n < 2) pair = false;
-  if (pair) CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt != 0, n & ~1, cs));
-  else      mxb::gg_launch_single(probs, count, status, needs_cvt != 0, n, cs);
+  if (pair) CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
+  else      mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
   CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;
 }
@@ -286,6 +296,15 @@ int mxmoe_gg_check(void* workspace, void* stream) {
                 words[0] == mxb::kDevErrTimeout ? "bounded wait ran out" : "too many problems",
                 role < 7 ? roles[role] : "?", words[1] & 0xffffff);
   }
+  return MXMOE_OK;
+}
+
+int mxmoe_gg_profile(void* workspace, uint64_t* counters, void* stream) {
+  if (!workspace || !counters) return fail(MXMOE_ERR_INVALID, "null argument");
+  mxb::GGStatus h;
+  CUDA_TRY(cudaMemcpyAsync(&h, workspace, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  for (int i = 0; i < 16; ++i) counters[i] = h.prof[i];
   return MXMOE_OK;
 }
 
@@ -386,7 +405,8 @@ static int to_token_args(const mxmoe_token_quant_args* t, mxb::TokenQuantArgs* o
   if (!t->in) return fail(MXMOE_ERR_INVALID, "null input");
   if (t->k <= 0 || t->k % 8 || t->k > 16384) return fail(MXMOE_ERR_INVALID, "row length must be a multiple of 8 in (0, 16384] (k=%d)", t->k);
   if (t->num_tokens < 0) return fail(MXMOE_ERR_INVALID, "negative token count");
-  if ((t->q8 && !t->s8) || (t->q4 && !t->s4)) return fail(MXMOE_ERR_INVALID, "a packed store needs its scale store");
+  if (t->q4x && t->k % 32) return fail(MXMOE_ERR_INVALID, "the expanded 4-bit format needs k %% 32 == 0 (k=%d)", t->k);
+  if ((t->q8 && !t->s8) || ((t->q4 || t->q4x) && !t->s4)) return fail(MXMOE_ERR_INVALID, "a packed store needs its scale store");
   if (t->rotate && ((t->k & (t->k - 1)) != 0 || t->k < 256)) return fail(MXMOE_ERR_UNSUPPORTED, "rotation needs a power-of-two row length >= 256 (k=%d)", t->k);
   o->in = static_cast<const __half*>(t->in);
   o->f16 = static_cast<__half*>(t->f16);
@@ -394,6 +414,7 @@ static int to_token_args(const mxmoe_token_quant_args* t, mxb::TokenQuantArgs* o
   o->s8 = static_cast<__half*>(t->s8);
   o->q4 = static_cast<__half*>(t->q4);
   o->s4 = static_cast<__half*>(t->s4);
+  o->q4x = static_cast<__half*>(t->q4x);
   o->signs = t->signs;
   o->k = t->k;
   o->num_tokens = t->num_tokens;

@@ -51,7 +51,7 @@ __device__ __forceinline__ void build_sched(Sched* sc, const GGProblemDev* probl
     if (pr.m_dev) m = min(max(*pr.m_dev, 0), pr.M);
     const int r0     = pr.row0_dev ? *pr.row0_dev : pr.row0;
     const int nt     = (pr.N + kBN - 1) / kBN;
-    const int kelems = (pr.scheme == SCH_W8A8 || pr.scheme == SCH_W4A4) ? 128 : 64;
+    const int kelems = (pr.scheme == SCH_FP16 || pr.scheme == SCH_W4A16G128) ? 64 : 128;
     const int nkb    = (pr.K + kelems - 1) / kelems;
     sc->tile_end[p] = ((m + rows_per_tile - 1) / rows_per_tile) * nt;
     sc->m_eff[p]    = m;
@@ -120,12 +120,13 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t w, int nib, __half2 s2
 // w4a4: `rows` packed rows of 64 bytes (128 two's-complement nibbles) at `src` -> rows of 128 int8
 // bytes at `dst` in the 128-byte-swizzled operand layout.  Code q becomes the byte 16*q: both
 // operands carry the factor, the accumulator is 256x the true one and is shifted back in the
-// epilogue.  128 threads, `ct` = thread index in the converter group.
+// epilogue.  `ct` = thread index in the converter group of kCvtThreads threads.
+template <int kCvtThreads>
 __device__ __forceinline__ void convert_w4a4(uint32_t src, uint32_t dst, int rows, int ct) {
-  const int iters = rows >> 5;   // rows * 4 chunks / 128 threads
+  const int iters = rows * 4 / kCvtThreads;
 #pragma unroll 4
   for (int i = 0; i < iters; ++i) {
-    const int g   = i * 128 + ct;
+    const int g   = i * kCvtThreads + ct;
     const int row = g >> 2;
     const int c   = g & 3;
     const uint4 w = lds128(src + row * 64 + c * 16);
@@ -144,36 +145,34 @@ __device__ __forceinline__ void convert_w4a4(uint32_t src, uint32_t dst, int row
 // w4a16 group-128: which part of the packed weight tile a converter thread owns.  A packed row holds
 // 8 interleaved n-rows x 64 k as 8 chunks of 16 bytes; chunk 2*kb16 + fh carries, for the 16-k block
 // kb16, the rows n_lo = 32*(prow/8) + 16*fh + prow%8 (nibbles 0,1) and n_lo + 8 (nibbles 2,3).
-template <int kPackedRows>   // 64: a 256-row B tile; 32: one CTA's 128-row half
+template <int kPackedRows, int kCvtThreads>   // packed rows: 64 = a 256-row B tile, 32 = one CTA's 128-row half
 struct W4A16Lane {
+  static constexpr int kGroups = kCvtThreads / (2 * kPackedRows);   // thread groups that split the four 16-k blocks
+  static constexpr int kIters  = 4 / kGroups;
+  static_assert(kGroups >= 1 && kGroups <= 4 && kIters * kGroups == 4, "unsupported converter geometry");
   int prow, fh, r, n_lo, kb0;
-  static constexpr int kIters = kPackedRows == 64 ? 4 : 2;
   __device__ __forceinline__ explicit W4A16Lane(int ct) {
-    if (kPackedRows == 64) {
-      prow = ct >> 1; fh = ct & 1; kb0 = 0;
-    } else {
-      const int c2 = ct & 63;
-      prow = c2 >> 1; fh = c2 & 1; kb0 = 2 * (ct >> 6);
-    }
+    const int c2 = ct % (2 * kPackedRows);
+    prow = c2 >> 1;
+    fh   = c2 & 1;
+    kb0  = (ct / (2 * kPackedRows)) * kIters;
     r    = prow & 7;
     n_lo = 32 * (prow >> 3) + 16 * fh + r;
   }
   // 16-k block handled in iteration i (rotated per row so that neighbouring threads hit different banks)
-  __device__ __forceinline__ int kb16(int i) const {
-    return kPackedRows == 64 ? ((prow + i) & 3) : (kb0 + ((prow + i) & 1));
-  }
+  __device__ __forceinline__ int kb16(int i) const { return kb0 + ((prow + i) % kIters); }
 };
 
-template <int kPackedRows>
-__device__ __forceinline__ void convert_w4a16(const W4A16Lane<kPackedRows>& ln, uint32_t raw_b, uint32_t op_b,
-                                              __half2 sz_lo, __half2 sz_hi) {
+template <int kPackedRows, int kCvtThreads>
+__device__ __forceinline__ void convert_w4a16(const W4A16Lane<kPackedRows, kCvtThreads>& ln, uint32_t raw_b,
+                                              uint32_t op_b, __half2 sz_lo, __half2 sz_hi) {
   const uint32_t src = raw_b + ln.prow * 128;
   const uint32_t dlo = op_b + ln.n_lo * 128;
   const uint32_t dhi = dlo + 8 * 128;
   const __half2 s_lo = __half2half2(__low2half(sz_lo)), z_lo = __half2half2(__high2half(sz_lo));
   const __half2 s_hi = __half2half2(__low2half(sz_hi)), z_hi = __half2half2(__high2half(sz_hi));
 #pragma unroll
-  for (int i = 0; i < W4A16Lane<kPackedRows>::kIters; ++i) {
+  for (int i = 0; i < W4A16Lane<kPackedRows, kCvtThreads>::kIters; ++i) {
     const int kb16 = ln.kb16(i);
     const uint4 w  = lds128(src + (2 * kb16 + ln.fh) * 16);
 #pragma unroll
@@ -213,8 +212,8 @@ __device__ __forceinline__ EpiCtx epi_prefetch(const GGProblemDev* pr, const Sch
   c.n_col0    = ti.n_tile * kBN;
   c.valid     = row < sc->m_eff[ti.p];
   c.grow      = (int64_t)sc->row0[ti.p] + row;
-  c.is_int    = (ti.scheme == SCH_W8A8 || ti.scheme == SCH_W4A4);
-  c.acc_shift = (ti.scheme == SCH_W4A4) ? 8 : 0;   // 4-bit codes ride in the high nibble of each byte
+  c.is_int    = (ti.scheme != SCH_FP16 && ti.scheme != SCH_W4A16G128);
+  c.acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // 4-bit codes ride in the high nibble of each byte
   c.sa        = __float2half(0.f);
   if (c.is_int && c.out_mode == OUT_FP16) {
     const int n = c.n_col0 + lane * 8;
@@ -228,62 +227,138 @@ __device__ __forceinline__ EpiCtx epi_prefetch(const GGProblemDev* pr, const Sch
   return c;
 }
 
+// Convert and store 32 accumulator columns (one tcgen05.ld chunk) of this thread's row.
+__device__ __forceinline__ void epi_store_chunk(const EpiCtx& c, const GGProblemDev* pr, const uint32_t (&v)[32], int ch,
+                                                const __half* sbw) {
+  const int n0 = c.n_col0 + ch * 32;
+  if (!c.valid || n0 >= c.N) return;
+  if (c.out_mode == OUT_ACC) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(pr->C) + c.grow * c.ldc + n0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (n0 + j * 4 < c.N) {
+        uint4 o;
+        if (c.is_int) {
+          o.x = (uint32_t)((int)v[4 * j + 0] >> c.acc_shift);
+          o.y = (uint32_t)((int)v[4 * j + 1] >> c.acc_shift);
+          o.z = (uint32_t)((int)v[4 * j + 2] >> c.acc_shift);
+          o.w = (uint32_t)((int)v[4 * j + 3] >> c.acc_shift);
+        } else {
+          o = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        *reinterpret_cast<uint4*>(dst + j * 4) = o;
+      }
+    }
+    return;
+  }
+  __half* dst        = reinterpret_cast<__half*>(pr->C) + c.grow * c.ldc + n0;
+  const __half2 sa2  = __half2half2(c.sa);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (n0 + j * 8 < c.N) {
+      uint32_t o[4];
+      if (c.is_int) {
+        // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
+        const uint4 sbv   = *reinterpret_cast<const uint4*>(sbw + ch * 32 + j * 8);
+        const __half2* s2 = reinterpret_cast<const __half2*>(&sbv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 p = __half22float2(__hmul2(sa2, s2[e]));     // two fp16-rounded scale products
+          const float f0 = (float)((int)v[8 * j + 2 * e] >> c.acc_shift) * p.x;
+          const float f1 = (float)((int)v[8 * j + 2 * e + 1] >> c.acc_shift) * p.y;
+          __half2 h      = __floats2half2_rn(f0, f1);
+          o[e]           = *reinterpret_cast<uint32_t*>(&h);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __half2 h = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+          o[e]      = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 // Drain 256 accumulator columns of this warp's 32 TMEM lanes (`taddr`: lane quarter and column base
-// already applied) and store the rows.
+// already applied) and store the rows.  Two 32-column TMEM loads are in flight per wait.
 __device__ __forceinline__ void epi_store(const EpiCtx& c, const GGProblemDev* pr, uint32_t taddr, const __half* sbw) {
 #pragma unroll 1
-  for (int ch = 0; ch < kBN / 32; ++ch) {
-    uint32_t v[32];
-    tmem_ld_32x32(taddr + ch * 32, v);
+  for (int ch = 0; ch < kBN / 32; ch += 2) {
+    uint32_t v0[32], v1[32];
+    tmem_ld_32x32(taddr + ch * 32, v0);
+    tmem_ld_32x32(taddr + ch * 32 + 32, v1);
     tmem_ld_wait();
-    const int n0 = c.n_col0 + ch * 32;
-    if (!c.valid || n0 >= c.N) continue;
-    if (c.out_mode == OUT_ACC) {
-      uint32_t* dst = reinterpret_cast<uint32_t*>(pr->C) + c.grow * c.ldc + n0;
+    epi_store_chunk(c, pr, v0, ch, sbw);
+    epi_store_chunk(c, pr, v1, ch + 1, sbw);
+  }
+}
+
+// fp16 conversion of 32 accumulator columns of this thread's row into 4 x 16 bytes
+__device__ __forceinline__ void epi_convert_chunk(const EpiCtx& c, const uint32_t (&v)[32], int ch, const __half* sbw,
+                                                  uint4 (&out)[4]) {
+  const __half2 sa2 = __half2half2(c.sa);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (n0 + j * 4 < c.N) {
-          uint4 o;
-          if (c.is_int) {
-            o.x = (uint32_t)((int)v[4 * j + 0] >> c.acc_shift);
-            o.y = (uint32_t)((int)v[4 * j + 1] >> c.acc_shift);
-            o.z = (uint32_t)((int)v[4 * j + 2] >> c.acc_shift);
-            o.w = (uint32_t)((int)v[4 * j + 3] >> c.acc_shift);
-          } else {
-            o = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          }
-          *reinterpret_cast<uint4*>(dst + j * 4) = o;
-        }
+  for (int j = 0; j < 4; ++j) {
+    uint32_t o[4];
+    if (c.is_int) {
+      const uint4 sbv   = *reinterpret_cast<const uint4*>(sbw + ch * 32 + j * 8);
+      const __half2* s2 = reinterpret_cast<const __half2*>(&sbv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 p = __half22float2(__hmul2(sa2, s2[e]));
+        const float f0 = (float)((int)v[8 * j + 2 * e] >> c.acc_shift) * p.x;
+        const float f1 = (float)((int)v[8 * j + 2 * e + 1] >> c.acc_shift) * p.y;
+        __half2 h      = __floats2half2_rn(f0, f1);
+        o[e]           = *reinterpret_cast<uint32_t*>(&h);
       }
     } else {
-      __half* dst = reinterpret_cast<__half*>(pr->C) + c.grow * c.ldc + n0;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (n0 + j * 8 < c.N) {
-          uint32_t o[4];
-          if (c.is_int) {
-            // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
-            const uint4 sbv   = *reinterpret_cast<const uint4*>(sbw + ch * 32 + j * 8);
-            const __half2* s2 = reinterpret_cast<const __half2*>(&sbv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float p0 = __half2float(__hmul(c.sa, __low2half(s2[e])));
-              const float p1 = __half2float(__hmul(c.sa, __high2half(s2[e])));
-              const float f0 = (float)((int)v[8 * j + 2 * e] >> c.acc_shift) * p0;
-              const float f1 = (float)((int)v[8 * j + 2 * e + 1] >> c.acc_shift) * p1;
-              __half2 h      = __floats2half2_rn(f0, f1);
-              o[e]           = *reinterpret_cast<uint32_t*>(&h);
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __half2 h = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
-              o[e]      = *reinterpret_cast<uint32_t*>(&h);
-            }
-          }
-          *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
+      for (int e = 0; e < 4; ++e) {
+        __half2 h = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+        o[e]      = *reinterpret_cast<uint32_t*>(&h);
       }
+    }
+    out[j] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// Same result as epi_store for fp16 output, but rows are transposed through a 4 KiB per-warp
+// shared-memory buffer (`stg`, 32 rows x 128 bytes, 16-byte chunks XOR-swizzled by row) so that one
+// store instruction writes four full 128-byte lines instead of 16 bytes of 32 different rows.
+// `m_rows`: rows of the problem; `row_base`: problem row of this warp's lane 0.
+__device__ __forceinline__ void epi_store_staged(const EpiCtx& c, const GGProblemDev* pr, uint32_t taddr,
+                                                 const __half* sbw, uint32_t stg, int lane, int row_base, int m_rows) {
+  if (c.out_mode != OUT_FP16) {          // raw accumulators keep the direct path
+    epi_store(c, pr, taddr, sbw);
+    return;
+  }
+  const int64_t grow0 = c.grow - lane;   // buffer row of lane 0
+  __half* cbase = reinterpret_cast<__half*>(pr->C);
+#pragma unroll 1
+  for (int ch = 0; ch < kBN / 32; ch += 2) {
+    uint32_t v0[32], v1[32];
+    tmem_ld_32x32(taddr + ch * 32, v0);
+    tmem_ld_32x32(taddr + ch * 32 + 32, v1);
+    tmem_ld_wait();
+    uint4 o[4];
+    __syncwarp();                        // the previous round's reads of the buffer are done
+    epi_convert_chunk(c, v0, ch, sbw, o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sts128(stg + lane * 128 + ((j ^ (lane & 7)) << 4), o[j]);
+    epi_convert_chunk(c, v1, ch + 1, sbw, o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sts128(stg + lane * 128 + (((4 + j) ^ (lane & 7)) << 4), o[j]);
+    __syncwarp();
+    // 8 rounds: lanes 0-7 -> row 4i, lanes 8-15 -> row 4i+1, ...; lane%8 = 16-byte chunk of the 128-byte row
+    const int n0 = c.n_col0 + ch * 32 + (lane & 7) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r   = i * 4 + (lane >> 3);
+      const uint4 w = lds128(stg + r * 128 + (((lane & 7) ^ (r & 7)) << 4));
+      if (row_base + r < m_rows && n0 < c.N)
+        *reinterpret_cast<uint4*>(cbase + (grow0 + r) * c.ldc + n0) = w;
     }
   }
 }

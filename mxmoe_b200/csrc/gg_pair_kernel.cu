@@ -122,6 +122,7 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
   cluster_sync_all();                               // both CTAs' barriers exist before anyone signals them
   tc_fence_after_sync();
 
+  const long long prof_t0 = clock64();
   const uint32_t tmem_base = ctrl->tmem_base;
   const int total_tiles    = sc->total_tiles;
 
@@ -132,13 +133,19 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long w_prod = 0, n_stage = 0, n_tile = 0;
       for (int t = pair; ok && t < total_tiles; t += npairs) {
         const Tile ti          = find_tile(sc, count, t);
         const GGProblemDev* pr = problems + ti.p;
+        ++n_tile;
         const int a_row        = sc->row0[ti.p] + ti.m_tile * 2 * kHalf + rank * kHalf;
         const int b_row        = ti.n_tile * kBN + rank * kHalf;
         for (int kb = 0; kb < ti.nkb; ++kb) {
-          if (!wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag)) {
+          const long long c0 = clock64();
+          const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag);
+          w_prod += clock64() - c0;
+          ++n_stage;
+          if (!got) {
             preport(status, 1, t);
             ok = false;
             break;
@@ -150,6 +157,11 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
             if (rank == 0) mbar_expect_tx(full, 4 * kOpBytes);          // A + B halves of both CTAs
             tma_load_2d_pair(opA(stage), &pr->tmA, full, x, a_row);
             tma_load_2d_pair(opB(stage), &pr->tmB, full, x, b_row);
+          } else if (kCvt && ti.scheme == SCH_W4A4_XA) {
+            if (rank == 0) mbar_expect_tx(full, 2 * kOpBytes);          // expanded int8 A of both CTAs
+            tma_load_2d_pair(opA(stage), &pr->tmA, full, kb * 128, a_row);
+            mbar_expect_tx(rawf, kRawBytes);
+            tma_load_2d(rawB(stage), &pr->tmB, rawf, kb * 64, b_row);
           } else if (kCvt && ti.scheme == SCH_W4A4) {
             mbar_expect_tx(rawf, 2 * kRawBytes);
             tma_load_2d(rawA(stage), &pr->tmA, rawf, kb * 64, a_row);
@@ -163,6 +175,11 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      if (blockIdx.x == 0) {
+        status->prof[PROF_PROD_WAIT] = w_prod;
+        status->prof[PROF_TILES]     = n_tile;
+        status->prof[PROF_STAGES]    = n_stage;
+      }
     }
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only) =====
@@ -171,19 +188,24 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
       int acc = 0;
       uint32_t acc_phase = 0, full_parity = 0, cvt_parity = 0;
       bool ok = true;
+      long long w_oper = 0, w_acc = 0, w_issue = 0;
       for (int t = pair; ok && t < total_tiles; t += npairs) {
         const Tile ti = find_tile(sc, count, t);
-        if (!wait_bar(smem_u32(&ctrl->tempty[acc]), acc_phase ^ 1u, abort_flag)) {
+        const long long ca = clock64();
+        const bool gota = wait_bar(smem_u32(&ctrl->tempty[acc]), acc_phase ^ 1u, abort_flag);
+        w_acc += clock64() - ca;
+        if (!gota) {
           preport(status, 2, t);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        const bool is_int     = (ti.scheme == SCH_W8A8 || ti.scheme == SCH_W4A4);
-        const bool has_cvt    = kCvt && (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A16G128);
+        const bool is_int     = (ti.scheme != SCH_FP16 && ti.scheme != SCH_W4A16G128);
+        const bool has_cvt    = kCvt && (ti.scheme != SCH_FP16 && ti.scheme != SCH_W8A8);
         const bool has_full   = ti.scheme != SCH_W4A4;
         const uint32_t idesc  = is_int ? idesc_i8(2 * kHalf, kBN) : idesc_f16(2 * kHalf, kBN);
         for (int kb = 0; kb < ti.nkb; ++kb) {
+          const long long c0 = clock64();
           bool w = true;
           if (has_full) {
             w = wait_bar(smem_u32(&ctrl->full[stage]), (full_parity >> stage) & 1u, abort_flag);
@@ -198,6 +220,8 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
             ok = false;
             break;
           }
+          const long long c1 = clock64();
+          w_oper += c1 - c0;
           tc_fence_after_sync();
           const uint64_t adesc = smem_desc_sw128(opA(stage));
           const uint64_t bdesc = smem_desc_sw128(opB(stage));
@@ -208,12 +232,18 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
             else        mma_f16_ss2(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
           }
           mma_commit2(smem_u32(&ctrl->empty[stage]), 3);
+          w_issue += clock64() - c1;
           if (++stage == C::kStages) stage = 0;
         }
         if (!ok) break;
         mma_commit2(smem_u32(&ctrl->tfull[acc]), 3);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
+      if (blockIdx.x == 0) {
+        status->prof[PROF_MMA_WAIT_OPER] = w_oper;
+        status->prof[PROF_MMA_WAIT_ACC]  = w_acc;
+        status->prof[PROF_MMA_ISSUE]     = w_issue;
       }
     }
   } else if (warp < 6) {
@@ -222,22 +252,31 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
     int acc = 0;
     uint32_t acc_phase = 0;
     __half* sbw = ctrl->sb_stage[warp - 2];
+    long long w_epi = 0, w_store = 0;
     for (int t = pair; t < total_tiles; t += npairs) {
       const Tile ti          = find_tile(sc, count, t);
       const GGProblemDev* pr = problems + ti.p;
       const EpiCtx ec = epi_prefetch(pr, sc, ti, ti.m_tile * 2 * kHalf + rank * kHalf + q * 32 + lane, lane, sbw);
+      const long long c0 = clock64();
       bool ok = wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag);
       ok      = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) preport(status, 4, t);
         break;
       }
+      const long long c1 = clock64();
+      w_epi += c1 - c0;
       tc_fence_after_sync();
       epi_store(ec, pr, tmem_base + acc * kBN + ((uint32_t)(q * 32) << 16), sbw);
       tc_fence_before_sync();
       mbar_arrive_leader(smem_u32(&ctrl->tempty[acc]));
+      w_store += clock64() - c1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (blockIdx.x == 0 && warp == 2 && lane == 0) {
+      status->prof[PROF_EPI_WAIT]  = w_epi;
+      status->prof[PROF_EPI_STORE] = w_store;
     }
   } else if (kCvt) {
     // ===== converter (both CTAs, 128 threads each, own halves only) =====
@@ -245,10 +284,11 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
     int stage = 0;
     uint32_t raw_parity = 0;
     bool alive = true;
-    const W4A16Lane<32> ln(ct);
+    long long w_cwait = 0, w_cwork = 0;
+    const W4A16Lane<32, 128> ln(ct);
     for (int t = pair; alive && t < total_tiles; t += npairs) {
       const Tile ti = find_tile(sc, count, t);
-      if (ti.scheme != SCH_W4A4 && ti.scheme != SCH_W4A16G128) {
+      if (ti.scheme == SCH_FP16 || ti.scheme == SCH_W8A8) {
         stage = (stage + ti.nkb) % C::kStages;      // rawfull / cvt are not used by this tile
         continue;
       }
@@ -262,6 +302,7 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
           if (gn < N) sz_lo = __ldg(sz + gn);
           if (gn + 8 < N) sz_hi = __ldg(sz + gn + 8);
         }
+        const long long c0 = clock64();
         bool ok = wait_bar(smem_u32(&ctrl->rawfull[stage]), (raw_parity >> stage) & 1u, abort_flag);
         raw_parity ^= 1u << stage;
         ok = __all_sync(0xffffffffu, ok);
@@ -270,21 +311,31 @@ gg_pair_kernel(const GGProblemDev* __restrict__ problems, int count, GGStatus* _
           alive = false;
           break;
         }
-        if (ti.scheme == SCH_W4A4) {
+        const long long c1 = clock64();
+        w_cwait += c1 - c0;
+        if (ti.scheme == SCH_W4A4_XA) {
+          convert_w4a4<128>(rawB(stage), opB(stage), kHalf, ct);
+        } else if (ti.scheme == SCH_W4A4) {
           // rawA | rawB-half are contiguous (2 x 128 packed rows), and so are opA | opB-half
-          convert_w4a4(rawA(stage), opA(stage), 2 * kHalf, ct);
+          convert_w4a4<128>(rawA(stage), opA(stage), 2 * kHalf, ct);
         } else {
-          convert_w4a16<32>(ln, rawB(stage), opB(stage), sz_lo, sz_hi);
+          convert_w4a16<32, 128>(ln, rawB(stage), opB(stage), sz_lo, sz_hi);
         }
         fence_proxy_async_all();
         mbar_arrive_leader(smem_u32(&ctrl->cvt[stage]));
+        w_cwork += clock64() - c1;
         if (++stage == C::kStages) stage = 0;
       }
+    }
+    if (blockIdx.x == 0 && ct == 0) {
+      status->prof[PROF_CVT_WAIT] = w_cwait;
+      status->prof[PROF_CVT_WORK] = w_cwork;
     }
   }
 
   // ---------------------------------------------------------------- teardown
   __syncthreads();
+  if (blockIdx.x == 0 && tid == 0) status->prof[PROF_TOTAL] = clock64() - prof_t0;
   if (*abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -306,8 +357,9 @@ cudaError_t gg_configure_pair() {
                               pair_smem_bytes<true>());
 }
 
-cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* status, bool needs_cvt, int num_ctas,
+cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
                            cudaStream_t stream) {
+  const bool needs_cvt   = cvt_mode != 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim            = dim3((unsigned)(num_ctas & ~1), 1, 1);
   cfg.blockDim           = dim3(kThreads, 1, 1);

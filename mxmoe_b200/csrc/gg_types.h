@@ -13,6 +13,7 @@ enum Scheme : int {
   SCH_W8A8      = 1,  // int8 codes, per-token / per-channel fp16 scales
   SCH_W4A4      = 2,  // int4 codes packed along K, per-token / per-channel fp16 scales
   SCH_W4A16G128 = 3,  // fp16 activations, 4-bit weights packed along N, (scale, zero) per 128-k group
+  SCH_W4A4_XA   = 4,  // w4a4 whose activations are already expanded: one byte 16*q per code (see below)
 };
 
 enum OutMode : int {
@@ -55,19 +56,38 @@ struct alignas(256) GGStatus {
   int where;       // role << 24 | tile index
   int count;       // problems prepared
   int needs_cvt;   // any problem needs the converter warps
-  int pad[60];
+  // cycle counters of CTA 0 of the last launch (clock64 deltas), see GGProf
+  unsigned long long prof[16];
+  int pad[28];
+};
+
+// indices into GGStatus::prof
+enum GGProf : int {
+  PROF_TOTAL = 0,        // kernel body
+  PROF_PROD_WAIT,        // producer waiting for a free stage
+  PROF_MMA_WAIT_OPER,    // MMA issuer waiting for operands (full / cvt)
+  PROF_MMA_WAIT_ACC,     // MMA issuer waiting for a drained accumulator
+  PROF_MMA_ISSUE,        // MMA issuer inside issue + commit
+  PROF_EPI_WAIT,         // epilogue warp 2 waiting for the accumulator
+  PROF_EPI_STORE,        // epilogue warp 2 draining + storing
+  PROF_CVT_WAIT,         // converter warp 6 waiting for packed operands
+  PROF_CVT_WORK,         // converter warp 6 converting
+  PROF_TILES,            // tiles processed by CTA 0
+  PROF_STAGES,           // pipeline stages processed by CTA 0
 };
 static_assert(sizeof(GGStatus) == 256, "GGStatus layout");
 
 constexpr int kDevErrTimeout = 1;   // a bounded wait ran out
 constexpr int kDevErrTooMany = 2;   // more problems than kMaxProblems
 
+// cvt_mode: 0 no 4-bit operand in the launch; 1 only weights need converting (w4a16, w4a4 with expanded
+// activations); 2 packed 4-bit activations are present as well.
 // single-CTA kernel (gg_kernel.cu): tiles of 128 x 256, any number of CTAs
-void gg_launch_single(const GGProblemDev* problems, int count, GGStatus* status, bool needs_cvt, int num_ctas,
+void gg_launch_single(const GGProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
                       cudaStream_t stream);
 cudaError_t gg_configure_single();
 // CTA-pair kernel (gg_pair_kernel.cu): tiles of 256 x 256 on clusters of two CTAs; num_ctas must be even
-cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* status, bool needs_cvt, int num_ctas,
+cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
                            cudaStream_t stream);
 cudaError_t gg_configure_pair();
 

@@ -142,7 +142,7 @@ class EPMoELayer:
         self.seg_tab_host = torch.zeros(2, max(nseg, 1), dtype=torch.int32).pin_memory()
         self.seg_expert_dev = torch.tensor(self.seg_expert or [0], **i32)
         self.recv_row_expert = torch.zeros(self.R_recv, **i32)
-        self.counts_all = [torch.zeros(E, **i32) for _ in range(self.world)]
+        self.counts_all = torch.zeros(self.world * E, **i32)
         self.counts_host = torch.zeros(self.world, E, dtype=torch.int32).pin_memory()
         self.ids_new = torch.zeros(T, k, **i32)
         self._gate_up, self._down = gate_up, down
@@ -160,7 +160,8 @@ class EPMoELayer:
         self._core = ExpertCompute(
             spec.num_experts, spec.hidden, spec.inter, self._gate_up, self._down, self.R_recv, self.seg_expert,
             self.seg_tab[0], self.seg_tab[1], self.recv_row_expert, self.recv.view(-1), self.rec,
-            self.recv.data_ptr() + self.P * 2, self.rec, self.device, shared=shared, shared_inter=spec.shared_inter)
+            self.recv.data_ptr() + self.P * 2, self.rec, self.device, shared=shared, shared_inter=spec.shared_inter,
+            tag_fn=tag_of)     # dispatched rows stay packed (half the NVLink bytes of the expanded format)
 
     def _mark(self, marks, name):
         if self.profile:
@@ -182,9 +183,8 @@ class EPMoELayer:
             f.gather(t, T * k, self.send.view(-1), self.rec, None, rec_scale_off=self.P)
             self._mark(marks, "route+quant+gather")
             # every split size of this step: one all-gather of the counts and one small copy to the host
-            dist.all_gather(self.counts_all, f.counts, group=self.group)
-            for s_, c_ in enumerate(self.counts_all):
-                self.counts_host[s_].copy_(c_, non_blocking=True)
+            dist.all_gather_into_tensor(self.counts_all, f.counts, group=self.group)
+            self.counts_host.view(-1).copy_(self.counts_all, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             plan = ExchangePlan.build(self.counts_host.numpy(), self.ranges, self.rank)
             if plan.total_recv > self.R_recv:
@@ -192,8 +192,9 @@ class EPMoELayer:
                                    "raise capacity_factor")
             nseg = len(plan.seg_m)
             if nseg:
-                self.seg_tab_host[0, :nseg] = torch.tensor(plan.seg_m, dtype=torch.int32)
-                self.seg_tab_host[1, :nseg] = torch.tensor(plan.seg_row0, dtype=torch.int32)
+                tab = self.seg_tab_host.numpy()
+                tab[0, :nseg] = plan.seg_m
+                tab[1, :nseg] = plan.seg_row0
                 self.seg_tab.copy_(self.seg_tab_host, non_blocking=True)
                 if plan.total_recv:
                     self.recv_row_expert[: plan.total_recv].copy_(torch.repeat_interleave(

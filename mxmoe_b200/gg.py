@@ -51,6 +51,7 @@ class Problem:
     row0_dev: object = None   # int32 device scalar: first row
     lda_bytes: int = 0        # row pitch of A in bytes (0 = dense)
     sa_stride: int = 0        # distance between per-token scales in elements (0 = contiguous)
+    a_expanded: int = 0       # w4a4: activations stored as one byte 16*q per code
 
     def fill(self, c: _lib.GGProblem) -> None:
         a_bits, w_bits, gsize, sym = self.qparams
@@ -63,6 +64,7 @@ class Problem:
         c.out_mode = int(self.out_mode)
         c.lda_bytes = int(self.lda_bytes)
         c.sa_stride = int(self.sa_stride)
+        c.a_expanded = int(self.a_expanded)
 
     def flops(self) -> int:
         return 2 * self.M * self.N * self.K
@@ -101,6 +103,18 @@ class GroupedGemm:
         """Synchronise the current stream and raise if the kernel recorded an error."""
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().mxmoe_gg_check(self._ws, current_stream_ptr()))
+
+
+PROF_NAMES = ("total", "producer_wait", "mma_wait_operands", "mma_wait_accumulator", "mma_issue", "epilogue_wait",
+              "epilogue_store", "converter_wait", "converter_work", "tiles", "stages")
+
+
+def profile(g: "GroupedGemm") -> dict:
+    """Cycle counters CTA 0 recorded during the last launch of ``g`` (see mxmoe_gg_profile)."""
+    buf = (C.c_uint64 * 16)()
+    with torch.cuda.device(g.device):
+        _lib.check(_lib.lib().mxmoe_gg_profile(g._ws, buf, current_stream_ptr()))
+    return {n: int(buf[i]) for i, n in enumerate(PROF_NAMES)}
 
 
 def grouped_gemm(problems: Sequence[Problem], check: bool = True, num_ctas: int = 0) -> GroupedGemm:

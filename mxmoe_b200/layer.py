@@ -39,8 +39,16 @@ def tag_of(qp) -> int:
     return 0 if a_bits >= 16 else (1 if a_bits == 8 else 2)
 
 
+def internal_tag(qp) -> int:
+    """Format the layer uses internally: 4-bit activations are kept expanded (tag 3: one byte 16*q per
+    code), so that the grouped GEMM only has to convert the weights."""
+    t = tag_of(qp)
+    return 3 if t == 2 else t
+
+
 def pack_of(tag: int) -> int:
-    return (1, 2, 4)[tag]
+    """Codes per fp16-sized element of a stored row: fp16 1, int8 2, int4 packed 4, int4 expanded 2."""
+    return (1, 2, 4, 2)[tag]
 
 
 def record_stride(row_len: int, tags) -> int:
@@ -69,7 +77,7 @@ class ExpertCompute:
     def __init__(self, num_experts, hidden, inter, gate_up: dict, down: dict, rows_cap: int,
                  seg_expert, seg_m: torch.Tensor, seg_row0: torch.Tensor, row_expert: torch.Tensor,
                  q1: torch.Tensor, rec1: int, scale1_ptr: int, scale1_stride: int, device,
-                 shared: dict | None = None, shared_inter: int = 0):
+                 shared: dict | None = None, shared_inter: int = 0, tag_fn=internal_tag):
         self.E, self.H, self.I, self.Is = num_experts, hidden, inter, shared_inter
         self.R, self.device = rows_cap, device
         self.gate_up, self.down = gate_up, down
@@ -79,12 +87,14 @@ class ExpertCompute:
         f16 = dict(dtype=torch.float16, device=dev)
         local = sorted(set(self.seg_expert))
 
-        def tags(block):
+        def tags(block, fn):
             t = [0] * (num_experts + 1)
             for e, w in block.items():
-                t[e] = tag_of(w.qparams)
+                t[e] = fn(w.qparams)
             return t
-        self._tag1, self._tag2 = tags(gate_up), tags(down)
+        # the first GEMM reads whatever format the caller stored (tag_fn); the second one reads this
+        # object's own store, always in the internal format
+        self._tag1, self._tag2 = tags(gate_up, tag_fn), tags(down, internal_tag)
         self.tag2 = torch.tensor(self._tag2, dtype=torch.int32, device=dev)
         self.rec2 = record_stride(I, {self._tag2[e] for e in local}) if local else I
         self.o1 = torch.zeros(max(R, 1) * 2 * I, **f16)        # gate_up output rows [R, 2I]
@@ -99,10 +109,12 @@ class ExpertCompute:
             w2: PackedWeight = down[e]
             p1.append(Problem(A=q1, B=w1.data, C=self.o1, M=R, N=2 * I, K=H, qparams=w1.qparams,
                               scale_a=scale1_ptr if self._tag1[e] else None, scale_b=w1.scale,
-                              a_rows=R, lda_bytes=rec1 * 2, sa_stride=scale1_stride, m_dev=m_ptr, row0_dev=r_ptr))
+                              a_rows=R, lda_bytes=rec1 * 2, sa_stride=scale1_stride, m_dev=m_ptr, row0_dev=r_ptr,
+                              a_expanded=1 if self._tag1[e] == 3 else 0))
             p2.append(Problem(A=self.q2, B=w2.data, C=self.o2, M=R, N=H, K=I, qparams=w2.qparams,
                               scale_a=self.s2 if self._tag2[e] else None, scale_b=w2.scale,
-                              a_rows=R, lda_bytes=self.rec2 * 2, m_dev=m_ptr, row0_dev=r_ptr))
+                              a_rows=R, lda_bytes=self.rec2 * 2, m_dev=m_ptr, row0_dev=r_ptr,
+                              a_expanded=1 if self._tag2[e] == 3 else 0))
         if shared is not None:
             T, Is, E = shared["tokens"], shared_inter, num_experts
             w1, w2 = gate_up[E], down[E]
@@ -114,9 +126,10 @@ class ExpertCompute:
             self.o2s = torch.zeros(T * H, **f16)
             # the shared expert reads the token-major store of its format directly: no copy
             p1.append(Problem(A=shared["a_ptr"], B=w1.data, C=self.o1s, M=T, N=2 * Is, K=H, qparams=w1.qparams,
-                              scale_a=shared["sa_ptr"] if self._tag1[E] else None, scale_b=w1.scale))
+                              scale_a=shared["sa_ptr"] if self._tag1[E] else None, scale_b=w1.scale,
+                              a_expanded=1 if self._tag1[E] == 3 else 0))
             p2.append(Problem(A=self.q2s, B=w2.data, C=self.o2s, M=T, N=H, K=Is, qparams=w2.qparams,
-                              scale_a=self.s2s if t2 else None, scale_b=w2.scale))
+                              scale_a=self.s2s if t2 else None, scale_b=w2.scale, a_expanded=1 if t2 == 3 else 0))
         else:
             self.o2s = None
         self.gg1 = GroupedGemm(p1, device=dev)
@@ -155,14 +168,15 @@ class TokenQuant:
         self.q8 = torch.zeros(tokens * hidden // 2, **f16) if 1 in tags_used else None
         self.s8 = torch.zeros(tokens, **f16) if 1 in tags_used else None
         self.q4 = torch.zeros(tokens * hidden // 4, **f16) if 2 in tags_used else None
-        self.s4 = torch.zeros(tokens, **f16) if 2 in tags_used else None
+        self.q4x = torch.zeros(tokens * hidden // 2, **f16) if 3 in tags_used else None
+        self.s4 = torch.zeros(tokens, **f16) if (2 in tags_used or 3 in tags_used) else None
         self.args = _lib.TokenQuantArgs()
 
     def fill(self, hidden: torch.Tensor) -> _lib.TokenQuantArgs:
         t = self.args
         t.inp, t.k, t.num_tokens, t.rotate = hidden.data_ptr(), self.H, hidden.shape[0], 1 if self.rotate else 0
         t.signs = None if self.signs is None else self.signs.data_ptr()
-        for name in ("f16", "q8", "s8", "q4", "s4"):
+        for name in ("f16", "q8", "s8", "q4", "s4", "q4x"):
             buf = getattr(self, name)
             setattr(t, name, None if buf is None else buf.data_ptr())
         return t
@@ -178,7 +192,7 @@ class TokenQuant:
             return (self.f16.data_ptr() if self.f16 is not None else hidden.data_ptr()), None
         if tag == 1:
             return self.q8.data_ptr(), self.s8.data_ptr()
-        return self.q4.data_ptr(), self.s4.data_ptr()
+        return (self.q4x if tag == 3 else self.q4).data_ptr(), self.s4.data_ptr()
 
 
 class MoELayer:
@@ -216,7 +230,7 @@ class MoELayer:
 
         tag1 = [0] * (E + 1)
         for e, w in gate_up.items():
-            tag1[e] = tag_of(w.qparams)
+            tag1[e] = internal_tag(w.qparams)
         self._tag1 = tag1
         self.tag1 = torch.tensor(tag1, **i32)
         routed = [e for e in sorted(gate_up) if e < E]
@@ -304,6 +318,26 @@ class MoELayer:
                 self._core.o2s.data_ptr() if self.has_shared else None, out.data_ptr(), T, self.topk, self.H,
                 current_stream_ptr()))
         return out
+
+    def forward_graph(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor | None = None):
+        """Same as :meth:`forward`, replayed from a CUDA graph.
+
+        The step launches nine kernels and never returns to the host, so it is captured once per set
+        of argument buffers (their addresses are baked into the graph: refill the same tensors for
+        the next step) and replayed with a single launch.
+        """
+        key = (hidden.data_ptr(), topk_ids.data_ptr(), None if topk_weights is None else topk_weights.data_ptr())
+        if getattr(self, "_graph_key", None) != key:
+            with torch.cuda.device(self.device):
+                self.forward(hidden, topk_ids, topk_weights)        # builds descriptors, warms up
+                self.check()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.forward(hidden, topk_ids, topk_weights)
+                self._graph, self._graph_key = g, key
+        self._graph.replay()
+        return self.out.view(self.T, self.H)
 
     launches_per_step = 9   # route x3, quant_tokens, gather_rows, GEMM, silu, GEMM, combine (+1 with a shared expert)
 

@@ -46,6 +46,17 @@ def unpack_k(words: np.ndarray, bits: int) -> np.ndarray:
     return f.reshape(words.shape[0], -1).astype(np.int32)
 
 
+def expand_k4(codes: np.ndarray) -> np.ndarray:
+    """``[R, K]`` 4-bit codes -> ``[R, K]`` bytes ``16*q`` in the order the B200 kernel's own int4 -> int8
+    unpacking produces from the packed row (no counterpart in the reference: an internal activation
+    format of this build).  Every 16 packed bytes become 16 bytes holding their high nibbles followed
+    by 16 bytes holding their low nibbles, each nibble moved to the top of its byte."""
+    pb = pack_k(codes, 4).view(np.uint8).reshape(codes.shape[0], -1, 16)       # [R, K/32, 16] packed bytes
+    hi = pb & 0xF0
+    lo = (pb << 4) & 0xF0
+    return np.concatenate((hi, lo), axis=2).reshape(codes.shape[0], -1)
+
+
 # ---------------------------------------------------------------------------
 # weight-only 4-bit scheme: N-packed, fragment-permuted
 # ---------------------------------------------------------------------------

@@ -22,7 +22,7 @@ REL_L2 = 1e-3
 def gg_kernel(request):
     """Every test of this file runs once per kernel: CTA pairs (256 x 256 tiles, cta_group::2) and
     single CTAs (128 x 256 tiles)."""
-    util.DEFAULT_CTAS = 0 if request.param == "pair" else 1 << 20
+    util.DEFAULT_CTAS = -(1 << 20) if request.param == "pair" else 1 << 20
     yield request.param
     util.DEFAULT_CTAS = 0
 
@@ -53,6 +53,18 @@ def test_int_scaled_output_bit_exact(cuda_device, bits, shape):
     got = c.C.cpu().numpy()
     assert np.array_equal(got.view(np.uint16), c.ref.view(np.uint16)), \
         f"{np.count_nonzero(got.view(np.uint16) != c.ref.view(np.uint16))} of {got.size} outputs differ"
+
+
+@pytest.mark.parametrize("shape", SHAPES_INT)
+def test_w4a4_expanded_activations_bit_exact(cuda_device, shape):
+    """Activations stored as one byte 16*q per code (what the layer's own prologue writes): accumulators
+    and scaled output are the same bits as with packed activations."""
+    rng = np.random.default_rng(hash((44,) + shape) % 2**32)
+    c = util.WxAxCase(rng, *shape, 4, expanded=True)
+    util.run([c.problem(cuda_device, gg.OUT_ACC)])
+    assert np.array_equal(c.C.cpu().numpy(), c.acc)
+    util.run([c.problem(cuda_device)])
+    assert np.array_equal(c.C.cpu().numpy().view(np.uint16), c.ref.view(np.uint16))
 
 
 def test_int_extreme_codes(cuda_device):
@@ -122,7 +134,8 @@ def test_few_ctas_walk_many_tiles_of_alternating_schemes(cuda_device, num_ctas):
              util.Fp16Case(rng, 140, 512, 192), util.WxAxCase(rng, 129, 256, 640, 8),
              util.W4A16Case(rng, 260, 512, 256), util.WxAxCase(rng, 64, 1024, 128, 4),
              util.WxAxCase(rng, 257, 512, 512, 8), util.W4A16Case(rng, 30, 768, 128),
-             util.Fp16Case(rng, 200, 264, 64), util.WxAxCase(rng, 500, 256, 1408, 4)]
+             util.Fp16Case(rng, 200, 264, 64), util.WxAxCase(rng, 500, 256, 1408, 4),
+             util.WxAxCase(rng, 333, 512, 256, 4, expanded=True), util.WxAxCase(rng, 70, 768, 384, 4, expanded=True)]
     util.run([c.problem(cuda_device) for c in cases], num_ctas=num_ctas)
     for i, c in enumerate(cases):
         got = c.C.cpu().numpy()

@@ -119,6 +119,27 @@ def test_layer_matches_fake_quant_loop(cuda_device, scheme, shared, rotate):
         assert torch.equal(got2, lay.o2[: got2.numel()])
 
 
+def test_graph_replay_matches_eager(cuda_device):
+    spec = _spec("mixed5", True, True, tokens=96)
+    gate_up, down, signs, _ = workload.build_layer_weights(spec, device=cuda_device)
+    lay = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens,
+                   shared_inter=spec.shared_inter, signs=signs, rotate=True, device=cuda_device)
+    hidden = workload.make_hidden(spec).to(cuda_device)
+    ids, wts = workload.make_routing(spec)
+    ids, wts = ids.to(cuda_device), wts.to(cuda_device)
+    want = lay.forward(hidden, ids, wts).clone()
+    got = lay.forward_graph(hidden, ids, wts).clone()
+    assert torch.equal(got, want)
+    # new routing and activations in the same buffers: the replayed graph follows the device-side counts
+    ids2, _ = workload.make_routing(spec, seed=77)
+    ids.copy_(ids2.to(cuda_device))
+    hidden.copy_(workload.make_hidden(spec, seed=9).to(cuda_device))
+    got2 = lay.forward_graph(hidden, ids, wts).clone()
+    want2 = lay.forward(hidden, ids, wts).clone()
+    lay.check()
+    assert torch.equal(got2, want2) and not torch.equal(got2, want)
+
+
 def test_layer_empty_experts_and_decode_batch(cuda_device):
     """Decode-sized batch: most experts receive no token."""
     spec = workload.LayerSpec("tiny-decode", 16, 2, 512, 256, 0, 3, "zipf", 1.0, False, False, "w4a16_g128_asym")

@@ -32,7 +32,7 @@ def test_struct_layouts_match_header():
     assert ctypes.sizeof(_lib.GGPlan) == 8
     assert ctypes.sizeof(_lib.ActArgs) == 11 * 8 + 8 * 4
     assert ctypes.sizeof(_lib.RouteArgs) == 8 * 8 + 4 * 4
-    assert ctypes.sizeof(_lib.TokenQuantArgs) == 7 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.TokenQuantArgs) == 8 * 8 + 4 * 4
 
 
 def test_no_device_is_an_error_not_a_fallback():

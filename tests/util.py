@@ -33,8 +33,9 @@ def rand_scales(rng, n, lo=0.002, hi=0.02):
 class WxAxCase:
     """Random w8a8 / w4a4 problem with known integer codes."""
 
-    def __init__(self, rng, m, n, k, bits):
+    def __init__(self, rng, m, n, k, bits, expanded=False):
         self.m, self.n, self.k, self.bits = m, n, k, bits
+        self.expanded = expanded      # 4-bit activations handed over as one byte 16*q per code
         self.qa = rand_codes(rng, m, k, bits)
         self.qb = rand_codes(rng, n, k, bits)
         self.sa = rand_scales(rng, m, 0.01, 0.5)
@@ -43,7 +44,10 @@ class WxAxCase:
         self.ref = og.wxax_epilogue(self.acc, self.sa, self.sb)
 
     def problem(self, dev, out_mode=gg.OUT_FP16):
-        self.A = t16(op.pack_k(self.qa, self.bits), dev)
+        if self.expanded:
+            self.A = torch.from_numpy(op.expand_k4(self.qa).copy()).to(dev)
+        else:
+            self.A = t16(op.pack_k(self.qa, self.bits), dev)
         self.B = t16(op.pack_k(self.qb, self.bits), dev)
         self.SA = t16(self.sa, dev)
         self.SB = t16(self.sb, dev)
@@ -53,7 +57,7 @@ class WxAxCase:
             self.C = torch.full((self.m, self.n), float("nan"), dtype=torch.float16, device=dev)
         q = Q_W8A8 if self.bits == 8 else Q_W4A4
         return gg.Problem(A=self.A, B=self.B, C=self.C, M=self.m, N=self.n, K=self.k, qparams=q,
-                          scale_a=self.SA, scale_b=self.SB, out_mode=out_mode)
+                          scale_a=self.SA, scale_b=self.SB, out_mode=out_mode, a_expanded=1 if self.expanded else 0)
 
 
 class Fp16Case:
@@ -92,8 +96,8 @@ class W4A16Case:
                           scale_b=self.SB, out_mode=out_mode)
 
 
-# launch geometry used when a test does not ask for one: 0 = library default (CTA-pair kernel on every
-# SM), a large positive number = single-CTA kernel on every SM.  tests/test_gpu_gemm.py runs with both.
+# launch geometry used when a test does not ask for one: 0 = library default, a large positive number =
+# single-CTA kernel on every SM, a large negative number = CTA-pair kernel on every SM.  tests/test_gpu_gemm.py runs with both.
 DEFAULT_CTAS = 0
 
 
