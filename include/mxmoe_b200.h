@@ -106,11 +106,22 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
                      void* stream, mxmoe_gg_plan* plan);
 
 /* Launch the persistent kernel over a prepared workspace; may be called any number of times after
- * one prepare.  `num_ctas` == 0: the default kernel on every SM (single CTAs, 128 x 256 tiles;
- * environment MXMOE_GG_KERNEL=pair selects the CTA-pair kernel instead); > 0: the single-CTA kernel
- * with that many CTAs; < 0: the CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles) with
- * -num_ctas CTAs (rounded down to even).  All choices give identical results. */
+ * one prepare.  `num_ctas` == 0: the default kernel on every SM; > 0: the default kernel with that
+ * many CTAs; < 0: the CTA-pair kernel with -num_ctas CTAs (rounded down to even).  The default kernel
+ * is named by the environment variable MXMOE_GG_KERNEL (swap | single | pair, read at every call).
+ * All kernels give identical results. */
 int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream);
+
+/* The same with the kernel named explicitly. */
+enum mxmoe_gg_kernel {
+  MXMOE_GG_KERNEL_DEFAULT = 0,
+  MXMOE_GG_KERNEL_SINGLE = 1, /* one CTA per tile of 128 rows x 256 channels, both operands from shared memory */
+  MXMOE_GG_KERNEL_PAIR = 2,   /* tcgen05 cta_group::2, 256 x 256 tiles on clusters of two CTAs */
+  MXMOE_GG_KERNEL_SWAP = 3    /* swapped operands: 128 channels x up to 192 tokens per tile, 4-bit weights
+                                 converted into tensor memory (launches with packed 4-bit activations
+                                 run on the SINGLE kernel) */
+};
+int mxmoe_gg_run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_ctas, void* stream);
 
 /* prepare + run */
 int mxmoe_gg_launch(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,

@@ -75,6 +75,7 @@ int device_state(DeviceState** out) {
     st.encode = reinterpret_cast<EncodeTiledFn>(fn);
     CUDA_TRY(mxb::gg_configure_single());
     CUDA_TRY(mxb::gg_configure_pair());
+    CUDA_TRY(mxb::gg_configure_swap());
     st.ready = true;
   }
   *out = &st;
@@ -183,14 +184,58 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   return MXMOE_OK;
 }
 
-// which kernel a launch with num_ctas == 0 uses: the single-CTA kernel unless MXMOE_GG_KERNEL=pair
-bool default_pair() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("MXMOE_GG_KERNEL");
-    v = (e && !strcmp(e, "pair")) ? 1 : 0;
+// The same problem for the kernel with swapped operands: tensor maps with its boxes (weights: 128 channels per
+// box; activations: 192-row and 32-row boxes).  `d` has been validated by build_problem already.
+int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, const mxb::GGProblemDev& d,
+                       mxb::GGSwapProblemDev* o) {
+  int rc;
+  const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
+  const uint64_t lda    = p.lda_bytes > 0 ? (uint64_t)p.lda_bytes : 0;
+  const uint64_t K = (uint64_t)p.K, N = (uint64_t)p.N;
+  const auto f16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const auto u8  = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const auto s128 = CU_TENSOR_MAP_SWIZZLE_128B;
+  switch (d.scheme) {
+    case mxb::SCH_FP16:
+      if ((rc = encode_2d(enc, &o->tmW, p.B, f16, 2, K, N, 64, mxb::kWT, s128, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W8A8:
+      if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K, N, 128, mxb::kWT, s128, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W4A4_XA:
+      // packed rows of 64 bytes per stage; the 64-byte swizzle spreads the rows a converter warp reads over the banks
+      if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K / 2, N, 64, mxb::kWT, CU_TENSOR_MAP_SWIZZLE_64B, "B", idx))) return rc;
+      break;
+    case mxb::SCH_W4A16G128:
+      // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, 32 packed rows = 128 channels
+      if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K * 2, N / 4, 128, mxb::kWT / 4, s128, "B", idx))) return rc;
+      break;
+    default:
+      break;   // packed 4-bit activations: served by the kernel without swapped operands
   }
-  return v == 1;
+  if (d.scheme == mxb::SCH_FP16 || d.scheme == mxb::SCH_W4A16G128) {
+    if ((rc = encode_2d(enc, &o->tmX, p.A, f16, 2, K, a_rows, 64, mxb::kTT, s128, "A", idx, lda))) return rc;
+    if ((rc = encode_2d(enc, &o->tmXs, p.A, f16, 2, K, a_rows, 64, mxb::kXBoxSmall, s128, "A", idx, lda))) return rc;
+  } else if (d.scheme == mxb::SCH_W8A8 || d.scheme == mxb::SCH_W4A4_XA) {
+    if ((rc = encode_2d(enc, &o->tmX, p.A, u8, 1, K, a_rows, 128, mxb::kTT, s128, "A", idx, lda))) return rc;
+    if ((rc = encode_2d(enc, &o->tmXs, p.A, u8, 1, K, a_rows, 128, mxb::kXBoxSmall, s128, "A", idx, lda))) return rc;
+  }
+  o->scale_a = d.scale_a; o->scale_b = d.scale_b; o->C = d.C; o->m_dev = d.m_dev; o->row0_dev = d.row0_dev;
+  o->M = d.M; o->N = d.N; o->K = d.K; o->row0 = d.row0;
+  o->scheme = d.scheme; o->out_mode = d.out_mode; o->ldc = d.ldc; o->sa_stride = d.sa_stride;
+  return MXMOE_OK;
+}
+
+enum GGKernel { GGK_DEFAULT = 0, GGK_SINGLE = 1, GGK_PAIR = 2, GGK_SWAP = 3 };
+
+// which kernel a launch that does not name one uses: MXMOE_GG_KERNEL = swap | single | pair (read at every call,
+// so that a test can switch it)
+int default_kernel() {
+  const char* e = getenv("MXMOE_GG_KERNEL");
+  if (e && !strcmp(e, "pair")) return GGK_PAIR;
+  if (e && !strcmp(e, "single")) return GGK_SINGLE;
+  if (e && !strcmp(e, "swap")) return GGK_SWAP;
+  return GGK_SWAP;
 }
 
 struct ShimScratch {
@@ -215,7 +260,7 @@ int mxmoe_device_sm_count(void) {
 
 size_t mxmoe_gg_workspace_bytes(int problem_count) {
   if (problem_count < 0) problem_count = 0;
-  return sizeof(mxb::GGStatus) + sizeof(mxb::GGProblemDev) * (size_t)problem_count;
+  return sizeof(mxb::GGStatus) + (sizeof(mxb::GGProblemDev) + sizeof(mxb::GGSwapProblemDev)) * (size_t)problem_count;
 }
 
 int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,
@@ -232,19 +277,27 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   std::memset(host.data(), 0, host.size());
   auto* status = reinterpret_cast<mxb::GGStatus*>(host.data());
   auto* dev    = reinterpret_cast<mxb::GGProblemDev*>(host.data() + sizeof(mxb::GGStatus));
+  std::vector<mxb::GGSwapProblemDev> swp((size_t)problem_count);
+  if (problem_count) std::memset(swp.data(), 0, swp.size() * sizeof(mxb::GGSwapProblemDev));
   int kept = 0, needs_cvt = 0;
   for (int i = 0; i < problem_count; ++i) {
     if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
     rc = build_problem(st->encode, problems[i], i, dev + kept);
     if (rc) return rc;
+    rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept]);
+    if (rc) return rc;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
     ++kept;
   }
+  status->pad[0]    = getenv("MXMOE_GG_PROFILE") ? atoi(getenv("MXMOE_GG_PROFILE")) : 0;   // per-role counters on
   status->count     = kept;
   status->needs_cvt = needs_cvt;
   // pageable source: the runtime stages the bytes before returning, so `host` may go out of scope
-  CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), sizeof(mxb::GGStatus) + sizeof(mxb::GGProblemDev) * (size_t)kept,
+  // the list for the kernel with swapped operands follows the kept entries of the first list
+  const size_t first = sizeof(mxb::GGStatus) + sizeof(mxb::GGProblemDev) * (size_t)kept;
+  if (kept) std::memcpy(host.data() + first, swp.data(), sizeof(mxb::GGSwapProblemDev) * (size_t)kept);
+  CUDA_TRY(cudaMemcpyAsync(workspace, host.data(), first + sizeof(mxb::GGSwapProblemDev) * (size_t)kept,
                            cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
   if (plan) {
     plan->count     = kept;
@@ -253,7 +306,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   return MXMOE_OK;
 }
 
-int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream) {
+namespace {
+int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_ctas, void* stream) {
   if (!workspace || !plan) return fail(MXMOE_ERR_WORKSPACE, "null workspace or plan");
   DeviceState* st = nullptr;
   int rc          = device_state(&st);
@@ -262,18 +316,32 @@ int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void*
   if (count < 0 || count > mxb::kMaxProblems) return fail(MXMOE_ERR_WORKSPACE, "plan holds an invalid problem count %d", count);
   if (count == 0) return MXMOE_OK;
   auto* status = static_cast<mxb::GGStatus*>(workspace);
-  auto* probs  = reinterpret_cast<const mxb::GGProblemDev*>(static_cast<unsigned char*>(workspace) + sizeof(mxb::GGStatus));
+  auto* base   = static_cast<unsigned char*>(workspace) + sizeof(mxb::GGStatus);
+  auto* probs  = reinterpret_cast<const mxb::GGProblemDev*>(base);
+  auto* swp    = reinterpret_cast<const mxb::GGSwapProblemDev*>(base + sizeof(mxb::GGProblemDev) * (size_t)count);
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  // num_ctas > 0: single-CTA kernel with that many CTAs; < 0: CTA-pair kernel with -num_ctas CTAs;
-  // 0: the library default on every SM
-  bool pair = num_ctas < 0 || (num_ctas == 0 && default_pair());
-  int n     = num_ctas < 0 ? -num_ctas : num_ctas;
+  if (kernel == GGK_DEFAULT) kernel = default_kernel();
+  if (kernel == GGK_SWAP && needs_cvt == 2) kernel = GGK_SINGLE;   // packed 4-bit activations
+  int n = num_ctas;
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
-  if (pair && n < 2) pair = false;
-  if (pair) CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
-  else      mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
+  if (kernel == GGK_PAIR && n < 2) kernel = GGK_SINGLE;
+  if (kernel == GGK_PAIR)       CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
+  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, n, cs);
+  else                          mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
   CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;
+}
+}  // namespace
+
+int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream) {
+  // num_ctas > 0: that many CTAs of the default kernel; < 0: CTA-pair kernel with -num_ctas CTAs; 0: every SM
+  if (num_ctas < 0) return run_kernel(workspace, plan, GGK_PAIR, -num_ctas, stream);
+  return run_kernel(workspace, plan, GGK_DEFAULT, num_ctas, stream);
+}
+
+int mxmoe_gg_run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_ctas, void* stream) {
+  if (kernel < GGK_DEFAULT || kernel > GGK_SWAP) return fail(MXMOE_ERR_INVALID, "unknown kernel id %d", kernel);
+  return run_kernel(workspace, plan, kernel, num_ctas < 0 ? -num_ctas : num_ctas, stream);
 }
 
 int mxmoe_gg_launch(const mxmoe_gg_problem* problems, int problem_count, void* workspace, size_t workspace_bytes,

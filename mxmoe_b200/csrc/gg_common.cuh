@@ -11,12 +11,13 @@ using namespace ptx;
 
 constexpr uint64_t kTimeoutNs = 1000000000ull;
 
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t it       = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((++it & 63u) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kTimeoutNs) {
@@ -25,6 +26,15 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
       }
     }
   }
+}
+
+// The same for a whole warp: lane 0 polls (every polling thread is one more access to the mbarrier in shared
+// memory), the outcome is broadcast.  __shfl_sync orders the lanes' later shared-memory reads after lane 0's
+// observation of the barrier.
+__device__ __forceinline__ bool warp_wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = wait_bar(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // per-problem scheduling tables kept in shared memory
@@ -41,16 +51,19 @@ struct Tile {
   int p, m_tile, n_tile, scheme, nkb;
 };
 
-// Fill the tables (all threads of the CTA; contains two __syncthreads).  `rows_per_tile` is 128 for
-// the single-CTA kernel and 256 for the CTA pair.
-__device__ __forceinline__ void build_sched(Sched* sc, const GGProblemDev* problems, int count, int rows_per_tile) {
+// Fill the tables (all threads of the CTA; contains two __syncthreads).  `rows_per_tile` x `cols_per_tile`
+// is the tile of C: 128 x 256 for the single-CTA kernel, 256 x 256 for the CTA pair, 192 x 128 for the
+// kernel with swapped operands.
+template <typename Problem>
+__device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, int count, int rows_per_tile,
+                                            int cols_per_tile = kBN) {
   const int tid = threadIdx.x, lane = tid & 31;
   for (int p = tid; p < count; p += blockDim.x) {
-    const GGProblemDev& pr = problems[p];
+    const Problem& pr = problems[p];
     int m = pr.M;
     if (pr.m_dev) m = min(max(*pr.m_dev, 0), pr.M);
     const int r0     = pr.row0_dev ? *pr.row0_dev : pr.row0;
-    const int nt     = (pr.N + kBN - 1) / kBN;
+    const int nt     = (pr.N + cols_per_tile - 1) / cols_per_tile;
     const int kelems = (pr.scheme == SCH_FP16 || pr.scheme == SCH_W4A16G128) ? 64 : 128;
     const int nkb    = (pr.K + kelems - 1) / kelems;
     sc->tile_end[p] = ((m + rows_per_tile - 1) / rows_per_tile) * nt;

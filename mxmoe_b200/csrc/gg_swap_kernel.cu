@@ -1,0 +1,621 @@
+// Persistent mixed-precision grouped GEMM for sm_100a with swapped operands, one CTA per SM.
+//
+// Same contract as gg_kernel.cu (one launch walks a device-side list of problems
+// C[M,N] = A[M,K] x B[N,K]^T, each with its own quantisation scheme; reference:
+// mxmoe/kernels/compose_kernel.py:150-295, cta_gemm.cuh:7-107, :291-421, :423-608), but the MMA
+// computes C^T: the WEIGHTS are the M side (tiles of 128 output channels) and the TOKENS the
+// N side (tiles of up to 192 rows, any multiple of 16).  Consequences:
+//   * 4-bit weights are unpacked / dequantised by the converter warps from shared memory straight
+//     into TENSOR MEMORY (tcgen05.st) and the MMA takes its A operand from there: the converted
+//     weights never travel through shared memory again, which is the unit that limits the kernel
+//     with the operands the other way round.
+//   * a ragged expert costs MMA time for its rows rounded up to 16, not to 128.
+//   * the weight-conversion work per MAC shrinks with the token tile (192 instead of 128 rows).
+//
+// TMEM columns: [0,192) and [192,384) two accumulators (128 channels x up to 192 tokens, fp32/int32),
+// [384,512) four A-operand slots of 32 columns (128 channels x 128 bytes of K each).
+//
+// One CTA (480 threads; 224 when no problem has 4-bit weights):
+//   warp 0      TMA producer: weights (packed or plain) + activations into a ring of 5 stages.
+//   warp 1      MMA issuer.  It never touches shared memory: while the tensor core streams its operands
+//               from shared memory, a shared-memory round trip of a regular warp (an mbarrier.try_wait, a
+//               plain load) takes hundreds of cycles, and one of them between two batches of MMAs leaves
+//               the tensor pipe idle.  The warp is paced by NAMED barriers (bar.sync) instead.
+//   warps 2-5   epilogue: tcgen05.ld (lane = channel, columns = tokens) -> scales -> fp16 ->
+//               transposed through shared memory -> 16-byte global stores along the channel axis.
+//   warp 6      watcher: waits on the mbarriers the TMA unit and the converters complete (full[s],
+//               afull[a]) and forwards each stage to the MMA warp with bar.arrive.
+//   warps 7-14  converters: thread = one weight row of the tile (its TMEM lane), two warps per lane
+//               quarter splitting the 128 bytes of K of a stage.
+//
+// Barrier protocol.  full[s] / empty[s] (mbarriers) are followed by the producer, the watcher and the
+// converter warps on EVERY stage (the converter warps arrive on empty[s] as well, also for tiles they have
+// nothing to convert in), so no waiter can be lapped and parities follow from the stage counter.
+// afull[a] / aempty[a] (A slots in TMEM) are used only for stages with converted weights; both sides count
+// those uses.  Named barriers: 1 + s "stage s is ready" (watcher arrives, MMA warp syncs), 6 + b
+// "accumulator b is drained" (epilogue warps arrive, MMA warp syncs).  Every mbarrier wait is bounded (1 s
+// of %globaltimer); a role whose wait ran out raises the abort flag and keeps walking its loop without
+// waiting or working, so that every bar.arrive another warp counts on is still made and the kernel ends.
+#include "gg_common.cuh"
+
+namespace mxb {
+
+using namespace ptx;
+using namespace ggc;
+
+namespace {
+
+constexpr int kWSlotBytes  = kWT * kRowBytes;   // 16 KiB: plain weights, or 8 / 4 KiB of packed ones
+constexpr int kXSlotBytes  = kTT * kRowBytes;   // 28 KiB
+constexpr int kStageBytesS = kWSlotBytes + kXSlotBytes;
+constexpr int kStagesS     = 5;
+constexpr int kRingBytesS  = kStagesS * kStageBytesS;   // 176 KiB
+constexpr int kEpiStageS   = 2048;                       // per epilogue warp: 16 token pairs x 32 channels x 4 bytes
+constexpr int kCvtWarps    = 8;
+constexpr uint32_t kAccCols = kTT;                       // columns per accumulator
+constexpr uint32_t kASlotCol0 = 2 * kTT;                 // 352: A slot s (one per ring stage) at kASlotCol0 + 32 s
+constexpr uint32_t kASlotCols = 32;
+constexpr int kCvtGroup    = 4;                          // warps per converter group (one per TMEM lane quarter)
+static_assert(kASlotCol0 + kStagesS * kASlotCols <= 512, "tensor memory budget");
+
+template <int kMode>
+struct CfgS {
+  static constexpr int kThreads = 224 + (kMode ? kCvtWarps * 32 : 0);
+};
+
+// What every role needs to know about one tile, precomputed once per CTA: looking a tile up in the
+// scheduling tables is a chain of dependent shared-memory loads, each of which takes hundreds of cycles
+// while the tensor core streams operands from shared memory.
+struct TileRec {
+  int pk;       // problem | scheme << 8 | k-blocks << 12
+  int x_row;    // buffer row of the tile's first token (A, scale_a and C)
+  int n_tile;   // channel tile
+  int ntok;     // tokens in the tile (1 .. kTT)
+};
+constexpr int kMaxRecs = 512;   // tiles per CTA kept in the table; later ones are looked up on the fly
+
+struct TileS {
+  int p, scheme, nkb, x_row, n_tile, ntok;
+};
+
+struct CtrlS {
+  uint64_t full[kStagesS];
+  uint64_t empty[kStagesS];
+  uint64_t afull[kStagesS];
+  uint64_t tfull[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int pad[2];
+  Sched sched;
+  alignas(16) __half sa_stage[4][kTT + 32];   // per epilogue warp: per-token scales of the current tile (read 16 bytes at a time)
+  alignas(16) TileRec recs[kMaxRecs];
+};
+
+static_assert((kTT + 32) % 8 == 0, "sa_stage rows must stay 16-byte aligned");
+constexpr int smem_bytes_swap() { return 1024 + kRingBytesS + 4 * kEpiStageS + (int)sizeof(CtrlS); }
+
+__device__ __forceinline__ void report_s(GGStatus* status, int role, int tile) {
+  atomicCAS(&status->error, 0, kDevErrTimeout);
+  atomicCAS(&status->where, 0, (role << 24) | tile);
+}
+
+__device__ __forceinline__ bool is_int_scheme(int s) { return s != SCH_FP16 && s != SCH_W4A16G128; }
+__device__ __forceinline__ bool is_cvt_scheme(int s) { return s == SCH_W4A4_XA || s == SCH_W4A16G128; }
+
+__device__ __forceinline__ long long tick(bool on) { return on ? clock64() : 0ll; }
+
+__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t) {
+  const Tile ti = find_tile(sc, count, t);
+  TileRec r;
+  r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12);
+  r.x_row  = sc->row0[ti.p] + ti.m_tile * kTT;
+  r.n_tile = ti.n_tile;
+  r.ntok   = min(kTT, sc->m_eff[ti.p] - ti.m_tile * kTT);
+  return r;
+}
+__device__ __forceinline__ TileS decode_rec(const TileRec& r) {
+  TileS t;
+  t.p = r.pk & 0xff; t.scheme = (r.pk >> 8) & 15; t.nkb = r.pk >> 12;
+  t.x_row = r.x_row; t.n_tile = r.n_tile; t.ntok = r.ntok;
+  return t;
+}
+
+constexpr int kBarStage0 = 1;   // named barriers 1..5: stage s is ready (watcher -> MMA warp), 64 threads
+constexpr int kBarAcc0   = 6;   // named barriers 6, 7: accumulator b is drained (epilogue -> MMA warp), 160 threads
+__device__ __forceinline__ void nbar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void nbar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+}  // namespace
+
+// The MMA warp's main loop over the K blocks of one tile, specialised on the operand kind and on where
+// the weights come from (kV: 0 int8 / shared memory, 1 fp16 / shared memory, 2 int8 / tensor memory, 3 fp16 /
+// tensor memory) so that the issue sequence of a stage is straight-line code: a branch per MMA made the
+// issue of every MMA several times slower.  All lanes walk the loop and meet the named barrier of each
+// stage; lane 0 issues.  One MMA consumes 32 bytes of K per row: 8 TMEM columns of A or 32 bytes of a
+// shared-memory row.
+template <int kV>
+__device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uint32_t d_tmem, uint32_t idesc,
+                                              uint32_t ring_base, uint32_t a_tmem0, uint32_t empty0, bool prof_on,
+                                              long long& w_oper, long long& w_issue) {
+  for (int kb = 0; kb < nkb; ++kb) {
+    const long long c0 = tick(prof_on);
+    nbar_sync(kBarStage0 + stage, 64);   // operands of this stage are in place
+    const long long c1 = tick(prof_on);
+    w_oper += c1 - c0;
+    if (lane == 0) {
+      tc_fence_after_sync();
+      const uint32_t wslot   = ring_base + stage * kStageBytesS;
+      const uint64_t xdesc   = smem_desc_sw128(wslot + kWSlotBytes);
+      const uint32_t accum0  = kb > 0 ? 1u : 0u;
+      if (kV == 0) {
+        const uint64_t wdesc = smem_desc_sw128(wslot);
+        mma_i8_ss(d_tmem, wdesc, xdesc, idesc, accum0);
+        mma_i8_ss(d_tmem, wdesc + 2, xdesc + 2, idesc, 1u);
+        mma_i8_ss(d_tmem, wdesc + 4, xdesc + 4, idesc, 1u);
+        mma_i8_ss(d_tmem, wdesc + 6, xdesc + 6, idesc, 1u);
+      } else if (kV == 1) {
+        const uint64_t wdesc = smem_desc_sw128(wslot);
+        mma_f16_ss(d_tmem, wdesc, xdesc, idesc, accum0);
+        mma_f16_ss(d_tmem, wdesc + 2, xdesc + 2, idesc, 1u);
+        mma_f16_ss(d_tmem, wdesc + 4, xdesc + 4, idesc, 1u);
+        mma_f16_ss(d_tmem, wdesc + 6, xdesc + 6, idesc, 1u);
+      } else if (kV == 2) {
+        const uint32_t a_tmem = a_tmem0 + stage * kASlotCols;   // A slot = ring stage
+        mma_i8_ts(d_tmem, a_tmem, xdesc, idesc, accum0);
+        mma_i8_ts(d_tmem, a_tmem + 8, xdesc + 2, idesc, 1u);
+        mma_i8_ts(d_tmem, a_tmem + 16, xdesc + 4, idesc, 1u);
+        mma_i8_ts(d_tmem, a_tmem + 24, xdesc + 6, idesc, 1u);
+      } else {
+        const uint32_t a_tmem = a_tmem0 + stage * kASlotCols;
+        mma_f16_ts(d_tmem, a_tmem, xdesc, idesc, accum0);
+        mma_f16_ts(d_tmem, a_tmem + 8, xdesc + 2, idesc, 1u);
+        mma_f16_ts(d_tmem, a_tmem + 16, xdesc + 4, idesc, 1u);
+        mma_f16_ts(d_tmem, a_tmem + 24, xdesc + 6, idesc, 1u);
+      }
+      mma_commit(empty0 + 8 * stage);
+    }
+    __syncwarp();
+    w_issue += tick(prof_on) - c1;
+    if (++stage == kStagesS) stage = 0;
+  }
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(CfgS<kMode>::kThreads, 1)
+gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatus* __restrict__ status) {
+  constexpr bool kCvt = kMode != 0;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
+  uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
+  CtrlS* ctrl              = reinterpret_cast<CtrlS*>(smem_gen + kRingBytesS + 4 * kEpiStageS);
+  const uint32_t epi_base  = smem_base + kRingBytesS;
+  Sched* sc                = &ctrl->sched;
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  const int tid  = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (count > kMaxProblems) {
+    if (tid == 0 && blockIdx.x == 0) atomicCAS(&status->error, 0, kDevErrTooMany);
+    return;
+  }
+
+  auto wslot = [&](int s) { return smem_base + s * kStageBytesS; };
+  auto xslot = [&](int s) { return smem_base + s * kStageBytesS + kWSlotBytes; };
+
+  // ------------------------------------------------------------------ setup
+  if (tid == 0) {
+    for (int s = 0; s < kStagesS; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1 + (kCvt ? kCvtGroup : 0));
+      mbar_init(smem_u32(&ctrl->afull[s]), kCvtGroup);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->tfull[b]), 1);
+    }
+    ctrl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  build_sched(sc, problems, count, kTT, kWT);
+  const int total_tiles = sc->total_tiles;
+  const int my_tiles    = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  for (int i = tid; i < my_tiles && i < kMaxRecs; i += blockDim.x) ctrl->recs[i] = make_rec(sc, count, blockIdx.x + i * gridDim.x);
+  auto tile_rec = [&](int i) -> TileRec {
+    if (i < kMaxRecs) return ctrl->recs[i];
+    return make_rec(sc, count, blockIdx.x + i * gridDim.x);
+  };
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  const bool prof_on = status->pad[0] != 0;   // per-role cycle counters wanted (costs a few percent)
+  const long long prof_t0  = clock64();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  // ------------------------------------------------------------------ roles
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long w_prod = 0, n_stage = 0, n_tile = 0;
+      TileRec nrec = tile_rec(0);
+      for (int i = 0; ok && i < my_tiles; ++i) {
+        const int t    = blockIdx.x + i * gridDim.x;
+        const TileS ti = decode_rec(nrec);
+        if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
+        const GGSwapProblemDev* pr = problems + ti.p;
+        ++n_tile;
+        const int ntok  = ti.ntok;
+        const int x_row = ti.x_row;
+        const int w_row = ti.n_tile * kWT;
+        // long token tiles take one 192-row box, short ones only the 32-row boxes they need
+        const bool big  = ntok > 4 * kXBoxSmall;
+        const int nbox  = (ntok + kXBoxSmall - 1) / kXBoxSmall;
+        const uint32_t xbytes = big ? (uint32_t)kXSlotBytes : (uint32_t)(nbox * kXBoxSmall * kRowBytes);
+        // weights: bytes per stage and coordinates in the weight tensor map
+        uint32_t wbytes;
+        int wx_step, wy;
+        if (ti.scheme == SCH_W8A8)          { wbytes = kWSlotBytes;     wx_step = 128; wy = w_row; }
+        else if (ti.scheme == SCH_FP16)     { wbytes = kWSlotBytes;     wx_step = 64;  wy = w_row; }
+        else if (ti.scheme == SCH_W4A4_XA)  { wbytes = kWSlotBytes / 2; wx_step = 64;  wy = w_row; }       // 64 packed bytes per row
+        else                                { wbytes = kWSlotBytes / 4; wx_step = 128; wy = w_row / 4; }   // w4a16: 32 packed rows x 128 B
+        const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;
+        for (int kb = 0; kb < ti.nkb; ++kb) {
+          const long long c0 = tick(prof_on);
+          const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag);
+          w_prod += tick(prof_on) - c0;
+          ++n_stage;
+          if (!got) {
+            report_s(status, 1, t);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&ctrl->full[stage]);
+          mbar_expect_tx(bar, wbytes + xbytes);
+          tma_load_2d(wslot(stage), &pr->tmW, bar, kb * wx_step, wy);
+          if (big) {
+            tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
+          } else {
+            for (int b = 0; b < nbox; ++b)
+              tma_load_2d(xslot(stage) + b * kXBoxSmall * kRowBytes, &pr->tmXs, bar, kb * xx_step, x_row + b * kXBoxSmall);
+          }
+          if (++stage == kStagesS) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (blockIdx.x == 0) {
+        status->prof[PROF_PROD_WAIT] = w_prod;
+        status->prof[PROF_TILES]     = n_tile;
+        status->prof[PROF_STAGES]    = n_stage;
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer (all lanes walk the loop and meet the named barriers, lane 0 issues) =====
+    int stage = 0;
+    int acc = 0;
+    long long w_oper = 0, w_acc = 0, w_issue = 0;
+    TileRec nrec = tile_rec(0);
+    for (int i = 0; i < my_tiles; ++i) {
+      const TileS ti = decode_rec(nrec);
+      if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
+      const long long ca = tick(prof_on);
+      if (i >= 2) nbar_sync(kBarAcc0 + acc, 160);     // the epilogue has drained this accumulator (tile i - 2)
+      w_acc += tick(prof_on) - ca;
+      const int npad        = (ti.ntok + 15) & ~15;
+      const uint32_t d_tmem = tmem_base + acc * kAccCols;
+      const bool is_int     = is_int_scheme(ti.scheme);
+      const bool from_tmem  = kCvt && is_cvt_scheme(ti.scheme);
+      const uint32_t idesc  = is_int ? idesc_i8(kWT, npad) : idesc_f16(kWT, npad);
+      const int variant     = (from_tmem ? 2 : 0) + (is_int ? 0 : 1);
+      const uint32_t a_tmem0 = tmem_base + kASlotCol0;
+      const uint32_t empty0  = smem_u32(&ctrl->empty[0]);
+      if (variant == 0)      mma_tile_loop<0>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      else if (variant == 1) mma_tile_loop<1>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      else if (variant == 2) mma_tile_loop<2>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      else                   mma_tile_loop<3>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      if (lane == 0) mma_commit(smem_u32(&ctrl->tfull[acc]));
+      __syncwarp();
+      acc ^= 1;
+    }
+    // consume the "drained" arrivals of the last two tiles, so that no named barrier is left half-way
+    for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(kBarAcc0 + (i & 1), 160);
+    if (blockIdx.x == 0 && lane == 0) {
+      status->prof[PROF_MMA_WAIT_OPER] = w_oper;
+      status->prof[PROF_MMA_WAIT_ACC]  = w_acc;
+      status->prof[PROF_MMA_ISSUE]     = w_issue;
+    }
+  } else if (warp < 6) {
+    // ===== epilogue (TMEM lane quarter = warp % 4; lane = output channel, columns = tokens) =====
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    __half* saw        = ctrl->sa_stage[warp - 2];
+    const uint32_t stg = epi_base + (warp - 2) * kEpiStageS;
+    long long w_epi = 0, w_store = 0;
+    bool dead = false;   // a wait ran out: walk the remaining tiles without waiting or working
+    TileRec nrec = tile_rec(0);
+    for (int i = 0; i < my_tiles; ++i) {
+      const int t    = blockIdx.x + i * gridDim.x;
+      const TileS ti = decode_rec(nrec);
+      if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
+      const GGSwapProblemDev* pr = problems + ti.p;
+      const int ntok      = ti.ntok;
+      const int64_t grow0 = ti.x_row;   // buffer row of token 0 of the tile
+      const int N = pr->N, ldc = pr->ldc, out_mode = pr->out_mode;
+      const bool is_int   = is_int_scheme(ti.scheme);
+      const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
+      const int n_ch      = ti.n_tile * kWT + q * 32 + lane;                                // this thread's channel
+      __half2 sb2 = __float2half2_rn(0.f);
+      if (!dead && is_int && out_mode == OUT_FP16) {
+        // everything that does not depend on the accumulator is fetched before waiting for it
+        if (n_ch < N) sb2 = __half2half2(__ldg(pr->scale_b + n_ch));
+        __syncwarp();
+        for (int i = lane; i < kTT + 32; i += 32)
+          saw[i] = (i < ntok) ? pr->scale_a[(grow0 + i) * pr->sa_stride] : __float2half(0.f);
+        __syncwarp();
+      }
+      const long long c0 = tick(prof_on);
+      if (!dead) {
+        const bool ok = warp_wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag, lane);
+        if (!ok) {
+          if (lane == 0) report_s(status, 4, t);
+          dead = true;
+        }
+      }
+      if (dead) {
+        // keep the MMA warp's bar.sync on this accumulator balanced, do nothing else
+        nbar_arrive(kBarAcc0 + acc, 160);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        continue;
+      }
+      const long long c1 = tick(prof_on);
+      w_epi += c1 - c0;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
+      const int nchunk     = (ntok + 31) >> 5;
+#pragma unroll 1
+      for (int ch = 0; ch < nchunk; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + ch * 32, v);
+        tmem_ld_wait();
+        if (out_mode == OUT_ACC) {
+          // raw accumulators (int32 / fp32): element (token, channel), used by the bit-exactness tests
+          uint32_t* dst = reinterpret_cast<uint32_t*>(pr->C);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tk = ch * 32 + j;
+            if (tk < ntok && n_ch < N)
+              dst[(grow0 + tk) * ldc + n_ch] = is_int ? (uint32_t)((int)v[j] >> acc_shift) : v[j];
+          }
+          continue;
+        }
+        // fp16 results of this channel for 32 tokens, two tokens per word
+        uint32_t h[16];
+        if (is_int) {
+          // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
+          const uint4* sap = reinterpret_cast<const uint4*>(saw + ch * 32);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint4 sv    = sap[g];
+            const __half2* s2 = reinterpret_cast<const __half2*>(&sv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j    = g * 4 + e;
+              const float2 p = __half22float2(__hmul2(s2[e], sb2));
+              const float f0 = (float)((int)v[2 * j] >> acc_shift) * p.x;
+              const float f1 = (float)((int)v[2 * j + 1] >> acc_shift) * p.y;
+              __half2 r      = __floats2half2_rn(f0, f1);
+              h[j]           = *reinterpret_cast<uint32_t*>(&r);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __half2 r = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+            h[j]      = *reinterpret_cast<uint32_t*>(&r);
+          }
+        }
+        // transpose through the warp's 2 KiB buffer: row = token pair (128 bytes = 32 channels x 2 tokens),
+        // 16-byte slots XOR-swizzled by the row so that writes and reads are conflict-free
+        __syncwarp();   // the previous chunk's reads of the buffer are done
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sts32(stg + j * 128 + (((lane >> 2) ^ (j & 7)) << 4) + (lane & 3) * 4, h[j]);
+        __syncwarp();
+        const int p8 = lane & 3;   // which 8 channels of the warp's 32
+#pragma unroll
+        for (int rd = 0; rd < 2; ++rd) {
+          const int tp   = (lane >> 2) + 8 * rd;
+          const uint4 a0 = lds128(stg + tp * 128 + (((2 * p8) ^ (tp & 7)) << 4));
+          const uint4 a1 = lds128(stg + tp * 128 + (((2 * p8 + 1) ^ (tp & 7)) << 4));
+          uint4 lo, hi;   // lo: token 2*tp, hi: token 2*tp + 1; 8 consecutive channels each
+          lo.x = __byte_perm(a0.x, a0.y, 0x5410); hi.x = __byte_perm(a0.x, a0.y, 0x7632);
+          lo.y = __byte_perm(a0.z, a0.w, 0x5410); hi.y = __byte_perm(a0.z, a0.w, 0x7632);
+          lo.z = __byte_perm(a1.x, a1.y, 0x5410); hi.z = __byte_perm(a1.x, a1.y, 0x7632);
+          lo.w = __byte_perm(a1.z, a1.w, 0x5410); hi.w = __byte_perm(a1.z, a1.w, 0x7632);
+          const int tk   = ch * 32 + 2 * tp;
+          const int ncol = ti.n_tile * kWT + q * 32 + 8 * p8;
+          __half* dst    = reinterpret_cast<__half*>(pr->C) + (grow0 + tk) * ldc + ncol;
+          if (ncol < N) {
+            if (tk < ntok) *reinterpret_cast<uint4*>(dst) = lo;
+            if (tk + 1 < ntok) *reinterpret_cast<uint4*>(dst + ldc) = hi;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      nbar_arrive(kBarAcc0 + acc, 160);
+      w_store += tick(prof_on) - c1;
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (blockIdx.x == 0 && warp == 2 && lane == 0) {
+      status->prof[PROF_EPI_WAIT]  = w_epi;
+      status->prof[PROF_EPI_STORE] = w_store;
+    }
+  } else if (warp == 6) {
+    // ===== watcher: forwards "stage ready" from the mbarriers to the MMA warp's named barriers =====
+    int stage = 0;
+    uint32_t phase = 0;
+    bool dead = false;
+    TileRec nrec = tile_rec(0);
+    for (int i = 0; i < my_tiles; ++i) {
+      const int t    = blockIdx.x + i * gridDim.x;
+      const TileS ti = decode_rec(nrec);
+      if (i + 1 < my_tiles) nrec = tile_rec(i + 1);
+      for (int kb = 0; kb < ti.nkb; ++kb) {
+        if (!dead) {
+          bool ok = warp_wait_bar(smem_u32(&ctrl->full[stage]), phase, abort_flag, lane);
+          // with converter warps in the CTA, afull[s] completes on every stage (converted weights in place,
+          // or nothing to convert)
+          if (ok && kCvt) ok = warp_wait_bar(smem_u32(&ctrl->afull[stage]), phase, abort_flag, lane);
+          if (!ok) {
+            if (lane == 0) report_s(status, 3, t);
+            dead = true;
+          }
+        }
+        nbar_arrive(kBarStage0 + stage, 64);   // always: the MMA warp's bar.sync must complete
+        if (++stage == kStagesS) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (kCvt) {
+    // ===== converters: two groups of four warps take alternate stages, so that the chain of shared-memory
+    // round trips of one stage (wait, load, store to tensor memory, arrive) overlaps the next stage's.
+    // Thread = weight row (channel) 32*q + lane of the tile = its TMEM lane; it converts the row's 128 bytes
+    // of K of the stage into A slot `stage`.  The slot is free when full[stage] has completed: the producer
+    // refilled the stage only after the MMAs of its previous use (which read the slot) had completed.
+    const int q     = warp & 3;               // TMEM lane quarter this warp may write
+    const int group = (warp - 7) / kCvtGroup;
+    const int row   = q * 32 + lane;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t it = 0;                          // stages walked so far
+    bool alive = true;
+    long long w_cwait = 0, w_cwork = 0;
+    TileRec nrec = tile_rec(0);
+    for (int i = 0; alive && i < my_tiles; ++i) {
+      const int t    = blockIdx.x + i * gridDim.x;
+      const TileS ti = decode_rec(nrec);
+      if (i + 1 < my_tiles) nrec = tile_rec(i + 1);
+      const GGSwapProblemDev* pr = problems + ti.p;
+      const bool convert         = is_cvt_scheme(ti.scheme);
+      const int N                = pr->N;
+      const int gn               = ti.n_tile * kWT + row;
+      for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
+        const int s_cur       = stage;
+        const uint32_t ph_cur = phase;
+        if (++stage == kStagesS) { stage = 0; phase ^= 1u; }
+        if ((int)(it & 1u) != group) continue;   // the other group's stage
+        __half2 sz = __float2half2_rn(0.f);
+        if (ti.scheme == SCH_W4A16G128 && gn < N) {
+          // (scale, zero) pairs, [K/128][N][2] fp16; one group of 128 k spans two 64-k stages
+          sz = __ldg(reinterpret_cast<const __half2*>(pr->scale_b) + (int64_t)(kb >> 1) * N + gn);
+        }
+        const long long c0 = tick(prof_on);
+        const bool ok = warp_wait_bar(smem_u32(&ctrl->full[s_cur]), ph_cur, abort_flag, lane);
+        const long long c1 = tick(prof_on);
+        w_cwait += c1 - c0;
+        if (!ok) {
+          if (lane == 0) report_s(status, convert ? 5 : 6, t);
+          alive = false;
+          break;
+        }
+        if (convert) {
+          tc_fence_after_sync();
+          uint32_t o[32];
+          if (ti.scheme == SCH_W4A4_XA) {
+            // packed row: 64 bytes, 16-byte chunks swizzled by (row >> 1) & 3 (64-byte swizzle of the tensor map).
+            // Chunk c becomes 32 int8 bytes: its high nibbles, then its low nibbles, each moved to the top of a
+            // byte (code q -> byte 16*q; the accumulator is shifted back in the epilogue).
+            const uint32_t src = wslot(s_cur) + row * 64;
+            const int sw       = (row >> 1) & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 w = lds128(src + ((j ^ sw) << 4));
+              o[8 * j + 0] = w.x & 0xF0F0F0F0u; o[8 * j + 4] = (w.x << 4) & 0xF0F0F0F0u;
+              o[8 * j + 1] = w.y & 0xF0F0F0F0u; o[8 * j + 5] = (w.y << 4) & 0xF0F0F0F0u;
+              o[8 * j + 2] = w.z & 0xF0F0F0F0u; o[8 * j + 6] = (w.z << 4) & 0xF0F0F0F0u;
+              o[8 * j + 3] = w.w & 0xF0F0F0F0u; o[8 * j + 7] = (w.w << 4) & 0xF0F0F0F0u;
+            }
+          } else {
+            // w4a16 g128: channel n = 32*q + 8*f + r lives in packed row 8*q + r; the 16-k block kb16 of this
+            // stage is the 16-byte chunk 2*kb16 + (f >> 1) (128-byte swizzle: XOR r), nibble 2*(f & 1) + c of
+            // word d holds k = 16*kb16 + 8*c + d.
+            const int f = lane >> 3, r = lane & 7;
+            const uint32_t src = wslot(s_cur) + (8 * q + r) * 128;
+            const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+#pragma unroll
+            for (int kb16 = 0; kb16 < 4; ++kb16) {
+              const uint4 w = lds128(src + (((2 * kb16 + (f >> 1)) ^ r) << 4));
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                const int nib = 2 * (f & 1) + c;
+                o[8 * kb16 + 4 * c + 0] = dequant_pair(w.x, nib, s2, z2);
+                o[8 * kb16 + 4 * c + 1] = dequant_pair(w.y, nib, s2, z2);
+                o[8 * kb16 + 4 * c + 2] = dequant_pair(w.z, nib, s2, z2);
+                o[8 * kb16 + 4 * c + 3] = dequant_pair(w.w, nib, s2, z2);
+              }
+            }
+          }
+          tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + kASlotCol0 + s_cur * kASlotCols, o);
+        }
+        // the stage's packed weights are in registers (or not needed): release the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->empty[s_cur]));
+        if (convert) {
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          w_cwork += tick(prof_on) - c1;
+        }
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->afull[s_cur]));
+      }
+    }
+    if (blockIdx.x == 0 && warp == 7 && lane == 0) {
+      status->prof[PROF_CVT_WAIT] = w_cwait;
+      status->prof[PROF_CVT_WORK] = w_cwork;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncthreads();
+  if (blockIdx.x == 0 && tid == 0) status->prof[PROF_TOTAL] = clock64() - prof_t0;
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+cudaError_t gg_configure_swap() {
+  cudaError_t e = cudaFuncSetAttribute(gg_swap_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gg_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
+}
+
+void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
+                    cudaStream_t stream) {
+  if (cvt_mode) gg_swap_kernel<1><<<num_ctas, CfgS<1>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
+  else          gg_swap_kernel<0><<<num_ctas, CfgS<0>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
+}
+
+}  // namespace mxb

@@ -50,7 +50,27 @@ struct alignas(128) GGProblemDev {
 };
 static_assert(sizeof(GGProblemDev) == 384, "GGProblemDev layout");
 
-// Workspace: [GGStatus (256 B)] [GGProblemDev x count]
+// The same problem as seen by the kernel with swapped operands (gg_swap_kernel.cu): the weights are the
+// M side of the MMA (tiles of 128 output channels), the tokens the N side (tiles of up to 176 rows).
+constexpr int kWT = 128;   // output channels per tile (tcgen05 M)
+constexpr int kTT = 176;   // tokens per tile (tcgen05 N, any multiple of 16 up to this)
+constexpr int kXBoxSmall = 32;   // rows of the small activation box (short token tiles load only what they need)
+struct alignas(128) GGSwapProblemDev {
+  CUtensorMap tmW;    // weights: 128 channels x one stage of K (packed for the 4-bit schemes)
+  CUtensorMap tmX;    // activations: kTT rows x 128 bytes of K
+  CUtensorMap tmXs;   // activations: kXBoxSmall rows x 128 bytes of K
+  const __half* scale_a;
+  const __half* scale_b;
+  void* C;
+  const int* m_dev;
+  const int* row0_dev;
+  int M, N, K, row0;
+  int scheme, out_mode, ldc, sa_stride;
+  int pad[14];
+};
+static_assert(sizeof(GGSwapProblemDev) == 512, "GGSwapProblemDev layout");
+
+// Workspace: [GGStatus (256 B)] [GGProblemDev x count] [GGSwapProblemDev x count]
 struct alignas(256) GGStatus {
   int error;       // 0 = ok; otherwise an MXMOE_DEVERR_* code
   int where;       // role << 24 | tile index
@@ -90,5 +110,10 @@ cudaError_t gg_configure_single();
 cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
                            cudaStream_t stream);
 cudaError_t gg_configure_pair();
+// kernel with swapped operands (gg_swap_kernel.cu): weights from tensor memory / shared memory as the M side,
+// token tiles of up to 176 rows as the N side; cvt_mode 0 or 1
+void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
+                    cudaStream_t stream);
+cudaError_t gg_configure_swap();
 
 }  // namespace mxb

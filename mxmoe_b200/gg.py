@@ -95,9 +95,14 @@ class GroupedGemm:
     def kept(self) -> int:
         return self._plan.count
 
-    def run(self, num_ctas: int = 0) -> None:
+    def run(self, num_ctas: int = 0, kernel: str | None = None) -> None:
+        """Launch; ``kernel`` in KERNELS names the kernel, None leaves the choice to the library."""
         with torch.cuda.device(self.device):
-            _lib.check(_lib.lib().mxmoe_gg_run(self._ws, C.byref(self._plan), num_ctas, current_stream_ptr()))
+            if kernel is None:
+                _lib.check(_lib.lib().mxmoe_gg_run(self._ws, C.byref(self._plan), num_ctas, current_stream_ptr()))
+            else:
+                _lib.check(_lib.lib().mxmoe_gg_run_kernel(self._ws, C.byref(self._plan), KERNELS[kernel], num_ctas,
+                                                          current_stream_ptr()))
 
     def check(self) -> None:
         """Synchronise the current stream and raise if the kernel recorded an error."""
@@ -105,8 +110,10 @@ class GroupedGemm:
             _lib.check(_lib.lib().mxmoe_gg_check(self._ws, current_stream_ptr()))
 
 
+KERNELS = {"default": 0, "single": 1, "pair": 2, "swap": 3}
+
 PROF_NAMES = ("total", "producer_wait", "mma_wait_operands", "mma_wait_accumulator", "mma_issue", "epilogue_wait",
-              "epilogue_store", "converter_wait", "converter_work", "tiles", "stages")
+              "epilogue_store", "converter_wait", "converter_work", "tiles", "stages", "mma_gap")
 
 
 def profile(g: "GroupedGemm") -> dict:

@@ -18,13 +18,12 @@ pytestmark = pytest.mark.gpu
 REL_L2 = 1e-3
 
 
-@pytest.fixture(autouse=True, params=["pair", "single"])
-def gg_kernel(request):
-    """Every test of this file runs once per kernel: CTA pairs (256 x 256 tiles, cta_group::2) and
-    single CTAs (128 x 256 tiles)."""
-    util.DEFAULT_CTAS = -(1 << 20) if request.param == "pair" else 1 << 20
+@pytest.fixture(autouse=True, params=["swap", "pair", "single"])
+def gg_kernel(request, monkeypatch):
+    """Every test of this file runs once per kernel: swapped operands (128 channels x 192 tokens, 4-bit weights
+    through tensor memory), CTA pairs (256 x 256 tiles, cta_group::2) and single CTAs (128 x 256 tiles)."""
+    monkeypatch.setenv("MXMOE_GG_KERNEL", request.param)
     yield request.param
-    util.DEFAULT_CTAS = 0
 
 # (M, N, K): one tile / one k-block; ragged M; ragged N tile; several k-blocks; layer shapes
 SHAPES_INT = [(128, 256, 128), (1, 256, 128), (17, 256, 256), (129, 512, 384), (300, 2816, 2048), (77, 2048, 1408),
