@@ -175,6 +175,61 @@ def run_reference_arm(args, spec):
 
 
 # --------------------------------------------------------------------------- GPU arm
+def class_pass(layer, spec, counts, peaks, reps: int = 10):
+    """Per-class roofline of the grouped GEMM: every (expert, linear block) problem is classified compute- or
+    memory-bound from its algorithmic flops and bytes against the measured peaks, and each class's problem
+    subset is launched alone (the other experts' device-side row counts zeroed) and timed with CUDA events."""
+    if spec.shared_inter:
+        return None   # the shared expert's problems have no device-side row count to mask
+    core, E = layer._core, spec.num_experts
+    orig = layer.counts.clone()
+    bw = peaks["hbm_gbs"] * 1e9
+    out = {}
+    for cls in ("compute", "memory"):
+        out[cls] = {"flops": 0.0, "bytes": 0.0, "ms": 0.0, "problems": 0}
+    try:
+        for gg, block, n, k in ((core.gg1, layer.gate_up, 2 * spec.inter, spec.hidden),
+                                (core.gg2, layer.down, spec.hidden, spec.inter)):
+            mask = {"compute": [0] * E, "memory": [0] * E}
+            for e in range(E):
+                m = counts[e]
+                if m == 0:
+                    continue
+                w = block[e]
+                a_bits = w.qparams[0]
+                peak = peaks["bf16_tflops"] * 1e12 * (2.0 if a_bits < 16 else 1.0)
+                fl = 2.0 * m * n * k
+                by = m * k * a_bits / 8 + w.nbytes() + m * n * 2 + (m * 2 if a_bits < 16 else 0)
+                cls = "compute" if fl / peak > by / bw else "memory"
+                mask[cls][e] = 1
+                out[cls]["flops"] += fl
+                out[cls]["bytes"] += by
+                out[cls]["problems"] += 1
+                out[cls].setdefault("peak_tflops", 0.0)
+                out[cls]["peak_tflops"] = max(out[cls]["peak_tflops"], peak / 1e12)
+            for cls in ("compute", "memory"):
+                if not any(mask[cls]):
+                    continue
+                layer.counts.copy_(orig * torch.tensor(mask[cls], dtype=orig.dtype, device=orig.device))
+                for _ in range(2):
+                    gg.run()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    gg.run()
+                e1.record()
+                torch.cuda.synchronize()
+                out[cls]["ms"] += e0.elapsed_time(e1) / reps
+    finally:
+        layer.counts.copy_(orig)
+    for cls, o in out.items():
+        if o["ms"] > 0:
+            o["tflops"] = o["flops"] / (o["ms"] * 1e-3) / 1e12
+            o["gbs"] = o["bytes"] / (o["ms"] * 1e-3) / 1e9
+            o["frac"] = o["tflops"] / o["peak_tflops"] if cls == "compute" else o["gbs"] / peaks["hbm_gbs"]
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,7 +398,7 @@ def main():
         achieved = flops_launch / (gemm_ms * 1e-3) / 1e12
         bytes_launch = layer.gemm_bytes(counts) / 2
         line["roofline"] = {
-            "bound": "tensor", "kernel": "gg_persistent_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "bound": "tensor", "kernel": "gg_swap_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "traffic": None,
             "peak_source": f"{peaks['source']} cuBLAS bf16 burst x{2 if int_kind else 1} (tcgen05 kind::i8 issues at twice the bf16 rate)",
             "launch_ms": {"gate_up": d1, "down": d2},
@@ -353,6 +408,8 @@ def main():
             "hbm_peak_gbs": peaks["hbm_gbs"],
         }
         line["gemm_only_tflops"] = flops_rank / ((d1 + d2) * 1e-3) / 1e12
+        # compute-bound and memory-bound problems timed apart (each class's experts launched alone)
+        line["roofline"]["classes"] = class_pass(layer, spec, counts, peaks)
         if not args.no_cpu and rank == 0:
             threads = os.cpu_count() or 1
             tf, secs, desc = cpu_expert_loop(spec, args.cpu_budget, threads)

@@ -75,6 +75,11 @@ typedef struct mxmoe_gg_problem {
   int32_t sa_stride; /* distance between consecutive per-token scales in fp16 elements; 0 or 1 = contiguous */
   int32_t a_expanded; /* w4a4 only: A holds one byte per code, the byte 16*q, in the order the kernel's own
                          int4 -> int8 unpacking produces (see mxmoe_token_quant_args.q4x); A is then [M, K] bytes */
+  int32_t reserved_;
+  const int32_t* c_row0_dev; /* optional: the rows of C start at *c_row0_dev instead of at row0 (A and scale_a keep
+                                row0).  Lets an expert-parallel rank store a segment's results straight into the
+                                buffer of the rank the rows came from, at their place in that rank's order; C may
+                                then be peer memory (plain stores).  Not available for packed 4-bit activations. */
 } mxmoe_gg_problem;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -96,6 +101,8 @@ size_t mxmoe_gg_workspace_bytes(int problem_count);
 typedef struct mxmoe_gg_plan {
   int32_t count;     /* problems kept (empty ones are dropped) */
   int32_t needs_cvt; /* kernel variant: 0 no 4-bit operand, 1 4-bit weights only, 2 packed 4-bit activations too */
+  int32_t flags;     /* bit 0: a problem redirects its C rows (c_row0_dev): only the SWAP kernel can run it */
+  int32_t reserved_;
 } mxmoe_gg_plan;
 
 /* Validate the problem list, encode the TMA descriptors on the host and copy the
@@ -181,6 +188,8 @@ typedef struct mxmoe_act_args {
   int32_t rotate;             /* quant_inp_act only: rotate rows by diag(signs) H_k / sqrt(k) first */
   int32_t rec_stride;         /* > 0: record layout (see below), in fp16 elements */
   int32_t rec_scale_off;      /* record layout: offset of the scale inside the record, or < 0 for s_store[row] */
+  const int32_t* rows_dev;    /* optional, silu_mul_then_quant without shared rows: live row count in device memory;
+                                 rows at or beyond it are skipped (rows_routed == rows_total is then an upper bound) */
 } mxmoe_act_args;
 
 /* Gather rows of `in` ([T,k] fp16) by expert, optionally rotate, quantise per
@@ -262,6 +271,41 @@ int mxmoe_route_topk_static(const mxmoe_route_args* args, void* stream);
  * mxmoe/kernels/src/ref_bind.cu:66); topk_weights may be NULL (all ones). */
 int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk_weights, const void* y_shared,
                        void* out, int num_tokens, int topk, int hidden, void* stream);
+
+/* ---- expert parallel ----------------------------------------------------------
+ * No reference counterpart: the reference has no distributed code.  One process per GPU; experts are
+ * numbered so that rank r owns the contiguous range [range_lo[r], range_lo[r+1]).  mxmoe_ep_plan turns the
+ * all-gathered routing counts into this rank's receive-side segment tables and send-side row offsets, on
+ * the device; mxmoe_ep_dispatch_rows writes every quantised row of this rank (packed row + scale, one
+ * record) straight into the receive store of the rank that owns its expert (plain stores to peer memory). */
+typedef struct mxmoe_ep_plan_args {
+  const int32_t* counts_all; /* [world][num_experts] */
+  const int32_t* range_lo;   /* [world + 1] */
+  int32_t world, rank, num_experts, experts_local, recv_capacity;
+  int32_t reserved_;
+  int32_t* seg_m;           /* [world * experts_local] rows of segment (source rank, local expert), source-major */
+  int32_t* seg_row0;        /* first row of the segment in this rank's receive store */
+  int32_t* seg_src_row0;    /* first row of the same rows in the source rank's expert-sorted order */
+  int32_t* recv_row_expert; /* [recv_capacity] expert of every received row */
+  int32_t* total_recv;      /* [0] rows received (clamped), [1] rows wanted when that exceeded the capacity */
+  int32_t* dst_row0;        /* [num_experts] first row of this rank's rows for expert e in its owner's store */
+  int32_t* exp_owner;       /* [num_experts] */
+} mxmoe_ep_plan_args;
+
+typedef struct mxmoe_ep_dispatch_args {
+  const uint64_t* peer_base;   /* [world] device array: receive store of every rank as mapped here */
+  const int32_t* row_expert;   /* [rows] */
+  const int64_t* row_token;    /* [rows] */
+  const int32_t* exp_row_start;
+  const int32_t* exp_qtag;     /* activation format per expert, as in mxmoe_act_args */
+  const int32_t* dst_row0;     /* from mxmoe_ep_plan */
+  const int32_t* exp_owner;    /* from mxmoe_ep_plan */
+  int32_t rows, k, rec_bytes, scale_off_bytes, recv_capacity;
+  int32_t reserved_;
+} mxmoe_ep_dispatch_args;
+
+int mxmoe_ep_plan(const mxmoe_ep_plan_args* args, void* stream);
+int mxmoe_ep_dispatch_rows(const mxmoe_ep_dispatch_args* args, const mxmoe_token_quant_args* stores, void* stream);
 
 #ifdef __cplusplus
 }

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libmxmoe_b200.so")
 # every symbol include/mxmoe_b200.h declares
 EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
-    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile",
+    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_dispatch_rows", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows",
     "mxmoe_silu_mul_then_quant",
     "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
@@ -41,12 +41,31 @@ class GGProblem(C.Structure):
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
         ("a_rows", C.c_int32), ("row0", C.c_int32), ("ldc", C.c_int32),
         ("q", QParams), ("out_mode", C.c_int32), ("lda_bytes", C.c_int32), ("sa_stride", C.c_int32),
-        ("a_expanded", C.c_int32),
+        ("a_expanded", C.c_int32), ("reserved_", C.c_int32), ("c_row0_dev", C.c_void_p),
     ]
 
 
 class GGPlan(C.Structure):
-    _fields_ = [("count", C.c_int32), ("needs_cvt", C.c_int32)]
+    _fields_ = [("count", C.c_int32), ("needs_cvt", C.c_int32), ("flags", C.c_int32), ("reserved_", C.c_int32)]
+
+
+class EpPlanArgs(C.Structure):
+    _fields_ = [
+        ("counts_all", C.c_void_p), ("range_lo", C.c_void_p),
+        ("world", C.c_int32), ("rank", C.c_int32), ("num_experts", C.c_int32), ("experts_local", C.c_int32),
+        ("recv_capacity", C.c_int32), ("reserved_", C.c_int32),
+        ("seg_m", C.c_void_p), ("seg_row0", C.c_void_p), ("seg_src_row0", C.c_void_p), ("recv_row_expert", C.c_void_p),
+        ("total_recv", C.c_void_p), ("dst_row0", C.c_void_p), ("exp_owner", C.c_void_p),
+    ]
+
+
+class EpDispatchArgs(C.Structure):
+    _fields_ = [
+        ("peer_base", C.c_void_p), ("row_expert", C.c_void_p), ("row_token", C.c_void_p), ("exp_row_start", C.c_void_p),
+        ("exp_qtag", C.c_void_p), ("dst_row0", C.c_void_p), ("exp_owner", C.c_void_p),
+        ("rows", C.c_int32), ("k", C.c_int32), ("rec_bytes", C.c_int32), ("scale_off_bytes", C.c_int32),
+        ("recv_capacity", C.c_int32), ("reserved_", C.c_int32),
+    ]
 
 
 class ActArgs(C.Structure):
@@ -57,6 +76,7 @@ class ActArgs(C.Structure):
         ("signs", C.c_void_p),
         ("k", C.c_int32), ("k_shared", C.c_int32), ("rows_routed", C.c_int32), ("rows_total", C.c_int32),
         ("num_experts", C.c_int32), ("rotate", C.c_int32), ("rec_stride", C.c_int32), ("rec_scale_off", C.c_int32),
+        ("rows_dev", C.c_void_p),
     ]
 
 
@@ -103,6 +123,8 @@ def lib() -> C.CDLL:
         l.mxmoe_silu_mul_then_quant.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_quant_tokens.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_gather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        l.mxmoe_ep_plan.argtypes = [C.c_void_p, C.c_void_p]
+        l.mxmoe_ep_dispatch_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_route_workspace_bytes.restype = C.c_size_t
         l.mxmoe_route_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
         l.mxmoe_route_topk.argtypes = [C.c_void_p, C.c_void_p]

@@ -366,7 +366,9 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_in_blk = warp / kWarps, w = warp % kWarps;
   const int row     = blockIdx.x * (8 / kWarps) + row_in_blk;
-  const bool row_ok = row < a.rows_total;
+  const int live    = a.rows_dev ? min(a.rows_total, __ldg(a.rows_dev)) : a.rows_total;
+  if (blockIdx.x * (8 / kWarps) >= live) return;   // the whole block lies beyond the live rows
+  const bool row_ok = row < live;
   RowInfo ri{0, 0, nullptr, nullptr};
   if (row_ok) ri = locate_row(a, row);
   const int nchunk = ri.k >> 3;

@@ -18,6 +18,7 @@
 #include "../../include/mxmoe_b200.h"
 #include "act_kernels.h"
 #include "gg_types.h"
+#include "ep_kernels.h"
 #include "route_kernels.h"
 
 namespace {
@@ -223,6 +224,7 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   o->scale_a = d.scale_a; o->scale_b = d.scale_b; o->C = d.C; o->m_dev = d.m_dev; o->row0_dev = d.row0_dev;
   o->M = d.M; o->N = d.N; o->K = d.K; o->row0 = d.row0;
   o->scheme = d.scheme; o->out_mode = d.out_mode; o->ldc = d.ldc; o->sa_stride = d.sa_stride;
+  o->c_row0_dev = p.c_row0_dev;
   return MXMOE_OK;
 }
 
@@ -280,17 +282,23 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   std::vector<mxb::GGSwapProblemDev> swp((size_t)problem_count);
   if (problem_count) std::memset(swp.data(), 0, swp.size() * sizeof(mxb::GGSwapProblemDev));
   int kept = 0, needs_cvt = 0;
+  bool redirect = false;
   for (int i = 0; i < problem_count; ++i) {
     if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
     rc = build_problem(st->encode, problems[i], i, dev + kept);
     if (rc) return rc;
     rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept]);
     if (rc) return rc;
+    if (dev[kept].scheme == mxb::SCH_W4A4 && problems[i].c_row0_dev)
+      return fail(MXMOE_ERR_UNSUPPORTED, "problem %d: c_row0_dev is not available with packed 4-bit activations", i);
+    if (problems[i].c_row0_dev) redirect = true;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
     ++kept;
   }
   status->pad[0]    = getenv("MXMOE_GG_PROFILE") ? atoi(getenv("MXMOE_GG_PROFILE")) : 0;   // per-role counters on
+  if (redirect && needs_cvt == 2)
+    return fail(MXMOE_ERR_UNSUPPORTED, "c_row0_dev cannot be combined with packed 4-bit activations in one launch");
   status->count     = kept;
   status->needs_cvt = needs_cvt;
   // pageable source: the runtime stages the bytes before returning, so `host` may go out of scope
@@ -302,6 +310,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   if (plan) {
     plan->count     = kept;
     plan->needs_cvt = needs_cvt;
+    plan->flags     = redirect ? 1 : 0;
+    plan->reserved_ = 0;
   }
   return MXMOE_OK;
 }
@@ -321,6 +331,9 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   auto* swp    = reinterpret_cast<const mxb::GGSwapProblemDev*>(base + sizeof(mxb::GGProblemDev) * (size_t)count);
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (kernel == GGK_DEFAULT) kernel = default_kernel();
+  if (plan->flags & 1) {
+    if (kernel != GGK_SWAP) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows run on the SWAP kernel only");
+  }
   if (kernel == GGK_SWAP && needs_cvt == 2) kernel = GGK_SINGLE;   // packed 4-bit activations
   int n = num_ctas;
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
@@ -451,6 +464,11 @@ static int to_act_args(const mxmoe_act_args* a, mxb::ActArgs* o, bool silu) {
   o->rotate = silu ? 0 : a->rotate;
   o->rec_stride = a->rec_stride > 0 ? a->rec_stride : 0;
   o->rec_scale_off = a->rec_scale_off;
+  o->rows_dev = nullptr;
+  if (a->rows_dev) {
+    if (!silu || has_shared) return fail(MXMOE_ERR_UNSUPPORTED, "rows_dev is for silu_mul_then_quant without shared-expert rows");
+    o->rows_dev = a->rows_dev;
+  }
   if (o->rec_stride > 0) {
     const int kmax = a->k > ks ? a->k : ks;
     if (o->rec_stride % 8) return fail(MXMOE_ERR_INVALID, "rec_stride must be a multiple of 8 fp16 elements");
@@ -579,6 +597,41 @@ int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk
   if (num_tokens < 0 || topk <= 0 || hidden <= 0 || hidden % 8) return fail(MXMOE_ERR_INVALID, "bad combine shape T=%d topk=%d H=%d (H %% 8 == 0)", num_tokens, topk, hidden);
   CUDA_TRY(mxb::launch_combine(y, slot_row, topk_weights, y_shared, out, num_tokens, topk, hidden,
                                static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+
+int mxmoe_ep_plan(const mxmoe_ep_plan_args* a, void* stream) {
+  if (!a) return fail(MXMOE_ERR_INVALID, "null args");
+  if (a->world <= 0 || a->world > 64 || a->rank < 0 || a->rank >= a->world || a->num_experts <= 0 ||
+      a->num_experts > 4096 || a->experts_local < 0 || a->recv_capacity < 0)
+    return fail(MXMOE_ERR_INVALID, "bad expert-parallel shape world=%d rank=%d experts=%d local=%d capacity=%d", a->world,
+                a->rank, a->num_experts, a->experts_local, a->recv_capacity);
+  if (!a->counts_all || !a->range_lo || !a->seg_m || !a->seg_row0 || !a->seg_src_row0 || !a->recv_row_expert ||
+      !a->total_recv || !a->dst_row0 || !a->exp_owner)
+    return fail(MXMOE_ERR_INVALID, "null table");
+  static_assert(sizeof(mxmoe_ep_plan_args) == sizeof(mxb::EpPlanArgs), "plan args layout");
+  mxb::EpPlanArgs k;
+  std::memcpy(&k, a, sizeof(k));
+  CUDA_TRY(mxb::launch_ep_plan(k, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+int mxmoe_ep_dispatch_rows(const mxmoe_ep_dispatch_args* a, const mxmoe_token_quant_args* stores, void* stream) {
+  if (!a) return fail(MXMOE_ERR_INVALID, "null args");
+  mxb::TokenQuantArgs t;
+  int rc = to_token_args(stores, &t);
+  if (rc) return rc;
+  if (a->rows < 0 || a->k != t.k || a->rec_bytes <= 0 || a->rec_bytes % 16 || a->scale_off_bytes < 0 ||
+      a->scale_off_bytes + 2 > a->rec_bytes || a->scale_off_bytes % 2)
+    return fail(MXMOE_ERR_INVALID, "bad dispatch shape rows=%d k=%d rec_bytes=%d scale_off=%d", a->rows, a->k, a->rec_bytes,
+                a->scale_off_bytes);
+  if (!a->peer_base || !a->row_expert || !a->row_token || !a->exp_row_start || !a->exp_qtag || !a->dst_row0 || !a->exp_owner)
+    return fail(MXMOE_ERR_INVALID, "null table");
+  static_assert(sizeof(mxmoe_ep_dispatch_args) == sizeof(mxb::EpDispatchArgs), "dispatch args layout");
+  mxb::EpDispatchArgs k;
+  std::memcpy(&k, a, sizeof(k));
+  CUDA_TRY(mxb::launch_ep_dispatch(k, t, static_cast<cudaStream_t>(stream)));
   return MXMOE_OK;
 }
 

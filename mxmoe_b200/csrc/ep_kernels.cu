@@ -1,0 +1,110 @@
+// Expert-parallel exchange without the host: the plan of a step (who sends how many rows where) is computed
+// on the device from the all-gathered routing counts, and the quantised rows are written straight into the
+// receive stores of the GPUs that own their experts (plain stores to peer memory over NVLink; no TMA and no
+// multicast is involved).  The reference has no distributed code; this is the multi-GPU form of the path.
+#include "ep_kernels.h"
+
+namespace mxb {
+
+namespace {
+
+constexpr int kPlanThreads = 256;
+
+__device__ __forceinline__ int owner_of(const int* range_lo, int world, int e) {
+  int d = 0;
+  while (d + 1 < world && e >= range_lo[d + 1]) ++d;
+  return d;
+}
+
+// One block.  counts_all[s][e]: rows rank s routes to expert e; experts are numbered so that rank r owns
+// [range_lo[r], range_lo[r+1]).
+__global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
+  const int tid = threadIdx.x;
+  const int E = a.num_experts, G = a.world, me = a.rank;
+  const int lo = a.range_lo[me], hi = a.range_lo[me + 1];
+  const int el = hi - lo;
+  // where my rows for expert e start in the receive store of e's owner: behind the rows of the lower ranks
+  // for the owner's experts, and behind my rows for the owner's earlier experts
+  for (int e = tid; e < E; e += kPlanThreads) {
+    const int d   = owner_of(a.range_lo, G, e);
+    const int dlo = a.range_lo[d], dhi = a.range_lo[d + 1];
+    int off = 0;
+    for (int s = 0; s < me; ++s)
+      for (int j = dlo; j < dhi; ++j) off += a.counts_all[s * E + j];
+    for (int j = dlo; j < e; ++j) off += a.counts_all[me * E + j];
+    a.dst_row0[e]  = off;
+    a.exp_owner[e] = d;
+  }
+  // my receive store: segments (source rank s, local expert j), s-major
+  const int nseg = G * el;
+  for (int i = tid; i < nseg; i += kPlanThreads) {
+    const int s = i / el, j = i - s * el;
+    int row0 = 0;
+    for (int s2 = 0; s2 < s; ++s2)
+      for (int j2 = lo; j2 < hi; ++j2) row0 += a.counts_all[s2 * E + j2];
+    for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s * E + j2];
+    int src0 = 0;   // the same rows in rank s's expert-sorted order
+    for (int e2 = 0; e2 < lo + j; ++e2) src0 += a.counts_all[s * E + e2];
+    int m = a.counts_all[s * E + lo + j];
+    // never let a segment reach past the store: the rows beyond the capacity are dropped and reported
+    if (row0 >= a.recv_capacity) m = 0;
+    else if (row0 + m > a.recv_capacity) m = a.recv_capacity - row0;
+    a.seg_m[i]        = m;
+    a.seg_row0[i]     = row0;
+    a.seg_src_row0[i] = src0;
+  }
+  if (tid == 0) {
+    int total = 0;
+    for (int s = 0; s < G; ++s)
+      for (int j = lo; j < hi; ++j) total += a.counts_all[s * E + j];
+    a.total_recv[0] = total < a.recv_capacity ? total : a.recv_capacity;
+    if (total > a.recv_capacity) atomicExch(&a.total_recv[1], total);   // overflow: rows wanted
+  }
+}
+
+// block = segment: expert of every received row (the second quantiser picks its format by expert)
+__global__ void ep_fill_row_expert_kernel(EpPlanArgs a) {
+  const int lo = a.range_lo[a.rank], el = a.range_lo[a.rank + 1] - lo;
+  const int i = blockIdx.x;
+  const int e = lo + (i % el);
+  const int row0 = a.seg_row0[i], m = a.seg_m[i];
+  for (int r = threadIdx.x; r < m; r += blockDim.x) a.recv_row_expert[row0 + r] = e;
+}
+
+// One warp per expert-sorted row of this rank: packed row + its scale -> record in the owner's receive store.
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs d, TokenQuantArgs t) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= d.rows) return;
+  const int e       = d.row_expert[row];
+  const int idx     = row - d.exp_row_start[e];
+  const int dst_row = d.dst_row0[e] + idx;
+  if (dst_row >= d.recv_capacity) return;   // reported by the owner's plan kernel
+  const int tag     = d.exp_qtag[e];
+  const int64_t tok = d.row_token[row];
+  const int pack    = tag == 0 ? 1 : (tag == 2 ? 4 : 2);
+  const __half* src = tag == 0 ? (t.f16 ? t.f16 : t.in) : (tag == 1 ? t.q8 : (tag == 2 ? t.q4 : t.q4x));
+  const uint4* s    = reinterpret_cast<const uint4*>(src + tok * (d.k / pack));
+  unsigned char* rec = reinterpret_cast<unsigned char*>(d.peer_base[d.exp_owner[e]]) + (int64_t)dst_row * d.rec_bytes;
+  uint4* dst        = reinterpret_cast<uint4*>(rec);
+  const int n16     = (d.k / pack) >> 3;
+  for (int c = lane; c < n16; c += 32) dst[c] = __ldg(s + c);
+  if (tag != 0 && lane == 0) *reinterpret_cast<__half*>(rec + d.scale_off_bytes) = (tag == 1 ? t.s8 : t.s4)[tok];
+}
+
+}  // namespace
+
+cudaError_t launch_ep_plan(const EpPlanArgs& a, cudaStream_t stream) {
+  ep_plan_kernel<<<1, kPlanThreads, 0, stream>>>(a);
+  const int el = a.experts_local;
+  if (a.world * el > 0) ep_fill_row_expert_kernel<<<a.world * el, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_dispatch(const EpDispatchArgs& d, const TokenQuantArgs& t, cudaStream_t stream) {
+  if (d.rows <= 0) return cudaSuccess;
+  ep_dispatch_kernel<<<(d.rows + 7) / 8, 256, 0, stream>>>(d, t);
+  return cudaGetLastError();
+}
+
+}  // namespace mxb

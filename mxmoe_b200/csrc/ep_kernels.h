@@ -1,0 +1,43 @@
+// Arguments of the expert-parallel plan and dispatch kernels (ep_kernels.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "act_kernels.h"
+
+namespace mxb {
+
+// Experts are numbered so that rank r owns the contiguous range [range_lo[r], range_lo[r+1]).
+struct EpPlanArgs {
+  const int* counts_all;   // [world][num_experts] rows rank s routes to expert e (all-gathered)
+  const int* range_lo;     // [world + 1]
+  int world, rank, num_experts, experts_local, recv_capacity;
+  int pad_;
+  // receive side of this rank: segment i = (source rank i / experts_local, local expert i % experts_local)
+  int* seg_m;              // [world * experts_local] rows of the segment
+  int* seg_row0;           // first row of the segment in this rank's receive store
+  int* seg_src_row0;       // first row of the same rows in the source rank's expert-sorted order
+  int* recv_row_expert;    // [recv_capacity] expert of every received row
+  int* total_recv;         // [0] rows received (clamped to the capacity), [1] rows wanted if that exceeded it
+  // send side of this rank
+  int* dst_row0;           // [num_experts] first row of this rank's rows for expert e in the owner's receive store
+  int* exp_owner;          // [num_experts] rank that owns expert e
+};
+
+struct EpDispatchArgs {
+  const uint64_t* peer_base;   // [world] receive store of every rank as mapped into this process
+  const int* row_expert;       // [rows] expert of each expert-sorted row of this rank
+  const int64_t* row_token;    // [rows] its token
+  const int* exp_row_start;    // [num_experts] first sorted row of each expert
+  const int* exp_qtag;         // [num_experts] activation format of each expert (see ActArgs::exp_qtag)
+  const int* dst_row0;         // from the plan
+  const int* exp_owner;        // from the plan
+  int rows, k, rec_bytes, scale_off_bytes, recv_capacity;
+  int pad_;
+};
+
+cudaError_t launch_ep_plan(const EpPlanArgs& a, cudaStream_t stream);
+cudaError_t launch_ep_dispatch(const EpDispatchArgs& d, const TokenQuantArgs& t, cudaStream_t stream);
+
+}  // namespace mxb

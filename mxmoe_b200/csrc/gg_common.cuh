@@ -45,6 +45,7 @@ struct Sched {
   int m_eff[kMaxProblems];      // rows of each problem
   int row0[kMaxProblems];       // row shift of each problem
   int meta[kMaxProblems];       // n_tiles << 16 | nkb << 4 | scheme   (nkb < 4096)
+  int c_shift[kMaxProblems];    // first row of C minus first row of A (0 unless the problem redirects C)
 };
 
 struct Tile {
@@ -54,6 +55,12 @@ struct Tile {
 // Fill the tables (all threads of the CTA; contains two __syncthreads).  `rows_per_tile` x `cols_per_tile`
 // is the tile of C: 128 x 256 for the single-CTA kernel, 256 x 256 for the CTA pair, 192 x 128 for the
 // kernel with swapped operands.
+// problems of the kernels that cannot redirect C have no c_row0_dev
+__device__ __forceinline__ int c_shift_of(const GGProblemDev&, int) { return 0; }
+__device__ __forceinline__ int c_shift_of(const GGSwapProblemDev& pr, int r0) {
+  return pr.c_row0_dev ? *pr.c_row0_dev - r0 : 0;
+}
+
 template <typename Problem>
 __device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, int count, int rows_per_tile,
                                             int cols_per_tile = kBN) {
@@ -70,6 +77,7 @@ __device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, 
     sc->m_eff[p]    = m;
     sc->row0[p]     = r0;
     sc->meta[p]     = (nt << 16) | (nkb << 4) | pr.scheme;
+    sc->c_shift[p]  = c_shift_of(pr, r0);
   }
   __syncthreads();
   if (tid < 32) {

@@ -68,14 +68,14 @@ struct CfgS {
 // while the tensor core streams operands from shared memory.
 struct TileRec {
   int pk;       // problem | scheme << 8 | k-blocks << 12
-  int x_row;    // buffer row of the tile's first token (A, scale_a and C)
-  int n_tile;   // channel tile
-  int ntok;     // tokens in the tile (1 .. kTT)
+  int x_row;    // buffer row of the tile's first token (A and scale_a)
+  int nt;       // channel tile | tokens in the tile (1 .. kTT) << 16
+  int c_row;    // row of C of the tile's first token
 };
 constexpr int kMaxRecs = 512;   // tiles per CTA kept in the table; later ones are looked up on the fly
 
 struct TileS {
-  int p, scheme, nkb, x_row, n_tile, ntok;
+  int p, scheme, nkb, x_row, n_tile, ntok, c_row;
 };
 
 struct CtrlS {
@@ -109,14 +109,14 @@ __device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t) {
   TileRec r;
   r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12);
   r.x_row  = sc->row0[ti.p] + ti.m_tile * kTT;
-  r.n_tile = ti.n_tile;
-  r.ntok   = min(kTT, sc->m_eff[ti.p] - ti.m_tile * kTT);
+  r.nt     = ti.n_tile | (min(kTT, sc->m_eff[ti.p] - ti.m_tile * kTT) << 16);
+  r.c_row  = r.x_row + sc->c_shift[ti.p];
   return r;
 }
 __device__ __forceinline__ TileS decode_rec(const TileRec& r) {
   TileS t;
   t.p = r.pk & 0xff; t.scheme = (r.pk >> 8) & 15; t.nkb = r.pk >> 12;
-  t.x_row = r.x_row; t.n_tile = r.n_tile; t.ntok = r.ntok;
+  t.x_row = r.x_row; t.n_tile = r.nt & 0xffff; t.ntok = r.nt >> 16; t.c_row = r.c_row;
   return t;
 }
 
@@ -354,7 +354,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
       const GGSwapProblemDev* pr = problems + ti.p;
       const int ntok      = ti.ntok;
-      const int64_t grow0 = ti.x_row;   // buffer row of token 0 of the tile
+      const int64_t grow0 = ti.x_row;   // buffer row of token 0 of the tile (A, scale_a)
+      const int64_t crow0 = ti.c_row;   // its row in C
       const int N = pr->N, ldc = pr->ldc, out_mode = pr->out_mode;
       const bool is_int   = is_int_scheme(ti.scheme);
       const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
@@ -400,7 +401,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           for (int j = 0; j < 32; ++j) {
             const int tk = ch * 32 + j;
             if (tk < ntok && n_ch < N)
-              dst[(grow0 + tk) * ldc + n_ch] = is_int ? (uint32_t)((int)v[j] >> acc_shift) : v[j];
+              dst[(crow0 + tk) * ldc + n_ch] = is_int ? (uint32_t)((int)v[j] >> acc_shift) : v[j];
           }
           continue;
         }
@@ -449,7 +450,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           lo.w = __byte_perm(a1.z, a1.w, 0x5410); hi.w = __byte_perm(a1.z, a1.w, 0x7632);
           const int tk   = ch * 32 + 2 * tp;
           const int ncol = ti.n_tile * kWT + q * 32 + 8 * p8;
-          __half* dst    = reinterpret_cast<__half*>(pr->C) + (grow0 + tk) * ldc + ncol;
+          __half* dst    = reinterpret_cast<__half*>(pr->C) + (crow0 + tk) * ldc + ncol;
           if (ncol < N) {
             if (tk < ntok) *reinterpret_cast<uint4*>(dst) = lo;
             if (tk + 1 < ntok) *reinterpret_cast<uint4*>(dst + ldc) = hi;

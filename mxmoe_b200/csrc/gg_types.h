@@ -66,7 +66,8 @@ struct alignas(128) GGSwapProblemDev {
   const int* row0_dev;
   int M, N, K, row0;
   int scheme, out_mode, ldc, sa_stride;
-  int pad[14];
+  const int* c_row0_dev;   // optional: rows of C start at *c_row0_dev instead of at row0
+  int pad[12];
 };
 static_assert(sizeof(GGSwapProblemDev) == 512, "GGSwapProblemDev layout");
 

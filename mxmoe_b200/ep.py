@@ -1,23 +1,33 @@
-"""Expert-parallel MoE layer: one process per GPU, experts sharded in contiguous ranges,
-tokens data-parallel, quantised rows dispatched with an all-to-all over NCCL / NVLink and fp16
-rows combined back.  (The reference has no distributed code; this is the multi-GPU form of the
-path described by the benchmark configurations.)
+"""Expert-parallel MoE layer: one process per GPU, experts sharded, tokens data-parallel.  (The reference has
+no distributed code; this is the multi-GPU form of the path described by the benchmark configurations.)
 
-Per step and rank::
+Two transports move the rows:
+
+``p2p`` (default) - no host round trip and no library all-to-all.  Per step and rank::
 
     route_topk (global expert ids)  ->  rows sorted by expert = grouped by destination rank
-    quant_tokens + gather_rows      ->  send records [T*topk, P + 8] (packed row + its scale)
-    all_gather(counts)              ->  one small device->host copy: every split size of the step
-    all_to_all_single(records)      ->  receive store in local HBM, grouped (source rank, expert)
-    ExpertCompute                   ->  one problem per (source rank, local expert), no re-sort
-    all_to_all_single(fp16 rows)    ->  back to the owners, in their original row order
-    combine_topk (+ shared expert, computed locally on the rank's own tokens)
+    quant_tokens                    ->  token-major quantised stores
+    all_gather(counts)              ->  every rank knows every split size, on the device
+    ep_plan (device)                ->  receive-side segment tables, send-side row offsets
+    ep_dispatch_rows                ->  packed row + scale written straight into the owner's receive store
+                                        (plain stores to peer memory over NVLink)
+    barrier                         ->  a one-element all-reduce, stream ordered
+    grouped GEMM, silu*mul+quantise, grouped GEMM
+                                    ->  one problem per (source rank, local expert); the epilogue of the down
+                                        projection stores every segment straight into the buffer of the rank its
+                                        rows came from, at their place in that rank's order (peer stores again)
+    barrier, combine_topk (+ shared expert, computed locally on the rank's own tokens)
+
+``nccl`` - ``all_to_all_single`` for both exchanges; NCCL needs the split sizes on the host, which costs one
+device->host copy and a stream synchronisation per step.
 
 TMA only ever reads this GPU's own memory (the receive store); no load uses cluster multicast.
 """
 from __future__ import annotations
 
 import dataclasses
+import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -88,10 +98,13 @@ class EPMoELayer:
     """Expert-parallel layer for ``spec`` (a :class:`mxmoe_b200.workload.LayerSpec`): ``spec.tokens`` tokens per rank."""
 
     def __init__(self, spec, device, gen_device="cpu", capacity_factor: float = 3.0, group=None,
-                 placement: str = "strided"):
+                 placement: str = "strided", transport: str | None = None):
         from . import workload
         self.spec, self.device, self.group = spec, torch.device(device), group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.transport = transport or os.environ.get("MXMOE_EP_TRANSPORT", "p2p")
+        if self.transport not in ("p2p", "nccl"):
+            raise ValueError(f"unknown transport {self.transport!r}")
         E, T, k, H, I = spec.num_experts, spec.tokens, spec.topk, spec.hidden, spec.inter
         if placement == "strided":
             remap, inverse, self.ranges = strided_placement(E, self.world)
@@ -131,10 +144,26 @@ class EPMoELayer:
         self.rec = self.P + 8
         self.R_send = T * k
         self.R_recv = int(T * k * capacity_factor)
-        self.send = torch.zeros(self.R_send, self.rec, **f16)
-        self.recv = torch.zeros(self.R_recv, self.rec, **f16)
-        self.ret = torch.zeros(self.R_send, H, **f16)            # expert outputs coming home
         self.out = torch.zeros(T, H, **f16)
+        if self.transport == "p2p":
+            # receive store and home-coming buffer live in symmetric memory: every rank maps every peer's copy
+            import torch.distributed._symmetric_memory as symm
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings only
+            grp = group if group is not None else dist.group.WORLD
+            self.recv = symm.empty((self.R_recv, self.rec), dtype=torch.float16, device=dev)
+            self.ret = symm.empty((self.R_send, H), dtype=torch.float16, device=dev)
+            self.recv.zero_()
+            self.ret.zero_()
+            self._h_recv = symm.rendezvous(self.recv, grp)
+            self._h_ret = symm.rendezvous(self.ret, grp)
+            self.peer_recv = torch.tensor([int(p) for p in self._h_recv.buffer_ptrs], dtype=torch.int64, device=dev)
+            self.peer_ret = [int(p) for p in self._h_ret.buffer_ptrs]
+            self.send = None
+            self._bar = torch.zeros(1, dtype=torch.float32, device=dev)
+        else:
+            self.send = torch.zeros(self.R_send, self.rec, **f16)
+            self.recv = torch.zeros(self.R_recv, self.rec, **f16)
+            self.ret = torch.zeros(self.R_send, H, **f16)        # expert outputs coming home
 
         nseg = self.world * (hi - lo)
         self.seg_expert = [e for _ in range(self.world) for e in range(lo, hi)]
@@ -145,6 +174,12 @@ class EPMoELayer:
         self.counts_all = torch.zeros(self.world * E, **i32)
         self.counts_host = torch.zeros(self.world, E, dtype=torch.int32).pin_memory()
         self.ids_new = torch.zeros(T, k, **i32)
+        # device-side plan of the p2p transport
+        self.range_lo = torch.tensor([r[0] for r in self.ranges] + [E], **i32)
+        self.seg_src_row0 = torch.zeros(max(nseg, 1), **i32)
+        self.dst_row0 = torch.zeros(E, **i32)
+        self.exp_owner = torch.zeros(E, **i32)
+        self.total_recv = torch.zeros(2, **i32)
         self._gate_up, self._down = gate_up, down
         self._core = None
         self.launches_per_step = 9
@@ -157,11 +192,18 @@ class EPMoELayer:
         if self.has_shared:
             a_ptr, sa_ptr = self.tq.rows_of(self._tag1[spec.num_experts], hidden)
             shared = {"tokens": spec.tokens, "a_ptr": a_ptr, "sa_ptr": sa_ptr}
+        down_out = None
+        if self.transport == "p2p":
+            # segment i = (source rank s, local expert j): its results go to rank s's home-coming buffer, at the rows
+            # the segment has in rank s's expert-sorted order
+            el = self.ranges[self.rank][1] - self.ranges[self.rank][0]
+            down_out = [(self.peer_ret[i // el], self.seg_src_row0.data_ptr() + 4 * i) for i in range(self.world * el)]
         self._core = ExpertCompute(
             spec.num_experts, spec.hidden, spec.inter, self._gate_up, self._down, self.R_recv, self.seg_expert,
             self.seg_tab[0], self.seg_tab[1], self.recv_row_expert, self.recv.view(-1), self.rec,
             self.recv.data_ptr() + self.P * 2, self.rec, self.device, shared=shared, shared_inter=spec.shared_inter,
-            tag_fn=tag_of)     # dispatched rows stay packed (half the NVLink bytes of the expanded format)
+            tag_fn=tag_of,     # dispatched rows stay packed (half the NVLink bytes of the expanded format)
+            down_out=down_out, rows_dev=self.total_recv if self.transport == "p2p" else None)
 
     def _mark(self, marks, name):
         if self.profile:
@@ -169,7 +211,62 @@ class EPMoELayer:
             ev.record()
             marks.append((name, ev))
 
+    def _barrier(self):
+        """Every rank's earlier kernels on this stream (their peer stores included) are complete before any
+        rank's later kernels start: a one-element all-reduce, ordered on the stream, no host involvement."""
+        dist.all_reduce(self._bar, group=self.group)
+
+    def _forward_p2p(self, hidden, topk_ids, topk_weights):
+        spec, f = self.spec, self.front
+        T, k, H, E = spec.tokens, spec.topk, spec.hidden, spec.num_experts
+        lib = _lib.lib()
+        marks = []
+        with torch.cuda.device(self.device):
+            if self._core is None:
+                self._build_core(hidden)
+            self._mark(marks, "start")
+            torch.index_select(self.remap, 0, topk_ids.reshape(-1), out=self.ids_new.view(-1))
+            f.route(self.ids_new)
+            t = self.tq.run(hidden)
+            self._mark(marks, "route+quant")
+            dist.all_gather_into_tensor(self.counts_all, f.counts, group=self.group)
+            lo, hi = self.ranges[self.rank]
+            pa = _lib.EpPlanArgs()
+            pa.counts_all, pa.range_lo = self.counts_all.data_ptr(), self.range_lo.data_ptr()
+            pa.world, pa.rank, pa.num_experts, pa.experts_local = self.world, self.rank, E, hi - lo
+            pa.recv_capacity = self.R_recv
+            pa.seg_m, pa.seg_row0 = self.seg_tab[0].data_ptr(), self.seg_tab[1].data_ptr()
+            pa.seg_src_row0, pa.recv_row_expert = self.seg_src_row0.data_ptr(), self.recv_row_expert.data_ptr()
+            pa.total_recv, pa.dst_row0, pa.exp_owner = self.total_recv.data_ptr(), self.dst_row0.data_ptr(), self.exp_owner.data_ptr()
+            _lib.check(lib.mxmoe_ep_plan(C.byref(pa), current_stream_ptr()))
+            da = _lib.EpDispatchArgs()
+            da.peer_base, da.row_expert, da.row_token = self.peer_recv.data_ptr(), f.row_expert.data_ptr(), f.row_token.data_ptr()
+            da.exp_row_start, da.exp_qtag = f.row_start.data_ptr(), f.tag1.data_ptr()
+            da.dst_row0, da.exp_owner = self.dst_row0.data_ptr(), self.exp_owner.data_ptr()
+            da.rows, da.k, da.rec_bytes, da.scale_off_bytes, da.recv_capacity = T * k, H, self.rec * 2, self.P * 2, self.R_recv
+            _lib.check(lib.mxmoe_ep_dispatch_rows(C.byref(da), C.byref(t), current_stream_ptr()))
+            self._mark(marks, "plan+dispatch")
+            self._barrier()
+            self._mark(marks, "barrier")
+            self._core.run(self.R_recv)
+            self._mark(marks, "experts")
+            self._barrier()
+            self._mark(marks, "barrier2")
+            _lib.check(lib.mxmoe_combine_topk(
+                self.ret.data_ptr(), f.slot_row.data_ptr(),
+                None if topk_weights is None else topk_weights.data_ptr(),
+                self._core.o2s.data_ptr() if self.has_shared else None, self.out.data_ptr(), T, k, H,
+                current_stream_ptr()))
+            self._mark(marks, "combine")
+            if self.profile:
+                torch.cuda.synchronize()
+                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                    self.phase_ms.setdefault(name, []).append(a.elapsed_time(b))
+        return self.out
+
     def forward(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor | None = None):
+        if self.transport == "p2p":
+            return self._forward_p2p(hidden, topk_ids, topk_weights)
         spec, f = self.spec, self.front
         T, k, H = spec.tokens, spec.topk, spec.hidden
         marks = []
@@ -222,3 +319,7 @@ class EPMoELayer:
 
     def check(self) -> None:
         self._core.check()
+        if self.transport == "p2p":
+            wanted = int(self.total_recv[1].item())
+            if wanted:
+                raise RuntimeError(f"rank {self.rank} was sent {wanted} rows, capacity is {self.R_recv}: raise capacity_factor")

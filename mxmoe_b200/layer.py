@@ -77,12 +77,17 @@ class ExpertCompute:
     def __init__(self, num_experts, hidden, inter, gate_up: dict, down: dict, rows_cap: int,
                  seg_expert, seg_m: torch.Tensor, seg_row0: torch.Tensor, row_expert: torch.Tensor,
                  q1: torch.Tensor, rec1: int, scale1_ptr: int, scale1_stride: int, device,
-                 shared: dict | None = None, shared_inter: int = 0, tag_fn=internal_tag):
+                 shared: dict | None = None, shared_inter: int = 0, tag_fn=internal_tag,
+                 down_out: list | None = None, rows_dev: torch.Tensor | None = None):
         self.E, self.H, self.I, self.Is = num_experts, hidden, inter, shared_inter
         self.R, self.device = rows_cap, device
         self.gate_up, self.down = gate_up, down
         self.row_expert, self.seg_expert = row_expert, list(seg_expert)
         self.shared = shared
+        # down_out[i] = (C pointer, pointer to the first C row) of segment i: the down projection then stores the
+        # segment's rows there (e.g. straight into the buffer of the rank they came from) instead of into o2.
+        # rows_dev: live row count on the device (sizes the work of the second quantiser)
+        self.rows_dev = rows_dev
         dev, R, H, I = device, rows_cap, hidden, inter
         f16 = dict(dtype=torch.float16, device=dev)
         local = sorted(set(self.seg_expert))
@@ -111,10 +116,11 @@ class ExpertCompute:
                               scale_a=scale1_ptr if self._tag1[e] else None, scale_b=w1.scale,
                               a_rows=R, lda_bytes=rec1 * 2, sa_stride=scale1_stride, m_dev=m_ptr, row0_dev=r_ptr,
                               a_expanded=1 if self._tag1[e] == 3 else 0))
-            p2.append(Problem(A=self.q2, B=w2.data, C=self.o2, M=R, N=H, K=I, qparams=w2.qparams,
+            c_out, c_row0 = (self.o2, None) if down_out is None else down_out[i]
+            p2.append(Problem(A=self.q2, B=w2.data, C=c_out, M=R, N=H, K=I, qparams=w2.qparams,
                               scale_a=self.s2 if self._tag2[e] else None, scale_b=w2.scale,
                               a_rows=R, lda_bytes=self.rec2 * 2, m_dev=m_ptr, row0_dev=r_ptr,
-                              a_expanded=1 if self._tag2[e] == 3 else 0))
+                              a_expanded=1 if self._tag2[e] == 3 else 0, c_row0_dev=c_row0))
         if shared is not None:
             T, Is, E = shared["tokens"], shared_inter, num_experts
             w1, w2 = gate_up[E], down[E]
@@ -143,7 +149,8 @@ class ExpertCompute:
         _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.q2, s_store=self.s2,
                   row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
                   exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
-                  rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1)
+                  rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1,
+                  rows_dev=self.rows_dev)
         if self.shared is not None:
             T = self.shared["tokens"]
             _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1s, in_shared=self.o1s, q_store=self.q2s,

@@ -29,10 +29,19 @@ def run(spec_name: str = "tiny-ep") -> None:
     hidden = workload.make_hidden(spec, seed=1 + rank).to(dev)
     ids, wts = workload.make_routing(spec, seed=2 + rank)
     ids, wts = ids.to(dev), wts.to(dev)
-    ep = EPMoELayer(spec, dev, capacity_factor=float(world) + 1.0)
-    out_ep = ep.forward(hidden, ids, wts).clone()
-    out_ep2 = ep.forward(hidden, ids, wts).clone()          # a second step reuses every buffer
-    ep.check()
+    outs = {}
+    for transport in ("p2p", "nccl"):
+        ep = EPMoELayer(spec, dev, capacity_factor=float(world) + 1.0, transport=transport)
+        out_ep = ep.forward(hidden, ids, wts).clone()
+        out_ep2 = ep.forward(hidden, ids, wts).clone()          # a second step reuses every buffer
+        ep.check()
+        outs[transport] = (out_ep, out_ep2)
+        if transport == "nccl":
+            assert sum(ep.last_plan.send_rows) == spec.tokens * spec.topk
+        else:
+            got = ep.total_recv[:1].clone().float()
+            dist.all_reduce(got)
+            assert int(got.item()) == world * spec.tokens * spec.topk, "rows received over all ranks"
     gate_up, down, signs, _ = workload.build_layer_weights(spec, device=dev)
     full = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens,
                     shared_inter=spec.shared_inter, signs=signs, rotate=spec.rotate, device=dev)
@@ -40,9 +49,9 @@ def run(spec_name: str = "tiny-ep") -> None:
     full.check()
     torch.cuda.synchronize()
     assert torch.isfinite(out_full.float()).all()
-    assert torch.equal(out_ep, out_full), f"rank {rank}: expert-parallel output differs from the single-GPU layer"
-    assert torch.equal(out_ep2, out_full), f"rank {rank}: second step differs"
-    assert sum(ep.last_plan.send_rows) == spec.tokens * spec.topk
+    for transport, (out_ep, out_ep2) in outs.items():
+        assert torch.equal(out_ep, out_full), f"rank {rank} ({transport}): expert-parallel output differs from the single-GPU layer"
+        assert torch.equal(out_ep2, out_full), f"rank {rank} ({transport}): second step differs"
 
 
 if __name__ == "__main__":
