@@ -65,6 +65,29 @@ def strided_placement(num_experts: int, world: int):
     return remap, inverse, ranges
 
 
+def balanced_placement(loads, world: int):
+    """Experts placed by longest-processing-time-first on expected loads (e.g. the row counts of a calibration
+    gate trace), every rank holding at most ceil(E / world) experts.  Same return value as
+    :func:`strided_placement`: experts renumbered rank-major."""
+    num_experts = len(loads)
+    cap = -(-num_experts // world)
+    order = sorted(range(num_experts), key=lambda e: (-float(loads[e]), e))
+    total, members = [0.0] * world, [[] for _ in range(world)]
+    for e in order:
+        r = min((r for r in range(world) if len(members[r]) < cap), key=lambda r: (total[r], r))
+        total[r] += float(loads[e])
+        members[r].append(e)
+    inverse = [e for r in range(world) for e in sorted(members[r])]
+    remap = [0] * num_experts
+    for new, e in enumerate(inverse):
+        remap[e] = new
+    ranges, lo = [], 0
+    for r in range(world):
+        ranges.append((lo, lo + len(members[r])))
+        lo += len(members[r])
+    return remap, inverse, ranges
+
+
 @dataclasses.dataclass
 class ExchangePlan:
     """Split sizes (in rows) and receive-side segments of one step, from the gathered counts."""
@@ -98,7 +121,7 @@ class EPMoELayer:
     """Expert-parallel layer for ``spec`` (a :class:`mxmoe_b200.workload.LayerSpec`): ``spec.tokens`` tokens per rank."""
 
     def __init__(self, spec, device, gen_device="cpu", capacity_factor: float = 3.0, group=None,
-                 placement: str = "strided", transport: str | None = None):
+                 placement: str = "balanced", transport: str | None = None, loads=None):
         from . import workload
         self.spec, self.device, self.group = spec, torch.device(device), group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
@@ -106,7 +129,13 @@ class EPMoELayer:
         if self.transport not in ("p2p", "nccl"):
             raise ValueError(f"unknown transport {self.transport!r}")
         E, T, k, H, I = spec.num_experts, spec.tokens, spec.topk, spec.hidden, spec.inter
-        if placement == "strided":
+        if placement == "balanced":
+            # expected rows per expert: a calibration routing sample of the workload unless the caller has a trace
+            if loads is None:
+                cal, _ = workload.make_routing(spec, seed=1234)
+                loads = torch.bincount(cal.reshape(-1).long(), minlength=E).tolist()
+            remap, inverse, self.ranges = balanced_placement(loads, self.world)
+        elif placement == "strided":
             remap, inverse, self.ranges = strided_placement(E, self.world)
         else:
             remap, inverse, self.ranges = list(range(E)), list(range(E)), expert_ranges(E, self.world)

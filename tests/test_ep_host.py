@@ -86,3 +86,18 @@ def _worker(rank, world, port, experts):
 @pytest.mark.parametrize("world,experts", [(2, 6), (3, 8)])
 def test_row_exchange_on_cpu_ranks(world, experts):
     mp.spawn(_worker, args=(world, _free_port(), experts), nprocs=world, join=True)
+
+
+def test_balanced_placement_is_a_permutation_and_balances():
+    from mxmoe_b200.ep import balanced_placement
+    loads = [1000 / (e + 1) ** 1.2 for e in range(60)]
+    for world in (1, 2, 4, 8):
+        remap, inverse, ranges = balanced_placement(loads, world)
+        assert sorted(remap) == list(range(60)) and sorted(inverse) == list(range(60))
+        assert all(inverse[remap[e]] == e for e in range(60))
+        assert ranges[0][0] == 0 and ranges[-1][1] == 60
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        assert max(hi - lo for lo, hi in ranges) <= -(-60 // world)
+        per_rank = [sum(loads[inverse[n]] for n in range(lo, hi)) for lo, hi in ranges]
+        strided = [sum(loads[r::world]) for r in range(world)]
+        assert max(per_rank) <= max(strided) + 1e-9
