@@ -175,6 +175,11 @@ def run_reference_arm(args, spec):
 
 
 # --------------------------------------------------------------------------- GPU arm
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (mean of the gate_up and the down
+# launch), from the ncu capture summarised in profiles/gg_swap_kernel_qwen15-w4a4-8192_ncu_full.md
+NCU_TRAFFIC_BYTES = {"qwen15-w4a4-8192": (410.8e6 + 243.1e6) / 2}
+
+
 def class_pass(layer, spec, counts, peaks, reps: int = 10):
     """Per-class roofline of the grouped GEMM: every (expert, linear block) problem is classified compute- or
     memory-bound from its algorithmic flops and bytes against the measured peaks, and each class's problem
@@ -399,7 +404,7 @@ def main():
         bytes_launch = layer.gemm_bytes(counts) / 2
         line["roofline"] = {
             "bound": "tensor", "kernel": "gg_swap_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak, "traffic": None,
+            "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(spec.name),
             "peak_source": f"{peaks['source']} cuBLAS bf16 burst x{2 if int_kind else 1} (tcgen05 kind::i8 issues at twice the bf16 rate)",
             "launch_ms": {"gate_up": d1, "down": d2},
             "algorithmic_flops_per_launch": flops_launch,

@@ -79,7 +79,7 @@ typedef struct mxmoe_gg_problem {
   const int32_t* c_row0_dev; /* optional: the rows of C start at *c_row0_dev instead of at row0 (A and scale_a keep
                                 row0).  Lets an expert-parallel rank store a segment's results straight into the
                                 buffer of the rank the rows came from, at their place in that rank's order; C may
-                                then be peer memory (plain stores).  Not available for packed 4-bit activations. */
+                                then be peer memory (plain stores). */
 } mxmoe_gg_problem;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -124,9 +124,8 @@ enum mxmoe_gg_kernel {
   MXMOE_GG_KERNEL_DEFAULT = 0,
   MXMOE_GG_KERNEL_SINGLE = 1, /* one CTA per tile of 128 rows x 256 channels, both operands from shared memory */
   MXMOE_GG_KERNEL_PAIR = 2,   /* tcgen05 cta_group::2, 256 x 256 tiles on clusters of two CTAs */
-  MXMOE_GG_KERNEL_SWAP = 3    /* swapped operands: 128 channels x up to 192 tokens per tile, 4-bit weights
-                                 converted into tensor memory (launches with packed 4-bit activations
-                                 run on the SINGLE kernel) */
+  MXMOE_GG_KERNEL_SWAP = 3    /* swapped operands: 128 channels x up to 176 tokens per tile (128 when a problem has
+                                 packed 4-bit activations), 4-bit weights converted into tensor memory */
 };
 int mxmoe_gg_run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_ctas, void* stream);
 

@@ -43,13 +43,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
         _nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
         "-shared", "-Xcompiler", "-fPIC",
         "-Xptxas", "-v" if verbose else "-warn-spills",
-        "-o", LIB,
+        "-o", LIB + ".tmp",
     ] + [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building libmxmoe_b200.so (see stderr)")
+    os.replace(LIB + ".tmp", LIB)   # a reader never sees a half-written library
     return LIB
 
 

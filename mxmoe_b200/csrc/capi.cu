@@ -186,7 +186,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
 }
 
 // The same problem for the kernel with swapped operands: tensor maps with its boxes (weights: 128 channels per
-// box; activations: 192-row and 32-row boxes).  `d` has been validated by build_problem already.
+// box; activations: 176-row and 32-row boxes).  `d` has been validated by build_problem already.
 int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, const mxb::GGProblemDev& d,
                        mxb::GGSwapProblemDev* o) {
   int rc;
@@ -203,6 +203,7 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
     case mxb::SCH_W8A8:
       if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K, N, 128, mxb::kWT, s128, "B", idx))) return rc;
       break;
+    case mxb::SCH_W4A4:
     case mxb::SCH_W4A4_XA:
       // packed rows of 64 bytes per stage; the 64-byte swizzle spreads the rows a converter warp reads over the banks
       if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K / 2, N, 64, mxb::kWT, CU_TENSOR_MAP_SWIZZLE_64B, "B", idx))) return rc;
@@ -212,11 +213,16 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
       if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K * 2, N / 4, 128, mxb::kWT / 4, s128, "B", idx))) return rc;
       break;
     default:
-      break;   // packed 4-bit activations: served by the kernel without swapped operands
+      break;
   }
   if (d.scheme == mxb::SCH_FP16 || d.scheme == mxb::SCH_W4A16G128) {
     if ((rc = encode_2d(enc, &o->tmX, p.A, f16, 2, K, a_rows, 64, mxb::kTT, s128, "A", idx, lda))) return rc;
     if ((rc = encode_2d(enc, &o->tmXs, p.A, f16, 2, K, a_rows, 64, mxb::kXBoxSmall, s128, "A", idx, lda))) return rc;
+  } else if (d.scheme == mxb::SCH_W4A4) {
+    // packed rows: 64 bytes of K per stage, unswizzled (the converters expand them in shared memory); token tiles
+    // of such launches have at most 128 rows, loaded as 32-row boxes
+    if ((rc = encode_2d(enc, &o->tmXs, p.A, u8, 1, K / 2, a_rows, 64, mxb::kXBoxSmall, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx, lda))) return rc;
+    o->tmX = o->tmXs;
   } else if (d.scheme == mxb::SCH_W8A8 || d.scheme == mxb::SCH_W4A4_XA) {
     if ((rc = encode_2d(enc, &o->tmX, p.A, u8, 1, K, a_rows, 128, mxb::kTT, s128, "A", idx, lda))) return rc;
     if ((rc = encode_2d(enc, &o->tmXs, p.A, u8, 1, K, a_rows, 128, mxb::kXBoxSmall, s128, "A", idx, lda))) return rc;
@@ -289,16 +295,12 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     if (rc) return rc;
     rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept]);
     if (rc) return rc;
-    if (dev[kept].scheme == mxb::SCH_W4A4 && problems[i].c_row0_dev)
-      return fail(MXMOE_ERR_UNSUPPORTED, "problem %d: c_row0_dev is not available with packed 4-bit activations", i);
     if (problems[i].c_row0_dev) redirect = true;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
     ++kept;
   }
   status->pad[0]    = getenv("MXMOE_GG_PROFILE") ? atoi(getenv("MXMOE_GG_PROFILE")) : 0;   // per-role counters on
-  if (redirect && needs_cvt == 2)
-    return fail(MXMOE_ERR_UNSUPPORTED, "c_row0_dev cannot be combined with packed 4-bit activations in one launch");
   status->count     = kept;
   status->needs_cvt = needs_cvt;
   // pageable source: the runtime stages the bytes before returning, so `host` may go out of scope
@@ -334,7 +336,6 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   if (plan->flags & 1) {
     if (kernel != GGK_SWAP) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows run on the SWAP kernel only");
   }
-  if (kernel == GGK_SWAP && needs_cvt == 2) kernel = GGK_SINGLE;   // packed 4-bit activations
   int n = num_ctas;
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
   if (kernel == GGK_PAIR && n < 2) kernel = GGK_SINGLE;

@@ -53,7 +53,7 @@ struct Tile {
 };
 
 // Fill the tables (all threads of the CTA; contains two __syncthreads).  `rows_per_tile` x `cols_per_tile`
-// is the tile of C: 128 x 256 for the single-CTA kernel, 256 x 256 for the CTA pair, 192 x 128 for the
+// is the tile of C: 128 x 256 for the single-CTA kernel, 256 x 256 for the CTA pair, 176 x 128 for the
 // kernel with swapped operands.
 // problems of the kernels that cannot redirect C have no c_row0_dev
 __device__ __forceinline__ int c_shift_of(const GGProblemDev&, int) { return 0; }

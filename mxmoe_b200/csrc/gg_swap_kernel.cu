@@ -4,16 +4,16 @@
 // C[M,N] = A[M,K] x B[N,K]^T, each with its own quantisation scheme; reference:
 // mxmoe/kernels/compose_kernel.py:150-295, cta_gemm.cuh:7-107, :291-421, :423-608), but the MMA
 // computes C^T: the WEIGHTS are the M side (tiles of 128 output channels) and the TOKENS the
-// N side (tiles of up to 192 rows, any multiple of 16).  Consequences:
+// N side (tiles of up to 176 rows, any multiple of 16).  Consequences:
 //   * 4-bit weights are unpacked / dequantised by the converter warps from shared memory straight
 //     into TENSOR MEMORY (tcgen05.st) and the MMA takes its A operand from there: the converted
 //     weights never travel through shared memory again, which is the unit that limits the kernel
 //     with the operands the other way round.
 //   * a ragged expert costs MMA time for its rows rounded up to 16, not to 128.
-//   * the weight-conversion work per MAC shrinks with the token tile (192 instead of 128 rows).
+//   * the weight-conversion work per MAC shrinks with the token tile (176 instead of 128 rows).
 //
-// TMEM columns: [0,192) and [192,384) two accumulators (128 channels x up to 192 tokens, fp32/int32),
-// [384,512) four A-operand slots of 32 columns (128 channels x 128 bytes of K each).
+// TMEM columns: [0,176) and [176,352) two accumulators (128 channels x up to 176 tokens, fp32/int32),
+// [352,512) five A-operand slots of 32 columns (128 channels x 128 bytes of K each), one per ring stage.
 //
 // One CTA (480 threads; 224 when no problem has 4-bit weights):
 //   warp 0      TMA producer: weights (packed or plain) + activations into a ring of 5 stages.
@@ -24,18 +24,23 @@
 //   warps 2-5   epilogue: tcgen05.ld (lane = channel, columns = tokens) -> scales -> fp16 ->
 //               transposed through shared memory -> 16-byte global stores along the channel axis.
 //   warp 6      watcher: waits on the mbarriers the TMA unit and the converters complete (full[s],
-//               afull[a]) and forwards each stage to the MMA warp with bar.arrive.
-//   warps 7-14  converters: thread = one weight row of the tile (its TMEM lane), two warps per lane
-//               quarter splitting the 128 bytes of K of a stage.
+//               afull[s]) and forwards each stage to the MMA warp with bar.arrive.
+//   warps 7-14  converters: two groups of four warps that take alternate stages; thread = one weight row
+//               of the tile (its TMEM lane).  With packed 4-bit ACTIVATIONS in the launch (the reference
+//               operator API's input format; token tiles are then 128 rows) the group also expands the
+//               stage's packed activation rows into the swizzled int8 operand tile in shared memory.
 //
-// Barrier protocol.  full[s] / empty[s] (mbarriers) are followed by the producer, the watcher and the
-// converter warps on EVERY stage (the converter warps arrive on empty[s] as well, also for tiles they have
-// nothing to convert in), so no waiter can be lapped and parities follow from the stage counter.
-// afull[a] / aempty[a] (A slots in TMEM) are used only for stages with converted weights; both sides count
-// those uses.  Named barriers: 1 + s "stage s is ready" (watcher arrives, MMA warp syncs), 6 + b
-// "accumulator b is drained" (epilogue warps arrive, MMA warp syncs).  Every mbarrier wait is bounded (1 s
-// of %globaltimer); a role whose wait ran out raises the abort flag and keeps walking its loop without
-// waiting or working, so that every bar.arrive another warp counts on is still made and the kernel ends.
+// Barrier protocol (mbarriers).  full[s] "TMA bytes of stage s have landed"; afull[s] "the converters are
+// done with stage s" (converted weights in tensor memory, expanded activations in shared memory, or nothing
+// to convert); empty[s] "stage s may be refilled" = the MMAs of the stage have completed (tcgen05.commit) and
+// the stage's converter group has read its packed operands.  Every barrier completes once per use of its
+// stage, whatever the tile's scheme, so parities follow from the stage counter and no waiter can be lapped.
+// A slot s of tensor memory needs no barrier of its own: full[s] completes only after the producer saw
+// empty[s] of the previous use, i.e. after the MMAs that read the slot.  Named barriers: 1 + s "stage s is
+// ready" (watcher arrives, MMA warp syncs), 6 + b "accumulator b is drained" (epilogue warps arrive, MMA warp
+// syncs).  Every mbarrier wait is bounded (1 s of %globaltimer); a role whose wait ran out raises the abort
+// flag and keeps walking its loop without waiting or working, so that every bar.arrive another warp counts
+// on is still made and the kernel ends.
 #include "gg_common.cuh"
 
 namespace mxb {
@@ -46,10 +51,10 @@ using namespace ggc;
 namespace {
 
 constexpr int kWSlotBytes  = kWT * kRowBytes;   // 16 KiB: plain weights, or 8 / 4 KiB of packed ones
-constexpr int kXSlotBytes  = kTT * kRowBytes;   // 28 KiB
+constexpr int kXSlotBytes  = kTT * kRowBytes;   // 22 KiB
 constexpr int kStageBytesS = kWSlotBytes + kXSlotBytes;
 constexpr int kStagesS     = 5;
-constexpr int kRingBytesS  = kStagesS * kStageBytesS;   // 176 KiB
+constexpr int kRingBytesS  = kStagesS * kStageBytesS;   // 190 KiB
 constexpr int kEpiStageS   = 2048;                       // per epilogue warp: 16 token pairs x 32 channels x 4 bytes
 constexpr int kCvtWarps    = 8;
 constexpr uint32_t kAccCols = kTT;                       // columns per accumulator
@@ -100,16 +105,24 @@ __device__ __forceinline__ void report_s(GGStatus* status, int role, int tile) {
 }
 
 __device__ __forceinline__ bool is_int_scheme(int s) { return s != SCH_FP16 && s != SCH_W4A16G128; }
-__device__ __forceinline__ bool is_cvt_scheme(int s) { return s == SCH_W4A4_XA || s == SCH_W4A16G128; }
+__device__ __forceinline__ bool is_cvt_scheme(int s) { return s == SCH_W4A4_XA || s == SCH_W4A16G128 || s == SCH_W4A4; }
 
 __device__ __forceinline__ long long tick(bool on) { return on ? clock64() : 0ll; }
 
-__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t) {
+// bytes per stage of a weight tile and its coordinates (x step per K block, y) in the weight tensor map
+__device__ __forceinline__ void weight_coords(int scheme, int w_row, uint32_t& wbytes, int& wx_step, int& wy) {
+  if (scheme == SCH_W8A8)         { wbytes = kWSlotBytes;     wx_step = 128; wy = w_row; }
+  else if (scheme == SCH_FP16)    { wbytes = kWSlotBytes;     wx_step = 64;  wy = w_row; }
+  else if (scheme == SCH_W4A4_XA || scheme == SCH_W4A4) { wbytes = kWSlotBytes / 2; wx_step = 64;  wy = w_row; }   // 64 packed bytes per row
+  else                            { wbytes = kWSlotBytes / 4; wx_step = 128; wy = w_row / 4; }   // w4a16: 32 packed rows x 128 B
+}
+
+__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, int tile_tok) {
   const Tile ti = find_tile(sc, count, t);
   TileRec r;
   r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12);
-  r.x_row  = sc->row0[ti.p] + ti.m_tile * kTT;
-  r.nt     = ti.n_tile | (min(kTT, sc->m_eff[ti.p] - ti.m_tile * kTT) << 16);
+  r.x_row  = sc->row0[ti.p] + ti.m_tile * tile_tok;
+  r.nt     = ti.n_tile | (min(tile_tok, sc->m_eff[ti.p] - ti.m_tile * tile_tok) << 16);
   r.c_row  = r.x_row + sc->c_shift[ti.p];
   return r;
 }
@@ -225,13 +238,17 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     ctrl->abort_flag = 0;
     fence_mbar_init();
   }
-  build_sched(sc, problems, count, kTT, kWT);
+  // launches with packed 4-bit activations use token tiles of 128 rows: the packed rows of a stage (128 x 64 B)
+  // then fit behind the packed weights in the stage's weight slot
+  constexpr int kTileTok = kMode == 2 ? 128 : kTT;
+  build_sched(sc, problems, count, kTileTok, kWT);
   const int total_tiles = sc->total_tiles;
   const int my_tiles    = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-  for (int i = tid; i < my_tiles && i < kMaxRecs; i += blockDim.x) ctrl->recs[i] = make_rec(sc, count, blockIdx.x + i * gridDim.x);
+  for (int i = tid; i < my_tiles && i < kMaxRecs; i += blockDim.x)
+    ctrl->recs[i] = make_rec(sc, count, blockIdx.x + i * gridDim.x, kTileTok);
   auto tile_rec = [&](int i) -> TileRec {
     if (i < kMaxRecs) return ctrl->recs[i];
-    return make_rec(sc, count, blockIdx.x + i * gridDim.x);
+    return make_rec(sc, count, blockIdx.x + i * gridDim.x, kTileTok);
   };
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
@@ -263,18 +280,16 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         const int ntok  = ti.ntok;
         const int x_row = ti.x_row;
         const int w_row = ti.n_tile * kWT;
-        // long token tiles take one 192-row box, short ones only the 32-row boxes they need
+        // long token tiles take one 176-row box, short ones only the 32-row boxes they need
         const bool big  = ntok > 4 * kXBoxSmall;
         const int nbox  = (ntok + kXBoxSmall - 1) / kXBoxSmall;
-        const uint32_t xbytes = big ? (uint32_t)kXSlotBytes : (uint32_t)(nbox * kXBoxSmall * kRowBytes);
+        const uint32_t xbytes = (kMode == 2 && ti.scheme == SCH_W4A4) ? (uint32_t)(nbox * kXBoxSmall * 64)
+                                : big ? (uint32_t)kXSlotBytes : (uint32_t)(nbox * kXBoxSmall * kRowBytes);
         // weights: bytes per stage and coordinates in the weight tensor map
         uint32_t wbytes;
         int wx_step, wy;
-        if (ti.scheme == SCH_W8A8)          { wbytes = kWSlotBytes;     wx_step = 128; wy = w_row; }
-        else if (ti.scheme == SCH_FP16)     { wbytes = kWSlotBytes;     wx_step = 64;  wy = w_row; }
-        else if (ti.scheme == SCH_W4A4_XA)  { wbytes = kWSlotBytes / 2; wx_step = 64;  wy = w_row; }       // 64 packed bytes per row
-        else                                { wbytes = kWSlotBytes / 4; wx_step = 128; wy = w_row / 4; }   // w4a16: 32 packed rows x 128 B
-        const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;
+        weight_coords(ti.scheme, w_row, wbytes, wx_step, wy);
+        const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;   // (packed int4: see below)
         for (int kb = 0; kb < ti.nkb; ++kb) {
           const long long c0 = tick(prof_on);
           const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag);
@@ -288,7 +303,11 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           const uint32_t bar = smem_u32(&ctrl->full[stage]);
           mbar_expect_tx(bar, wbytes + xbytes);
           tma_load_2d(wslot(stage), &pr->tmW, bar, kb * wx_step, wy);
-          if (big) {
+          if (kMode == 2 && ti.scheme == SCH_W4A4) {
+            // packed activation rows (64 bytes of K each) go behind the packed weights; the converters expand them
+            for (int b = 0; b < nbox; ++b)
+              tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, bar, kb * 64, x_row + b * kXBoxSmall);
+          } else if (big) {
             tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
           } else {
             for (int b = 0; b < nbox; ++b)
@@ -389,6 +408,28 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
       const int nchunk     = (ntok + 31) >> 5;
+      // read one transposed chunk back and store it: lane -> (token pair, 8 channels), 16-byte stores
+      auto store_chunk = [&](uint32_t buf, int ch) {
+        const int p8 = lane & 3;   // which 8 channels of the warp's 32
+#pragma unroll
+        for (int rd = 0; rd < 2; ++rd) {
+          const int tp   = (lane >> 2) + 8 * rd;
+          const uint4 a0 = lds128(buf + tp * 128 + (((2 * p8) ^ (tp & 7)) << 4));
+          const uint4 a1 = lds128(buf + tp * 128 + (((2 * p8 + 1) ^ (tp & 7)) << 4));
+          uint4 lo, hi;   // lo: token 2*tp, hi: token 2*tp + 1; 8 consecutive channels each
+          lo.x = __byte_perm(a0.x, a0.y, 0x5410); hi.x = __byte_perm(a0.x, a0.y, 0x7632);
+          lo.y = __byte_perm(a0.z, a0.w, 0x5410); hi.y = __byte_perm(a0.z, a0.w, 0x7632);
+          lo.z = __byte_perm(a1.x, a1.y, 0x5410); hi.z = __byte_perm(a1.x, a1.y, 0x7632);
+          lo.w = __byte_perm(a1.z, a1.w, 0x5410); hi.w = __byte_perm(a1.z, a1.w, 0x7632);
+          const int tk   = ch * 32 + 2 * tp;
+          const int ncol = ti.n_tile * kWT + q * 32 + 8 * p8;
+          __half* dst    = reinterpret_cast<__half*>(pr->C) + (crow0 + tk) * ldc + ncol;
+          if (ncol < N) {
+            if (tk < ntok) *reinterpret_cast<uint4*>(dst) = lo;
+            if (tk + 1 < ntok) *reinterpret_cast<uint4*>(dst + ldc) = hi;
+          }
+        }
+      };
 #pragma unroll 1
       for (int ch = 0; ch < nchunk; ++ch) {
         uint32_t v[32];
@@ -437,25 +478,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
 #pragma unroll
         for (int j = 0; j < 16; ++j) sts32(stg + j * 128 + (((lane >> 2) ^ (j & 7)) << 4) + (lane & 3) * 4, h[j]);
         __syncwarp();
-        const int p8 = lane & 3;   // which 8 channels of the warp's 32
-#pragma unroll
-        for (int rd = 0; rd < 2; ++rd) {
-          const int tp   = (lane >> 2) + 8 * rd;
-          const uint4 a0 = lds128(stg + tp * 128 + (((2 * p8) ^ (tp & 7)) << 4));
-          const uint4 a1 = lds128(stg + tp * 128 + (((2 * p8 + 1) ^ (tp & 7)) << 4));
-          uint4 lo, hi;   // lo: token 2*tp, hi: token 2*tp + 1; 8 consecutive channels each
-          lo.x = __byte_perm(a0.x, a0.y, 0x5410); hi.x = __byte_perm(a0.x, a0.y, 0x7632);
-          lo.y = __byte_perm(a0.z, a0.w, 0x5410); hi.y = __byte_perm(a0.z, a0.w, 0x7632);
-          lo.z = __byte_perm(a1.x, a1.y, 0x5410); hi.z = __byte_perm(a1.x, a1.y, 0x7632);
-          lo.w = __byte_perm(a1.z, a1.w, 0x5410); hi.w = __byte_perm(a1.z, a1.w, 0x7632);
-          const int tk   = ch * 32 + 2 * tp;
-          const int ncol = ti.n_tile * kWT + q * 32 + 8 * p8;
-          __half* dst    = reinterpret_cast<__half*>(pr->C) + (crow0 + tk) * ldc + ncol;
-          if (ncol < N) {
-            if (tk < ntok) *reinterpret_cast<uint4*>(dst) = lo;
-            if (tk + 1 < ntok) *reinterpret_cast<uint4*>(dst + ldc) = hi;
-          }
-        }
+        store_chunk(stg, ch);
       }
       tc_fence_before_sync();
       nbar_arrive(kBarAcc0 + acc, 160);
@@ -537,7 +560,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         if (convert) {
           tc_fence_after_sync();
           uint32_t o[32];
-          if (ti.scheme == SCH_W4A4_XA) {
+          if (ti.scheme == SCH_W4A4_XA || ti.scheme == SCH_W4A4) {
             // packed row: 64 bytes, 16-byte chunks swizzled by (row >> 1) & 3 (64-byte swizzle of the tensor map).
             // Chunk c becomes 32 int8 bytes: its high nibbles, then its low nibbles, each moved to the top of a
             // byte (code q -> byte 16*q; the accumulator is shifted back in the epilogue).
@@ -572,6 +595,12 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             }
           }
           tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + kASlotCol0 + s_cur * kASlotCols, o);
+          if (kMode == 2 && ti.scheme == SCH_W4A4) {
+            // packed activation rows -> int8 rows of the swizzled operand tile (the same nibble -> byte 16*q map)
+            const int rows32 = (ti.ntok + 31) & ~31;
+            convert_w4a4<kCvtGroup * 32>(wslot(s_cur) + kWSlotBytes / 2, wslot(s_cur) + kWSlotBytes, rows32, q * 32 + lane);
+            fence_proxy_async_smem();
+          }
         }
         // the stage's packed weights are in registers (or not needed): release the stage
         __syncwarp();
@@ -610,12 +639,15 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
 cudaError_t gg_configure_swap() {
   cudaError_t e = cudaFuncSetAttribute(gg_swap_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(gg_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
+  e = cudaFuncSetAttribute(gg_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gg_swap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
 }
 
 void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
                     cudaStream_t stream) {
-  if (cvt_mode) gg_swap_kernel<1><<<num_ctas, CfgS<1>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
+  if (cvt_mode == 2) gg_swap_kernel<2><<<num_ctas, CfgS<2>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
+  else if (cvt_mode) gg_swap_kernel<1><<<num_ctas, CfgS<1>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
   else          gg_swap_kernel<0><<<num_ctas, CfgS<0>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
 }
 

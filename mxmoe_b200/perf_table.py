@@ -11,8 +11,9 @@ scheme the persistent kernel is timed on grouped launches whose tile count sweep
 of one wave to many waves at fixed N and K, and ``time = first_iter_cost + inc * tiles`` is fitted
 by least squares over the multi-wave points; ``stderr`` is the residual standard deviation.  The key
 is the ``repr`` of a dataclass with the reference's field names (``tile_config.py:195-207``), so the
-file drops into the solver unchanged; B200 has one tile shape per scheme (128 x 256, 128 bytes of K
-per stage).
+file drops into the solver unchanged; B200 has one tile shape per scheme (up to 176 token rows x 128
+output channels, 128 bytes of K per stage: the kernel with swapped operands; w4a4 is profiled with the
+layer's expanded int4 activations).
 
     python -m mxmoe_b200.perf_table [out.json]
 """
@@ -42,13 +43,13 @@ class QConfig:
 
 @dataclasses.dataclass
 class TileConfig:
-    BM: int = 128
-    BN: int = 256
+    BM: int = 176
+    BN: int = 128
     BK: int = 128
     WM: int = 4
     WN: int = 1
     WK: int = 1
-    STAGE: int = 4
+    STAGE: int = 5
     SPLITK: int = -1
     MMA: str = "TCGEN05_F16_F32"
     QCFGA: object = dataclasses.field(default_factory=NO_QUANT)
@@ -60,12 +61,12 @@ def b200_tile(scheme: str) -> TileConfig:
     from .weights import parse_scheme
     a, w, g, sym = parse_scheme(scheme)
     if a >= 16 and w >= 16:
-        return TileConfig(BK=64, STAGE=4, MMA="TCGEN05_F16_F32")
+        return TileConfig(BK=64, MMA="TCGEN05_F16_F32")
     if a < 16:
         q = QConfig(QBITS=w, GSIZE=g, SYM=sym, PACK_DIM="PackDim::K")
         qa = QConfig(QBITS=a, GSIZE=g, SYM=sym, PACK_DIM="PackDim::K")
-        return TileConfig(BK=128, STAGE=4 if w == 8 else 3, MMA="TCGEN05_S8_S32", QCFGA=qa, QCFGB=q)
-    return TileConfig(BK=64, STAGE=3, MMA="TCGEN05_F16_F32",
+        return TileConfig(BK=128, MMA="TCGEN05_S8_S32", QCFGA=qa, QCFGB=q)
+    return TileConfig(BK=64, MMA="TCGEN05_F16_F32",
                       QCFGB=QConfig(QBITS=w, GSIZE=g, SYM=sym, PACK_DIM="PackDim::MN"))
 
 
@@ -95,12 +96,13 @@ def profile(schemes=None, shapes=((2816, 2048), (2048, 1408)), iters: int = 20) 
         a_bits, w_bits, g, sym = parse_scheme(scheme)
         entry = {"inc_by_nk": {}}
         for (N, K) in shapes:
-            nt = (N + 255) // 256
+            nt = (N + 127) // 128
             pts_t, pts_ms = [], []
             for waves in (0.5, 1, 2, 3, 4, 6, 8, 12, 16):
                 m_tiles = max(1, round(waves * sms / nt))
-                M = m_tiles * 128
-                A = (torch.randint(-30000, 30000, (M, K * a_bits // 16), dtype=torch.int16, device=dev)
+                M = m_tiles * 176
+                expanded = a_bits == 4          # the layer's activation format for w4a4: one byte 16*q per code
+                A = (torch.randint(-30000, 30000, (M, K * (8 if expanded else a_bits) // 16), dtype=torch.int16, device=dev)
                      if a_bits < 16 else torch.randn(M, K, device=dev).half())
                 if w_bits >= 16:
                     B, SB = (torch.randn(N, K, device=dev) * 0.02).half(), None
@@ -113,7 +115,7 @@ def profile(schemes=None, shapes=((2816, 2048), (2048, 1408)), iters: int = 20) 
                 SA = (torch.rand(M, device=dev) * 0.1).half() if a_bits < 16 else None
                 Cc = torch.empty(M, N, dtype=torch.float16, device=dev)
                 run = gg.GroupedGemm([gg.Problem(A=A, B=B, C=Cc, M=M, N=N, K=K, qparams=(a_bits, w_bits, g, sym),
-                                                 scale_a=SA, scale_b=SB)])
+                                                 scale_a=SA, scale_b=SB, a_expanded=1 if expanded else 0)])
                 for _ in range(3):
                     run.run()
                 run.check()

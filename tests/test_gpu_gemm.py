@@ -11,6 +11,7 @@ import torch
 
 from oracle import gemm as og
 from mxmoe_b200 import gg
+from mxmoe_b200._lib import MxMoEError
 from tests import util
 
 pytestmark = pytest.mark.gpu
@@ -225,3 +226,45 @@ def test_bad_arguments_raise(cuda_device):
     p.A = c.A.data_ptr() + 2              # misaligned operand
     with pytest.raises(MxMoEError):
         gg.GroupedGemm([p])
+
+
+def test_redirected_c_rows(cuda_device, gg_kernel):
+    """c_row0_dev: the rows of C start somewhere else than the rows of A (what lets an expert-parallel rank store
+    a segment straight into another rank's buffer).  Only the kernel with swapped operands offers it."""
+    rng = np.random.default_rng(11)
+    counts, c_starts = [200, 3, 77], [400, 0, 100]
+    k, n, bits = 256, 384, 8
+    total = sum(counts)
+    qa = util.rand_codes(rng, total, k, bits)
+    sa = util.rand_scales(rng, total, 0.01, 0.5)
+    from oracle import pack as op
+    A, SA = util.t16(op.pack_k(qa, bits), cuda_device), util.t16(sa, cuda_device)
+    Cbuf = torch.full((700, n), float("nan"), dtype=torch.float16, device=cuda_device)
+    cnt = torch.tensor(counts, dtype=torch.int32, device=cuda_device)
+    starts = torch.tensor(np.concatenate(([0], np.cumsum(counts)[:-1])), dtype=torch.int32, device=cuda_device)
+    cst = torch.tensor(c_starts, dtype=torch.int32, device=cuda_device)
+    probs, refs, keep = [], [], []
+    for e, m in enumerate(counts):
+        qb = util.rand_codes(rng, n, k, bits)
+        sb = util.rand_scales(rng, n)
+        B, SB = util.t16(op.pack_k(qb, bits), cuda_device), util.t16(sb, cuda_device)
+        keep += [B, SB]
+        r0 = int(starts[e])
+        refs.append(og.wxax_epilogue(og.int_accumulate(qa[r0:r0 + m], qb), sa[r0:r0 + m], sb))
+        probs.append(gg.Problem(A=A, B=B, C=Cbuf, M=total, N=n, K=k, qparams=util.Q_W8A8, scale_a=SA, scale_b=SB,
+                                a_rows=total, m_dev=cnt.data_ptr() + 4 * e, row0_dev=starts.data_ptr() + 4 * e,
+                                c_row0_dev=cst.data_ptr() + 4 * e))
+    g = gg.GroupedGemm(probs)
+    assert g._plan.flags & 1
+    if gg_kernel != "swap":
+        with pytest.raises(MxMoEError):
+            g.run()
+        return
+    g.run()
+    g.check()
+    got = Cbuf.cpu().numpy()
+    written = np.zeros(700, dtype=bool)
+    for m, c0, ref in zip(counts, c_starts, refs):
+        assert np.array_equal(got[c0:c0 + m].view(np.uint16), ref.view(np.uint16))
+        written[c0:c0 + m] = True
+    assert np.isnan(got[~written].astype(np.float32)).all(), "rows outside the redirected ranges were written"

@@ -194,3 +194,59 @@ def test_combine(cuda_device):
                                              out.data_ptr(), t, k, h, current_stream_ptr()))
     ref = (y.float()[slot.long()].view(t, k, h) * w[:, :, None]).sum(1) + ysh.float()
     assert torch.allclose(out.float(), ref, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("world,rank", [(1, 0), (3, 1), (4, 3)])
+def test_device_exchange_plan_matches_host_plan(cuda_device, world, rank):
+    """mxmoe_ep_plan on one GPU with made-up counts of `world` ranks against the numpy plan of the NCCL transport."""
+    import ctypes as C
+    from mxmoe_b200 import _lib
+    from mxmoe_b200.ep import ExchangePlan, expert_ranges
+    from mxmoe_b200.gg import current_stream_ptr
+    rng = np.random.default_rng(7 + world)
+    E = 13
+    counts = rng.integers(0, 40, (world, E)).astype(np.int32)
+    counts[:, 2] = 0
+    ranges = expert_ranges(E, world)
+    lo, hi = ranges[rank]
+    el = hi - lo
+    plan = ExchangePlan.build(counts, ranges, rank)
+    i32 = dict(dtype=torch.int32, device=cuda_device)
+    cap = plan.total_recv + 5
+    t = {
+        "counts_all": torch.tensor(counts.reshape(-1), **i32), "range_lo": torch.tensor([r[0] for r in ranges] + [E], **i32),
+        "seg_m": torch.zeros(world * el, **i32), "seg_row0": torch.zeros(world * el, **i32),
+        "seg_src_row0": torch.zeros(world * el, **i32), "recv_row_expert": torch.full((cap,), -1, **i32),
+        "total_recv": torch.zeros(2, **i32), "dst_row0": torch.zeros(E, **i32), "exp_owner": torch.zeros(E, **i32),
+    }
+    a = _lib.EpPlanArgs()
+    for name, ten in t.items():
+        setattr(a, name, ten.data_ptr())
+    a.world, a.rank, a.num_experts, a.experts_local, a.recv_capacity = world, rank, E, el, cap
+    _lib.check(_lib.lib().mxmoe_ep_plan(C.byref(a), current_stream_ptr()))
+    torch.cuda.synchronize()
+    assert t["seg_m"].tolist() == plan.seg_m and t["seg_row0"].tolist() == plan.seg_row0
+    assert t["total_recv"].tolist() == [plan.total_recv, 0]
+    # first row of each segment in the source's expert-sorted order
+    want_src = [int(counts[s, :lo + j].sum()) for s in range(world) for j in range(el)]
+    assert t["seg_src_row0"].tolist() == want_src
+    owner = [next(r for r, (a0, b0) in enumerate(ranges) if a0 <= e < b0) for e in range(E)]
+    assert t["exp_owner"].tolist() == owner
+    # where my rows for expert e start at their owner: behind lower ranks' rows for the owner's experts and my
+    # rows for the owner's earlier experts
+    want_dst = []
+    for e in range(E):
+        dlo, dhi = ranges[owner[e]]
+        want_dst.append(int(counts[:rank, dlo:dhi].sum() + counts[rank, dlo:e].sum()))
+    assert t["dst_row0"].tolist() == want_dst
+    rexp = t["recv_row_expert"].cpu().numpy()
+    want_rexp = np.concatenate([np.full(m, lo + (i % el)) for i, m in enumerate(plan.seg_m)] + [np.full(5, -1)])
+    assert np.array_equal(rexp, want_rexp)
+    # a store that is too small: segments are clipped and the overflow word reports the rows wanted
+    a.recv_capacity = max(plan.total_recv - 7, 0)
+    _lib.check(_lib.lib().mxmoe_ep_plan(C.byref(a), current_stream_ptr()))
+    torch.cuda.synchronize()
+    if plan.total_recv > 7:
+        assert t["total_recv"].tolist() == [plan.total_recv - 7, plan.total_recv]
+        ends = (t["seg_row0"] + t["seg_m"]).max().item()
+        assert ends <= plan.total_recv - 7

@@ -157,7 +157,7 @@ def test_perf_table_schema_matches_the_solver_input():
         sk = "1" if ("a16" in scheme or scheme == "fp16") else "3"
         assert list(by_key) == [sk]
         key = repr(perf_table.b200_tile(scheme))
-        assert key.startswith("TileConfig(BM=128, BN=256, BK=") and key in by_key[sk]
+        assert key.startswith("TileConfig(BM=176, BN=128, BK=") and key in by_key[sk]
         cost = by_key[sk][key]
         assert {"first_iter_cost", "inc", "stderr"} <= set(cost) and cost["inc"] > 0
     # int8 tiles must be cheaper than fp16 tiles of the same shape, 4-bit weight-only the most expensive
