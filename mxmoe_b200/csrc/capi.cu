@@ -246,6 +246,14 @@ int default_kernel() {
   return GGK_SWAP;
 }
 
+// token-tile geometry of the SWAP kernel: the plan's flag unless MXMOE_GG_TILES = small | large overrides it
+bool small_tiles(int plan_flags) {
+  const char* e = getenv("MXMOE_GG_TILES");
+  if (e && !strcmp(e, "small")) return true;
+  if (e && !strcmp(e, "large")) return false;
+  return (plan_flags & 2) != 0;
+}
+
 struct ShimScratch {
   void* ws        = nullptr;
   size_t ws_bytes = 0;
@@ -289,6 +297,7 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   if (problem_count) std::memset(swp.data(), 0, swp.size() * sizeof(mxb::GGSwapProblemDev));
   int kept = 0, needs_cvt = 0;
   bool redirect = false;
+  int max_rows = 0;
   for (int i = 0; i < problem_count; ++i) {
     if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
     rc = build_problem(st->encode, problems[i], i, dev + kept);
@@ -296,6 +305,7 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept]);
     if (rc) return rc;
     if (problems[i].c_row0_dev) redirect = true;
+    if (problems[i].M > max_rows) max_rows = problems[i].M;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
     ++kept;
@@ -312,7 +322,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   if (plan) {
     plan->count     = kept;
     plan->needs_cvt = needs_cvt;
-    plan->flags     = redirect ? 1 : 0;
+    // few rows in every problem: token tiles of 32 rows and a deeper ring (more weight bytes in flight per SM)
+    plan->flags     = (redirect ? 1 : 0) | (max_rows <= 192 ? 2 : 0);
     plan->reserved_ = 0;
   }
   return MXMOE_OK;
@@ -340,7 +351,7 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
   if (kernel == GGK_PAIR && n < 2) kernel = GGK_SINGLE;
   if (kernel == GGK_PAIR)       CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
-  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, n, cs);
+  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, small_tiles(plan->flags), n, cs);
   else                          mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
   CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;

@@ -51,17 +51,30 @@ using namespace ggc;
 namespace {
 
 constexpr int kWSlotBytes  = kWT * kRowBytes;   // 16 KiB: plain weights, or 8 / 4 KiB of packed ones
-constexpr int kXSlotBytes  = kTT * kRowBytes;   // 22 KiB
-constexpr int kStageBytesS = kWSlotBytes + kXSlotBytes;
-constexpr int kStagesS     = 5;
-constexpr int kRingBytesS  = kStagesS * kStageBytesS;   // 190 KiB
-constexpr int kEpiStageS   = 2048;                       // per epilogue warp: 16 token pairs x 32 channels x 4 bytes
+constexpr int kEpiStageS   = 2048;              // per epilogue warp: 16 token pairs x 32 channels x 4 bytes
 constexpr int kCvtWarps    = 8;
-constexpr uint32_t kAccCols = kTT;                       // columns per accumulator
-constexpr uint32_t kASlotCol0 = 2 * kTT;                 // 352: A slot s (one per ring stage) at kASlotCol0 + 32 s
-constexpr uint32_t kASlotCols = 32;
-constexpr int kCvtGroup    = 4;                          // warps per converter group (one per TMEM lane quarter)
-static_assert(kASlotCol0 + kStagesS * kASlotCols <= 512, "tensor memory budget");
+constexpr uint32_t kASlotCols = 32;             // TMEM columns of one A slot (128 bytes of K per channel)
+constexpr int kCvtGroup    = 4;                 // warps per converter group (one per TMEM lane quarter)
+
+// Two geometries of the same kernel.  Large: token tiles of up to 176 rows, ring of 5 stages - for launches
+// with compute-bound problems.  Small: token tiles of up to 32 rows, ring of 10 stages - for launches whose
+// problems all have few rows (decode): what matters there is how many weight bytes are in flight per SM, and a
+// stage of such a tile carries only 4-16 KiB of weights.
+template <bool kSmall>
+struct Geo {
+  static constexpr int kTok        = kSmall ? 32 : kTT;          // tokens per tile (tcgen05 N, any multiple of 16 up to this)
+  static constexpr int kStages     = kSmall ? 10 : 5;
+  static constexpr int kXSlotBytes = kTok * kRowBytes;           // 22 KiB / 4 KiB
+  static constexpr int kStageBytes = kWSlotBytes + kXSlotBytes;
+  static constexpr int kRingBytes  = kStages * kStageBytes;      // 190 KiB / 200 KiB
+  static constexpr uint32_t kAccCols   = kTok;                   // TMEM columns per accumulator
+  static constexpr uint32_t kASlotCol0 = 2 * kTok;               // A slot s (one per ring stage) at kASlotCol0 + 32 s
+  static constexpr int kBarStage0 = 1;                           // named barriers 1 .. kStages: stage s is ready
+  static constexpr int kBarAcc0   = 1 + kStages;                 // two more: accumulator b is drained
+  static_assert(kASlotCol0 + kStages * kASlotCols <= 512, "tensor memory budget");
+  static_assert(kBarAcc0 + 1 <= 15, "named barrier budget");
+  static_assert((kTok + 32) % 8 == 0, "sa_stage rows must stay 16-byte aligned");
+};
 
 template <int kMode>
 struct CfgS {
@@ -83,21 +96,22 @@ struct TileS {
   int p, scheme, nkb, x_row, n_tile, ntok, c_row;
 };
 
+template <typename G>
 struct CtrlS {
-  uint64_t full[kStagesS];
-  uint64_t empty[kStagesS];
-  uint64_t afull[kStagesS];
+  uint64_t full[G::kStages];
+  uint64_t empty[G::kStages];
+  uint64_t afull[G::kStages];
   uint64_t tfull[2];
   uint32_t tmem_base;
   int abort_flag;
   int pad[2];
   Sched sched;
-  alignas(16) __half sa_stage[4][kTT + 32];   // per epilogue warp: per-token scales of the current tile (read 16 bytes at a time)
+  alignas(16) __half sa_stage[4][G::kTok + 32];   // per epilogue warp: per-token scales of the current tile (read 16 bytes at a time)
   alignas(16) TileRec recs[kMaxRecs];
 };
 
-static_assert((kTT + 32) % 8 == 0, "sa_stage rows must stay 16-byte aligned");
-constexpr int smem_bytes_swap() { return 1024 + kRingBytesS + 4 * kEpiStageS + (int)sizeof(CtrlS); }
+template <typename G>
+constexpr int smem_bytes_swap() { return 1024 + G::kRingBytes + 4 * kEpiStageS + (int)sizeof(CtrlS<G>); }
 
 __device__ __forceinline__ void report_s(GGStatus* status, int role, int tile) {
   atomicCAS(&status->error, 0, kDevErrTimeout);
@@ -133,8 +147,8 @@ __device__ __forceinline__ TileS decode_rec(const TileRec& r) {
   return t;
 }
 
-constexpr int kBarStage0 = 1;   // named barriers 1..5: stage s is ready (watcher -> MMA warp), 64 threads
-constexpr int kBarAcc0   = 6;   // named barriers 6, 7: accumulator b is drained (epilogue -> MMA warp), 160 threads
+// named barriers (ids in Geo): stage s is ready (watcher -> MMA warp, 64 threads); accumulator b is drained
+// (epilogue -> MMA warp, 160 threads)
 __device__ __forceinline__ void nbar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -154,18 +168,18 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
 // issue of every MMA several times slower.  All lanes walk the loop and meet the named barrier of each
 // stage; lane 0 issues.  One MMA consumes 32 bytes of K per row: 8 TMEM columns of A or 32 bytes of a
 // shared-memory row.
-template <int kV>
+template <int kV, typename G>
 __device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uint32_t d_tmem, uint32_t idesc,
                                               uint32_t ring_base, uint32_t a_tmem0, uint32_t empty0, bool prof_on,
                                               long long& w_oper, long long& w_issue) {
   for (int kb = 0; kb < nkb; ++kb) {
     const long long c0 = tick(prof_on);
-    nbar_sync(kBarStage0 + stage, 64);   // operands of this stage are in place
+    nbar_sync(G::kBarStage0 + stage, 64);   // operands of this stage are in place
     const long long c1 = tick(prof_on);
     w_oper += c1 - c0;
     if (lane == 0) {
       tc_fence_after_sync();
-      const uint32_t wslot   = ring_base + stage * kStageBytesS;
+      const uint32_t wslot   = ring_base + stage * G::kStageBytes;
       const uint64_t xdesc   = smem_desc_sw128(wslot + kWSlotBytes);
       const uint32_t accum0  = kb > 0 ? 1u : 0u;
       if (kV == 0) {
@@ -197,19 +211,20 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uin
     }
     __syncwarp();
     w_issue += tick(prof_on) - c1;
-    if (++stage == kStagesS) stage = 0;
+    if (++stage == G::kStages) stage = 0;
   }
 }
 
-template <int kMode>
+template <int kMode, bool kSmall>
 __global__ void __launch_bounds__(CfgS<kMode>::kThreads, 1)
 gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatus* __restrict__ status) {
+  using G = Geo<kSmall>;
   constexpr bool kCvt = kMode != 0;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
   uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
-  CtrlS* ctrl              = reinterpret_cast<CtrlS*>(smem_gen + kRingBytesS + 4 * kEpiStageS);
-  const uint32_t epi_base  = smem_base + kRingBytesS;
+  CtrlS<G>* ctrl              = reinterpret_cast<CtrlS<G>*>(smem_gen + G::kRingBytes + 4 * kEpiStageS);
+  const uint32_t epi_base  = smem_base + G::kRingBytes;
   Sched* sc                = &ctrl->sched;
   volatile int* abort_flag = &ctrl->abort_flag;
 
@@ -222,12 +237,12 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     return;
   }
 
-  auto wslot = [&](int s) { return smem_base + s * kStageBytesS; };
-  auto xslot = [&](int s) { return smem_base + s * kStageBytesS + kWSlotBytes; };
+  auto wslot = [&](int s) { return smem_base + s * G::kStageBytes; };
+  auto xslot = [&](int s) { return smem_base + s * G::kStageBytes + kWSlotBytes; };
 
   // ------------------------------------------------------------------ setup
   if (tid == 0) {
-    for (int s = 0; s < kStagesS; ++s) {
+    for (int s = 0; s < G::kStages; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), 1);
       mbar_init(smem_u32(&ctrl->empty[s]), 1 + (kCvt ? kCvtGroup : 0));
       mbar_init(smem_u32(&ctrl->afull[s]), kCvtGroup);
@@ -240,7 +255,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   }
   // launches with packed 4-bit activations use token tiles of 128 rows: the packed rows of a stage (128 x 64 B)
   // then fit behind the packed weights in the stage's weight slot
-  constexpr int kTileTok = kMode == 2 ? 128 : kTT;
+  constexpr int kTileTok = (kMode == 2 && G::kTok > 128) ? 128 : G::kTok;
   build_sched(sc, problems, count, kTileTok, kWT);
   const int total_tiles = sc->total_tiles;
   const int my_tiles    = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -284,7 +299,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         const bool big  = ntok > 4 * kXBoxSmall;
         const int nbox  = (ntok + kXBoxSmall - 1) / kXBoxSmall;
         const uint32_t xbytes = (kMode == 2 && ti.scheme == SCH_W4A4) ? (uint32_t)(nbox * kXBoxSmall * 64)
-                                : big ? (uint32_t)kXSlotBytes : (uint32_t)(nbox * kXBoxSmall * kRowBytes);
+                                : big ? (uint32_t)G::kXSlotBytes : (uint32_t)(nbox * kXBoxSmall * kRowBytes);
         // weights: bytes per stage and coordinates in the weight tensor map
         uint32_t wbytes;
         int wx_step, wy;
@@ -313,7 +328,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             for (int b = 0; b < nbox; ++b)
               tma_load_2d(xslot(stage) + b * kXBoxSmall * kRowBytes, &pr->tmXs, bar, kb * xx_step, x_row + b * kXBoxSmall);
           }
-          if (++stage == kStagesS) { stage = 0; phase ^= 1u; }
+          if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
         }
       }
       if (blockIdx.x == 0) {
@@ -332,26 +347,26 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
       const long long ca = tick(prof_on);
-      if (i >= 2) nbar_sync(kBarAcc0 + acc, 160);     // the epilogue has drained this accumulator (tile i - 2)
+      if (i >= 2) nbar_sync(G::kBarAcc0 + acc, 160);     // the epilogue has drained this accumulator (tile i - 2)
       w_acc += tick(prof_on) - ca;
       const int npad        = (ti.ntok + 15) & ~15;
-      const uint32_t d_tmem = tmem_base + acc * kAccCols;
+      const uint32_t d_tmem = tmem_base + acc * G::kAccCols;
       const bool is_int     = is_int_scheme(ti.scheme);
       const bool from_tmem  = kCvt && is_cvt_scheme(ti.scheme);
       const uint32_t idesc  = is_int ? idesc_i8(kWT, npad) : idesc_f16(kWT, npad);
       const int variant     = (from_tmem ? 2 : 0) + (is_int ? 0 : 1);
-      const uint32_t a_tmem0 = tmem_base + kASlotCol0;
+      const uint32_t a_tmem0 = tmem_base + G::kASlotCol0;
       const uint32_t empty0  = smem_u32(&ctrl->empty[0]);
-      if (variant == 0)      mma_tile_loop<0>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      else if (variant == 1) mma_tile_loop<1>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      else if (variant == 2) mma_tile_loop<2>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      else                   mma_tile_loop<3>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      if (variant == 0)      mma_tile_loop<0, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      else if (variant == 1) mma_tile_loop<1, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      else if (variant == 2) mma_tile_loop<2, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      else                   mma_tile_loop<3, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
       if (lane == 0) mma_commit(smem_u32(&ctrl->tfull[acc]));
       __syncwarp();
       acc ^= 1;
     }
     // consume the "drained" arrivals of the last two tiles, so that no named barrier is left half-way
-    for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(kBarAcc0 + (i & 1), 160);
+    for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(G::kBarAcc0 + (i & 1), 160);
     if (blockIdx.x == 0 && lane == 0) {
       status->prof[PROF_MMA_WAIT_OPER] = w_oper;
       status->prof[PROF_MMA_WAIT_ACC]  = w_acc;
@@ -384,7 +399,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         // everything that does not depend on the accumulator is fetched before waiting for it
         if (n_ch < N) sb2 = __half2half2(__ldg(pr->scale_b + n_ch));
         __syncwarp();
-        for (int i = lane; i < kTT + 32; i += 32)
+        for (int i = lane; i < G::kTok + 32; i += 32)
           saw[i] = (i < ntok) ? pr->scale_a[(grow0 + i) * pr->sa_stride] : __float2half(0.f);
         __syncwarp();
       }
@@ -398,7 +413,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       }
       if (dead) {
         // keep the MMA warp's bar.sync on this accumulator balanced, do nothing else
-        nbar_arrive(kBarAcc0 + acc, 160);
+        nbar_arrive(G::kBarAcc0 + acc, 160);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
         continue;
@@ -406,7 +421,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const long long c1 = tick(prof_on);
       w_epi += c1 - c0;
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * G::kAccCols + ((uint32_t)(q * 32) << 16);
       const int nchunk     = (ntok + 31) >> 5;
       // read one transposed chunk back and store it: lane -> (token pair, 8 channels), 16-byte stores
       auto store_chunk = [&](uint32_t buf, int ch) {
@@ -481,7 +496,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         store_chunk(stg, ch);
       }
       tc_fence_before_sync();
-      nbar_arrive(kBarAcc0 + acc, 160);
+      nbar_arrive(G::kBarAcc0 + acc, 160);
       w_store += tick(prof_on) - c1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -511,8 +526,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             dead = true;
           }
         }
-        nbar_arrive(kBarStage0 + stage, 64);   // always: the MMA warp's bar.sync must complete
-        if (++stage == kStagesS) { stage = 0; phase ^= 1u; }
+        nbar_arrive(G::kBarStage0 + stage, 64);   // always: the MMA warp's bar.sync must complete
+        if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (kCvt) {
@@ -538,16 +553,21 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const bool convert         = is_cvt_scheme(ti.scheme);
       const int N                = pr->N;
       const int gn               = ti.n_tile * kWT + row;
+      // w4a16: (scale, zero) pairs, [K/128][N][2] fp16; one group of 128 k spans two 64-k stages.  The pair of
+      // the group's NEXT stage (two K blocks on) is fetched while the current stage is converted: a global load
+      // at the head of every stage's chain of waits would bound the whole pipeline.
+      const bool has_sz   = ti.scheme == SCH_W4A16G128 && gn < N;
+      const __half2* szp  = reinterpret_cast<const __half2*>(pr->scale_b) + gn;
+      const int kb_first  = (int)((group - it) & 1u);          // first K block of this tile the group handles
+      __half2 sz_next = __float2half2_rn(0.f);
+      if (has_sz && kb_first < ti.nkb) sz_next = __ldg(szp + (int64_t)(kb_first >> 1) * N);
       for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
         const int s_cur       = stage;
         const uint32_t ph_cur = phase;
-        if (++stage == kStagesS) { stage = 0; phase ^= 1u; }
+        if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
         if ((int)(it & 1u) != group) continue;   // the other group's stage
-        __half2 sz = __float2half2_rn(0.f);
-        if (ti.scheme == SCH_W4A16G128 && gn < N) {
-          // (scale, zero) pairs, [K/128][N][2] fp16; one group of 128 k spans two 64-k stages
-          sz = __ldg(reinterpret_cast<const __half2*>(pr->scale_b) + (int64_t)(kb >> 1) * N + gn);
-        }
+        const __half2 sz = sz_next;
+        if (has_sz && kb + 2 < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + 2) >> 1) * N);
         const long long c0 = tick(prof_on);
         const bool ok = warp_wait_bar(smem_u32(&ctrl->full[s_cur]), ph_cur, abort_flag, lane);
         const long long c1 = tick(prof_on);
@@ -594,7 +614,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
               }
             }
           }
-          tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + kASlotCol0 + s_cur * kASlotCols, o);
+          tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + G::kASlotCol0 + s_cur * kASlotCols, o);
           if (kMode == 2 && ti.scheme == SCH_W4A4) {
             // packed activation rows -> int8 rows of the swizzled operand tile (the same nibble -> byte 16*q map)
             const int rows32 = (ti.ntok + 31) & ~31;
@@ -636,19 +656,39 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   }
 }
 
+namespace {
+template <int kMode, bool kSmall>
+cudaError_t configure_one() {
+  return cudaFuncSetAttribute(gg_swap_kernel<kMode, kSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              smem_bytes_swap<Geo<kSmall>>());
+}
+template <int kMode, bool kSmall>
+void launch_one(const GGSwapProblemDev* problems, int count, GGStatus* status, int num_ctas, cudaStream_t stream) {
+  gg_swap_kernel<kMode, kSmall><<<num_ctas, CfgS<kMode>::kThreads, smem_bytes_swap<Geo<kSmall>>(), stream>>>(problems, count, status);
+}
+}  // namespace
+
 cudaError_t gg_configure_swap() {
-  cudaError_t e = cudaFuncSetAttribute(gg_swap_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(gg_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(gg_swap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap());
+  cudaError_t e;
+  if ((e = configure_one<0, false>()) != cudaSuccess) return e;
+  if ((e = configure_one<1, false>()) != cudaSuccess) return e;
+  if ((e = configure_one<2, false>()) != cudaSuccess) return e;
+  if ((e = configure_one<0, true>()) != cudaSuccess) return e;
+  if ((e = configure_one<1, true>()) != cudaSuccess) return e;
+  return configure_one<2, true>();
 }
 
-void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
-                    cudaStream_t stream) {
-  if (cvt_mode == 2) gg_swap_kernel<2><<<num_ctas, CfgS<2>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
-  else if (cvt_mode) gg_swap_kernel<1><<<num_ctas, CfgS<1>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
-  else          gg_swap_kernel<0><<<num_ctas, CfgS<0>::kThreads, smem_bytes_swap(), stream>>>(problems, count, status);
+void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles,
+                    int num_ctas, cudaStream_t stream) {
+  if (small_tiles) {
+    if (cvt_mode == 2)  launch_one<2, true>(problems, count, status, num_ctas, stream);
+    else if (cvt_mode)  launch_one<1, true>(problems, count, status, num_ctas, stream);
+    else                launch_one<0, true>(problems, count, status, num_ctas, stream);
+  } else {
+    if (cvt_mode == 2)  launch_one<2, false>(problems, count, status, num_ctas, stream);
+    else if (cvt_mode)  launch_one<1, false>(problems, count, status, num_ctas, stream);
+    else                launch_one<0, false>(problems, count, status, num_ctas, stream);
+  }
 }
 
 }  // namespace mxb

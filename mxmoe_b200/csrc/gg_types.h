@@ -112,9 +112,10 @@ cudaError_t gg_launch_pair(const GGProblemDev* problems, int count, GGStatus* st
                            cudaStream_t stream);
 cudaError_t gg_configure_pair();
 // kernel with swapped operands (gg_swap_kernel.cu): weights from tensor memory / shared memory as the M side,
-// token tiles of up to 176 rows as the N side; cvt_mode 0 or 1
-void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
-                    cudaStream_t stream);
+// token tiles of up to 176 rows (ring of 5 stages) or, with `small_tiles`, of up to 32 rows (ring of 10 stages)
+// as the N side
+void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles,
+                    int num_ctas, cudaStream_t stream);
 cudaError_t gg_configure_swap();
 
 }  // namespace mxb

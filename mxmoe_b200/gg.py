@@ -97,6 +97,11 @@ class GroupedGemm:
     def kept(self) -> int:
         return self._plan.count
 
+    def set_small_tiles(self, on: bool) -> None:
+        """Override the library's choice of token-tile geometry (32-row tiles and a deeper ring: for launches whose
+        problems hold few rows each, e.g. a decode batch whose row counts only exist on the device)."""
+        self._plan.flags = (self._plan.flags | 2) if on else (self._plan.flags & ~2)
+
     def run(self, num_ctas: int = 0, kernel: str | None = None) -> None:
         """Launch; ``kernel`` in KERNELS names the kernel, None leaves the choice to the library."""
         with torch.cuda.device(self.device):
