@@ -345,19 +345,23 @@ def main():
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = max(3, min(args.steps, 50))
-    def step_e2e():
-        # host -> device copies of this step's inputs into the layer's input buffers, the step, and the
-        # device -> host copy of its result, all on the timed stream
-        hidden.copy_(hidden_host, non_blocking=True)
-        ids_d.copy_(ids_host, non_blocking=True)
-        wts_d.copy_(wts_host, non_blocking=True)
-        out_host.copy_(step_resident(), non_blocking=True)
-    for _ in range(2):
-        step_e2e()
+    # the public serving loop over host buffers (mxmoe_b200.layer.HostPipeline): per step the host -> device copy of
+    # the step's inputs from pinned memory, the layer pass and the device -> host copy of its result; copies of
+    # neighbouring steps overlap the compute on their own streams
+    from mxmoe_b200.layer import HostPipeline
+    pipe = HostPipeline(layer, T, spec.hidden, spec.topk, device=dev, use_graph=use_graph)
+    out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
+
+    def step_e2e(i):
+        pipe.submit(hidden_host, ids_host, wts_host, out_hosts[i & 1])
+    for i in range(4):
+        step_e2e(i)
+    pipe.drain()
     barrier()
     e0.record()
-    for _ in range(e2e_steps):
-        step_e2e()
+    for i in range(e2e_steps):
+        step_e2e(i)
+    pipe.drain()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)

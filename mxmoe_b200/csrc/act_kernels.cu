@@ -202,13 +202,24 @@ struct RowQuant {
     sc   = __half2float(sc_h);
     rcp  = sc != 0.f ? __frcp_rn(sc) : 0.f;
   }
-  __device__ __forceinline__ int code(float v) const {
-    float q = v * rcp;
-    const float r = fmaf(-q, sc, v);
-    q = fmaf(r, rcp, q);
-    q = __half2float(__float2half_rn(q));
-    q = fminf(fmaxf(q, -qmax), qmax);
-    return __float2int_rn(q);
+  // correctly rounded fp32 quotient v / sc (Markstein: one FMA residual, one FMA correction)
+  __device__ __forceinline__ float quotient(float v) const {
+    const float q = v * rcp;
+    return fmaf(fmaf(-q, sc, v), rcp, q);
+  }
+  // Codes of two values: quotient rounded once to fp16 (the reference divides in fp16), clamped, rounded to the
+  // nearest-even integer.  Clamp and rounding run on packed halves, and the integer is read off the mantissa of
+  // 1536 + q (fp16 has unit spacing in [1024, 2048), so the addition IS the round-to-nearest-even): no
+  // float<->half or float->int conversion instruction is issued per value - those share the 16-lane
+  // special-function pipe with exp and reciprocal and were what bound the kernels.
+  __device__ __forceinline__ void code2(float v0, float v1, int& c0, int& c1) const {
+    __half2 h = __floats2half2_rn(quotient(v0), quotient(v1));
+    const __half2 lim = __float2half2_rn(qmax);
+    h = __hmin2(__hmax2(h, __hneg2(lim)), lim);
+    h = __hadd2(h, __float2half2_rn(1536.f));
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(&h);
+    c0 = (int)(b & 0x3ffu) - 512;
+    c1 = (int)((b >> 16) & 0x3ffu) - 512;
   }
 };
 
@@ -268,7 +279,7 @@ __device__ __forceinline__ void emit_row(const float (&x)[kJ][8], float amax, in
     if (ci >= nchunk) continue;
     int code[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) code[e] = rq.code(x[j][e]);
+    for (int e = 0; e < 8; e += 2) rq.code2(x[j][e], x[j][e + 1], code[e], code[e + 1]);
     store_codes(q_dst, ci, tag, code);
   }
 }
@@ -431,8 +442,7 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 f = __half22float2(h[j][e]);
-      code[2 * e]     = rq.code(f.x);
-      code[2 * e + 1] = rq.code(f.y);
+      rq.code2(f.x, f.y, code[2 * e], code[2 * e + 1]);
     }
     store_codes(q_dst, ci, ri.tag, code);
   }

@@ -36,30 +36,54 @@ __global__ void __launch_bounds__(kThreads) route_count_kernel(RouteArgs a) {
   for (int e = threadIdx.x; e < a.num_experts; e += kThreads) a.workspace[blockIdx.x * a.num_experts + e] = hist[e];
 }
 
-// one block: per-expert exclusive prefix over blocks, then exclusive prefix over experts
-__global__ void __launch_bounds__(kThreads) route_scan_kernel(RouteArgs a, int nblocks) {
+// one block: per-expert exclusive prefix over blocks, then exclusive prefix over experts.  A warp owns an
+// expert and scans its per-block counts 32 at a time (independent loads + a shuffle scan); one thread walking
+// the blocks with a load -> store chain per step cost a global-memory latency per block.
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads) route_scan_kernel(RouteArgs a, int nblocks) {
   __shared__ int total[kMaxE];
   __shared__ int start[kMaxE + 1];
   const int E = a.num_experts;
-  for (int e = threadIdx.x; e < E; e += kThreads) {
-    int run = 0;
-    for (int b = 0; b < nblocks; ++b) {
-      const int c = a.workspace[b * E + e];
-      a.workspace[b * E + e] = run;
-      run += c;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < E; e += kScanThreads / 32) {
+    int carry = 0;
+    for (int b0 = 0; b0 < nblocks; b0 += 32) {
+      const int b = b0 + lane;
+      const int c = b < nblocks ? a.workspace[b * E + e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+      }
+      if (b < nblocks) a.workspace[b * E + e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    total[e] = run;
-    a.counts[e] = run;
+    if (lane == 0) {
+      total[e] = carry;
+      a.counts[e] = carry;
+    }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) { start[e] = run; run += total[e]; }
-    start[E] = run;
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int c = e < E ? total[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+      }
+      if (e < E) start[e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) start[E] = carry;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += kThreads) a.row_start[e] = start[e];
-  for (int i = threadIdx.x; i < nblocks * E; i += kThreads) a.workspace[i] += start[i % E];
+  for (int e = threadIdx.x; e <= E; e += kScanThreads) a.row_start[e] = start[e];
+  for (int i = threadIdx.x; i < nblocks * E; i += kScanThreads) a.workspace[i] += start[i % E];
 }
 
 __global__ void __launch_bounds__(kThreads) route_scatter_kernel(RouteArgs a) {
@@ -162,7 +186,7 @@ cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream) {
   const int nblocks = (n + kChunk - 1) / kChunk;
   if (a.num_experts > kMaxE) return cudaErrorInvalidValue;
   if (nblocks > 0) route_count_kernel<<<nblocks, kThreads, 0, stream>>>(a);
-  route_scan_kernel<<<1, kThreads, 0, stream>>>(a, nblocks);
+  route_scan_kernel<<<1, kScanThreads, 0, stream>>>(a, nblocks);
   if (nblocks > 0) route_scatter_kernel<<<nblocks, kThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }

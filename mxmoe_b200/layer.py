@@ -368,3 +368,65 @@ class MoELayer:
                 a_bits = w.qparams[0]
                 total += m * k * a_bits // 8 + w.nbytes() + m * n * 2 + (m * 2 if a_bits < 16 else 0)
         return total
+
+
+class HostPipeline:
+    """Serving loop over HOST buffers: the host->device copy of step i + 1, the layer pass of step i and the
+    device->host copy of the result of step i - 1 run concurrently (copy-in stream, compute stream, copy-out
+    stream, two sets of device buffers, events between them).  ``layer`` is a :class:`MoELayer` (replayed from
+    its CUDA graph) or any object with ``forward(hidden, ids, weights) -> [T, H]``.
+
+        pipe = HostPipeline(layer, T, H, topk)
+        for hidden_host, ids_host, wts_host, out_host in batches:     # pinned host tensors
+            pipe.submit(hidden_host, ids_host, wts_host, out_host)
+        pipe.drain()                                                  # out_host of every submitted step is complete
+    """
+
+    def __init__(self, layer, tokens: int, hidden: int, topk: int, device=None, use_graph: bool = True):
+        self.layer = layer
+        self.device = torch.device(device) if device is not None else layer.device
+        dev = self.device
+        self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.bufs = [dict(hidden=torch.empty(tokens, hidden, dtype=torch.float16, device=dev),
+                          ids=torch.empty(tokens, topk, dtype=torch.int32, device=dev),
+                          wts=torch.empty(tokens, topk, dtype=torch.float32, device=dev),
+                          out=torch.empty(tokens, hidden, dtype=torch.float16, device=dev),
+                          ev_in=torch.cuda.Event(), ev_comp=torch.cuda.Event(), ev_out=torch.cuda.Event())
+                     for _ in range(2)]
+        # the layer's graph bakes in the addresses of its inputs: one static set, filled by device copies
+        self.x = torch.empty(tokens, hidden, dtype=torch.float16, device=dev)
+        self.i = torch.empty(tokens, topk, dtype=torch.int32, device=dev)
+        self.w = torch.empty(tokens, topk, dtype=torch.float32, device=dev)
+        self.use_graph = use_graph and hasattr(layer, "forward_graph")
+        self.step = 0
+
+    def submit(self, hidden_host, ids_host, wts_host, out_host) -> None:
+        b = self.bufs[self.step & 1]
+        comp = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.s_in):
+            if self.step >= 2:
+                self.s_in.wait_event(b["ev_comp"])          # step - 2 no longer reads this input set
+            b["hidden"].copy_(hidden_host, non_blocking=True)
+            b["ids"].copy_(ids_host, non_blocking=True)
+            b["wts"].copy_(wts_host, non_blocking=True)
+            b["ev_in"].record(self.s_in)
+        comp.wait_event(b["ev_in"])
+        if self.step >= 2:
+            comp.wait_event(b["ev_out"])                    # step - 2's result has left this output buffer
+        self.x.copy_(b["hidden"], non_blocking=True)
+        self.i.copy_(b["ids"], non_blocking=True)
+        self.w.copy_(b["wts"], non_blocking=True)
+        fwd = self.layer.forward_graph if self.use_graph else self.layer.forward
+        b["out"].copy_(fwd(self.x, self.i, self.w), non_blocking=True)
+        b["ev_comp"].record(comp)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(b["ev_comp"])
+            out_host.copy_(b["out"], non_blocking=True)
+            b["ev_out"].record(self.s_out)
+        self.step += 1
+
+    def drain(self) -> None:
+        """Make the compute stream wait for every copy that is still in flight."""
+        comp = torch.cuda.current_stream(self.device)
+        comp.wait_stream(self.s_in)
+        comp.wait_stream(self.s_out)
