@@ -61,9 +61,10 @@ __device__ __forceinline__ int c_shift_of(const GGSwapProblemDev& pr, int r0) {
   return pr.c_row0_dev ? *pr.c_row0_dev - r0 : 0;
 }
 
+// `packed_rows_per_tile` (> 0) replaces rows_per_tile for problems with packed 4-bit activations
 template <typename Problem>
 __device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, int count, int rows_per_tile,
-                                            int cols_per_tile = kBN) {
+                                            int cols_per_tile = kBN, int packed_rows_per_tile = 0) {
   const int tid = threadIdx.x, lane = tid & 31;
   for (int p = tid; p < count; p += blockDim.x) {
     const Problem& pr = problems[p];
@@ -73,7 +74,8 @@ __device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, 
     const int nt     = (pr.N + cols_per_tile - 1) / cols_per_tile;
     const int kelems = (pr.scheme == SCH_FP16 || pr.scheme == SCH_W4A16G128) ? 64 : 128;
     const int nkb    = (pr.K + kelems - 1) / kelems;
-    sc->tile_end[p] = ((m + rows_per_tile - 1) / rows_per_tile) * nt;
+    const int rpt   = (packed_rows_per_tile > 0 && pr.scheme == SCH_W4A4) ? packed_rows_per_tile : rows_per_tile;
+    sc->tile_end[p] = ((m + rpt - 1) / rpt) * nt;
     sc->m_eff[p]    = m;
     sc->row0[p]     = r0;
     sc->meta[p]     = (nt << 16) | (nkb << 4) | pr.scheme;

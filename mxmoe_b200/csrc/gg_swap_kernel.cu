@@ -131,8 +131,9 @@ __device__ __forceinline__ void weight_coords(int scheme, int w_row, uint32_t& w
   else                            { wbytes = kWSlotBytes / 4; wx_step = 128; wy = w_row / 4; }   // w4a16: 32 packed rows x 128 B
 }
 
-__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, int tile_tok) {
-  const Tile ti = find_tile(sc, count, t);
+__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, int tok, int tok_packed) {
+  const Tile ti      = find_tile(sc, count, t);
+  const int tile_tok = ti.scheme == SCH_W4A4 ? tok_packed : tok;   // problems with packed activations: shorter tiles
   TileRec r;
   r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12);
   r.x_row  = sc->row0[ti.p] + ti.m_tile * tile_tok;
@@ -253,17 +254,17 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     ctrl->abort_flag = 0;
     fence_mbar_init();
   }
-  // launches with packed 4-bit activations use token tiles of 128 rows: the packed rows of a stage (128 x 64 B)
-  // then fit behind the packed weights in the stage's weight slot
-  constexpr int kTileTok = (kMode == 2 && G::kTok > 128) ? 128 : G::kTok;
-  build_sched(sc, problems, count, kTileTok, kWT);
+  // problems with packed 4-bit activations use token tiles of at most 128 rows: the packed rows of a stage
+  // (128 x 64 B) then fit behind the packed weights in the stage's weight slot
+  constexpr int kTokPacked = G::kTok > 128 ? 128 : G::kTok;
+  build_sched(sc, problems, count, G::kTok, kWT, kTokPacked);
   const int total_tiles = sc->total_tiles;
   const int my_tiles    = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   for (int i = tid; i < my_tiles && i < kMaxRecs; i += blockDim.x)
-    ctrl->recs[i] = make_rec(sc, count, blockIdx.x + i * gridDim.x, kTileTok);
+    ctrl->recs[i] = make_rec(sc, count, blockIdx.x + i * gridDim.x, G::kTok, kTokPacked);
   auto tile_rec = [&](int i) -> TileRec {
     if (i < kMaxRecs) return ctrl->recs[i];
-    return make_rec(sc, count, blockIdx.x + i * gridDim.x, kTileTok);
+    return make_rec(sc, count, blockIdx.x + i * gridDim.x, G::kTok, kTokPacked);
   };
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctrl->tmem_base), 512);

@@ -34,7 +34,7 @@ import torch.distributed as dist
 
 from . import _lib
 from .gg import current_stream_ptr
-from .layer import ExpertCompute, MoELayer, TokenQuant, record_stride, tag_of
+from .layer import ExpertCompute, MoELayer, TokenQuant, internal_tag, record_stride, tag_of
 
 
 def expert_ranges(num_experts: int, world: int) -> list[tuple[int, int]]:
@@ -121,20 +121,41 @@ class EPMoELayer:
     """Expert-parallel layer for ``spec`` (a :class:`mxmoe_b200.workload.LayerSpec`): ``spec.tokens`` tokens per rank."""
 
     def __init__(self, spec, device, gen_device="cpu", capacity_factor: float = 3.0, group=None,
-                 placement: str = "balanced", transport: str | None = None, loads=None):
+                 placement: str = "balanced", transport: str | None = None, loads=None, granularity: int = 2,
+                 dispatch_format: str | None = None):
         from . import workload
         self.spec, self.device, self.group = spec, torch.device(device), group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.transport = transport or os.environ.get("MXMOE_EP_TRANSPORT", "p2p")
+        # int4 activation rows cross NVLink either packed (two codes per byte: half the bytes, but the receiving
+        # GEMM then has to expand them in shared memory, which costs it about a third of its speed) or already
+        # expanded to one byte per code (the layer's internal format): expanded is the default on NVLink
+        self.dispatch_format = dispatch_format or os.environ.get("MXMOE_EP_DISPATCH", "expanded")
+        if self.dispatch_format not in ("expanded", "packed"):
+            raise ValueError(f"unknown dispatch format {self.dispatch_format!r}")
+        self._tag_fn = internal_tag if self.dispatch_format == "expanded" else tag_of
         if self.transport not in ("p2p", "nccl"):
             raise ValueError(f"unknown transport {self.transport!r}")
-        E, T, k, H, I = spec.num_experts, spec.tokens, spec.topk, spec.hidden, spec.inter
+        E0, T, k, H, I = spec.num_experts, spec.tokens, spec.topk, spec.hidden, spec.inter
+        # Virtual experts: an expert whose expected load exceeds 1 / (world * granularity) of the rows is
+        # REPLICATED (same weights on several ranks) and its rows are dealt to the replicas by token index, so
+        # that no single expert can hold more than a rank's fair share (the hottest expert of a skewed routing
+        # otherwise bounds the step).  Everything below works on the virtual experts; vorig maps them back.
+        reps = [1] * E0
         if placement == "balanced":
             # expected rows per expert: a calibration routing sample of the workload unless the caller has a trace
             if loads is None:
                 cal, _ = workload.make_routing(spec, seed=1234)
-                loads = torch.bincount(cal.reshape(-1).long(), minlength=E).tolist()
-            remap, inverse, self.ranges = balanced_placement(loads, self.world)
+                loads = torch.bincount(cal.reshape(-1).long(), minlength=E0).tolist()
+            if self.world > 1 and granularity > 0:
+                target = max(1.0, float(sum(loads)) / (self.world * granularity))
+                reps = [max(1, min(self.world, -(-int(l) // int(target + 0.5)))) for l in loads]
+        self.vorig = [e for e in range(E0) for _ in range(reps[e])]
+        E = len(self.vorig)
+        self.replicated = E > E0
+        if placement == "balanced":
+            vloads = [float(loads[e]) / reps[e] for e in self.vorig]
+            remap, inverse, self.ranges = balanced_placement(vloads, self.world)
         elif placement == "strided":
             remap, inverse, self.ranges = strided_placement(E, self.world)
         else:
@@ -143,17 +164,26 @@ class EPMoELayer:
         dev = self.device
         i32 = dict(dtype=torch.int32, device=dev)
         f16 = dict(dtype=torch.float16, device=dev)
-        self.remap = torch.tensor(remap, **i32)
+        self.remap = torch.tensor(remap, **i32)                       # virtual expert -> new (rank-major) id
+        vbase = [0] * E0
+        for e in range(1, E0):
+            vbase[e] = vbase[e - 1] + reps[e - 1]
+        self.vbase = torch.tensor(vbase, **i32)                       # original expert -> its first virtual expert
+        self.vrep = torch.tensor(reps, **i32)
+        self.slot_token = torch.arange(T, **i32).repeat_interleave(k)  # token of every (token, slot) pair
 
         # weights of the local experts, keyed by their NEW ids (the shared expert keeps key E)
+        local_orig = [self.vorig[inverse[n]] for n in range(lo, hi)]
         gu_o, dn_o, signs, (gu_s, dn_s) = workload.build_layer_weights(
-            spec, experts=[inverse[n] for n in range(lo, hi)], gen_device=gen_device, device=dev)
-        gate_up = {(remap[e] if e < E else E): w for e, w in gu_o.items()}
-        down = {(remap[e] if e < E else E): w for e, w in dn_o.items()}
+            spec, experts=sorted(set(local_orig)), gen_device=gen_device, device=dev)
+        gate_up = {n: gu_o[self.vorig[inverse[n]]] for n in range(lo, hi)}
+        down = {n: dn_o[self.vorig[inverse[n]]] for n in range(lo, hi)}
         self.has_shared = spec.shared_inter > 0
+        if self.has_shared:
+            gate_up[E], down[E] = gu_o[E0], dn_o[E0]
         # activation format of EVERY expert (also the remote ones) by new id: decides what is sent
-        tags_orig = [tag_of(workload.parse_scheme(s)) for s in gu_s]
-        self._tag1 = [tags_orig[inverse[n]] for n in range(E)] + [tags_orig[E] if self.has_shared else 0]
+        tags_orig = [self._tag_fn(workload.parse_scheme(s)) for s in gu_s]
+        self._tag1 = [tags_orig[self.vorig[inverse[n]]] for n in range(E)] + [tags_orig[E0] if self.has_shared else 0]
         # routing + per-token quantiser reuse the single-GPU layer's machinery without its compute core
         self.front = MoELayer.__new__(MoELayer)
         f = self.front
@@ -171,6 +201,7 @@ class EPMoELayer:
         # records: packed row (P fp16 elements) + 8 elements carrying the per-token scale
         self.P = record_stride(H, set(self._tag1[:E]))
         self.rec = self.P + 8
+        self.E = E
         self.R_send = T * k
         self.R_recv = int(T * k * capacity_factor)
         self.out = torch.zeros(T, H, **f16)
@@ -219,7 +250,7 @@ class EPMoELayer:
         spec = self.spec
         shared = None
         if self.has_shared:
-            a_ptr, sa_ptr = self.tq.rows_of(self._tag1[spec.num_experts], hidden)
+            a_ptr, sa_ptr = self.tq.rows_of(self._tag1[self.E], hidden)
             shared = {"tokens": spec.tokens, "a_ptr": a_ptr, "sa_ptr": sa_ptr}
         down_out = None
         if self.transport == "p2p":
@@ -228,10 +259,10 @@ class EPMoELayer:
             el = self.ranges[self.rank][1] - self.ranges[self.rank][0]
             down_out = [(self.peer_ret[i // el], self.seg_src_row0.data_ptr() + 4 * i) for i in range(self.world * el)]
         self._core = ExpertCompute(
-            spec.num_experts, spec.hidden, spec.inter, self._gate_up, self._down, self.R_recv, self.seg_expert,
+            self.E, spec.hidden, spec.inter, self._gate_up, self._down, self.R_recv, self.seg_expert,
             self.seg_tab[0], self.seg_tab[1], self.recv_row_expert, self.recv.view(-1), self.rec,
             self.recv.data_ptr() + self.P * 2, self.rec, self.device, shared=shared, shared_inter=spec.shared_inter,
-            tag_fn=tag_of,     # dispatched rows stay packed (half the NVLink bytes of the expanded format)
+            tag_fn=self._tag_fn,
             down_out=down_out, rows_dev=self.total_recv if self.transport == "p2p" else None)
 
     def _mark(self, marks, name):
@@ -240,6 +271,15 @@ class EPMoELayer:
             ev.record()
             marks.append((name, ev))
 
+    def _renumber(self, topk_ids: torch.Tensor) -> None:
+        """Original expert ids -> new ids (virtual expert chosen by token index, then the rank-major numbering)."""
+        flat = topk_ids.reshape(-1)
+        if not self.replicated:
+            torch.index_select(self.remap, 0, flat, out=self.ids_new.view(-1))
+            return
+        virt = torch.index_select(self.vbase, 0, flat) + torch.remainder(self.slot_token, torch.index_select(self.vrep, 0, flat))
+        torch.index_select(self.remap, 0, virt, out=self.ids_new.view(-1))
+
     def _barrier(self):
         """Every rank's earlier kernels on this stream (their peer stores included) are complete before any
         rank's later kernels start: a one-element all-reduce, ordered on the stream, no host involvement."""
@@ -247,14 +287,14 @@ class EPMoELayer:
 
     def _forward_p2p(self, hidden, topk_ids, topk_weights):
         spec, f = self.spec, self.front
-        T, k, H, E = spec.tokens, spec.topk, spec.hidden, spec.num_experts
+        T, k, H, E = spec.tokens, spec.topk, spec.hidden, self.E
         lib = _lib.lib()
         marks = []
         with torch.cuda.device(self.device):
             if self._core is None:
                 self._build_core(hidden)
             self._mark(marks, "start")
-            torch.index_select(self.remap, 0, topk_ids.reshape(-1), out=self.ids_new.view(-1))
+            self._renumber(topk_ids)
             f.route(self.ids_new)
             t = self.tq.run(hidden)
             self._mark(marks, "route+quant")
@@ -303,7 +343,7 @@ class EPMoELayer:
             if self._core is None:
                 self._build_core(hidden)
             self._mark(marks, "start")
-            torch.index_select(self.remap, 0, topk_ids.reshape(-1), out=self.ids_new.view(-1))
+            self._renumber(topk_ids)
             f.route(self.ids_new)
             t = self.tq.run(hidden)
             f.gather(t, T * k, self.send.view(-1), self.rec, None, rec_scale_off=self.P)

@@ -30,12 +30,12 @@ def run(spec_name: str = "tiny-ep") -> None:
     ids, wts = workload.make_routing(spec, seed=2 + rank)
     ids, wts = ids.to(dev), wts.to(dev)
     outs = {}
-    for transport in ("p2p", "nccl"):
-        ep = EPMoELayer(spec, dev, capacity_factor=float(world) + 1.0, transport=transport)
+    for transport, fmt in (("p2p", "expanded"), ("p2p", "packed"), ("nccl", "packed")):
+        ep = EPMoELayer(spec, dev, capacity_factor=float(world) + 1.0, transport=transport, dispatch_format=fmt)
         out_ep = ep.forward(hidden, ids, wts).clone()
         out_ep2 = ep.forward(hidden, ids, wts).clone()          # a second step reuses every buffer
         ep.check()
-        outs[transport] = (out_ep, out_ep2)
+        outs[transport + "/" + fmt] = (out_ep, out_ep2)
         if transport == "nccl":
             assert sum(ep.last_plan.send_rows) == spec.tokens * spec.topk
         else:
