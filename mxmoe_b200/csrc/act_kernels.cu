@@ -212,16 +212,35 @@ struct RowQuant {
   // 1536 + q (fp16 has unit spacing in [1024, 2048), so the addition IS the round-to-nearest-even): no
   // float<->half or float->int conversion instruction is issued per value - those share the 16-lane
   // special-function pipe with exp and reciprocal and were what bound the kernels.
-  __device__ __forceinline__ void code2(float v0, float v1, int& c0, int& c1) const {
+  // bit pattern of (1536 + code0, 1536 + code1) as packed halves: the two's-complement code sits in the low
+  // mantissa bits (512 is a multiple of 16 and of 256, so `bits & 0xf` / `bits & 0xff` IS the 4- / 8-bit code)
+  __device__ __forceinline__ uint32_t bits2(float v0, float v1) const {
     __half2 h = __floats2half2_rn(quotient(v0), quotient(v1));
     const __half2 lim = __float2half2_rn(qmax);
     h = __hmin2(__hmax2(h, __hneg2(lim)), lim);
     h = __hadd2(h, __float2half2_rn(1536.f));
-    const uint32_t b = *reinterpret_cast<const uint32_t*>(&h);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  __device__ __forceinline__ void code2(float v0, float v1, int& c0, int& c1) const {
+    const uint32_t b = bits2(v0, v1);
     c0 = (int)(b & 0x3ffu) - 512;
     c1 = (int)((b >> 16) & 0x3ffu) - 512;
   }
 };
+
+// Expanded int4 (tag 3) straight from the packed-half bit patterns of 8 consecutive codes (b01 = codes 0, 1; ...):
+// the same bytes store_codes produces for tag 3 - every code as the byte 16*q, high nibbles of the packed row's
+// bytes first - with shifts, masks and byte permutes only.
+__device__ __forceinline__ void store_expanded4(__half* q_dst, int ci, uint32_t b01, uint32_t b23, uint32_t b45,
+                                                uint32_t b67) {
+  const uint32_t x01 = (b01 << 4) & 0x00F000F0u, x23 = (b23 << 4) & 0x00F000F0u;   // byte 0: even code, byte 2: odd code
+  const uint32_t x45 = (b45 << 4) & 0x00F000F0u, x67 = (b67 << 4) & 0x00F000F0u;
+  const uint32_t ylo = __byte_perm(x23, x01, 0x6240);   // c2, c0, c3, c1
+  const uint32_t yhi = __byte_perm(x67, x45, 0x6240);   // c6, c4, c7, c5
+  uint32_t* d = reinterpret_cast<uint32_t*>(q_dst) + 8 * (ci >> 2) + (ci & 3);
+  d[0] = __byte_perm(ylo, yhi, 0x5410);                 // c2, c0, c6, c4
+  d[4] = __byte_perm(ylo, yhi, 0x7632);                 // c3, c1, c7, c5
+}
 
 // pack 8 consecutive codes of a row and store them as chunk `ci` of the packed row
 __device__ __forceinline__ void store_codes(__half* q_dst, int ci, int tag, const int (&code)[8]) {
@@ -277,6 +296,11 @@ __device__ __forceinline__ void emit_row(const float (&x)[kJ][8], float amax, in
   for (int j = 0; j < kJ; ++j) {
     const int ci = chunk_of<kWarps>(w, j, lane);
     if (ci >= nchunk) continue;
+    if (tag == 3) {
+      store_expanded4(q_dst, ci, rq.bits2(x[j][0], x[j][1]), rq.bits2(x[j][2], x[j][3]), rq.bits2(x[j][4], x[j][5]),
+                      rq.bits2(x[j][6], x[j][7]));
+      continue;
+    }
     int code[8];
 #pragma unroll
     for (int e = 0; e < 8; e += 2) rq.code2(x[j][e], x[j][e + 1], code[e], code[e + 1]);
@@ -438,6 +462,16 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
   for (int j = 0; j < kJ; ++j) {
     const int ci = chunk_of<kWarps>(w, j, lane);
     if (ci >= nchunk) continue;
+    if (ri.tag == 3) {
+      uint32_t b[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[j][e]);
+        b[e] = rq.bits2(f.x, f.y);
+      }
+      store_expanded4(q_dst, ci, b[0], b[1], b[2], b[3]);
+      continue;
+    }
     int code[8];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {

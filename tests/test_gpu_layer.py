@@ -140,6 +140,30 @@ def test_graph_replay_matches_eager(cuda_device):
     assert torch.equal(got2, want2) and not torch.equal(got2, want)
 
 
+def test_host_pipeline_matches_forward(cuda_device):
+    """The serving loop over host buffers: five different batches through the three-stream pipeline give the bits
+    of five plain forward passes."""
+    from mxmoe_b200.layer import HostPipeline
+    spec = _spec("w4a4_g-1_sym", False, True, tokens=80)
+    gate_up, down, signs, _ = workload.build_layer_weights(spec, device=cuda_device)
+    lay = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens,
+                   signs=signs, rotate=True, device=cuda_device)
+    batches = []
+    for i in range(5):
+        ids, wts = workload.make_routing(spec, seed=20 + i)
+        batches.append((workload.make_hidden(spec, seed=40 + i).pin_memory(), ids.pin_memory(), wts.pin_memory(),
+                        torch.zeros(spec.tokens, spec.hidden, dtype=torch.float16).pin_memory()))
+    pipe = HostPipeline(lay, spec.tokens, spec.hidden, spec.topk, device=cuda_device)
+    for b in batches:
+        pipe.submit(*b)
+    pipe.drain()
+    torch.cuda.synchronize()
+    lay.check()
+    for h, i, w, out in batches:
+        want = lay.forward(h.to(cuda_device), i.to(cuda_device), w.to(cuda_device)).cpu()
+        assert torch.equal(out, want)
+
+
 def test_layer_empty_experts_and_decode_batch(cuda_device):
     """Decode-sized batch: most experts receive no token."""
     spec = workload.LayerSpec("tiny-decode", 16, 2, 512, 256, 0, 3, "zipf", 1.0, False, False, "w4a16_g128_asym")
