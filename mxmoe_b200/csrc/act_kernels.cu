@@ -166,7 +166,12 @@ __device__ __forceinline__ void rotate_row(float (&x)[kJ][8], const int8_t* sign
 #pragma unroll
   for (int j = 0; j < kJ; ++j)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) x[j][e] = __half2float(__float2half_rn(x[j][e] * norm));
+    for (int e = 0; e < 8; e += 2) {
+      // round to fp16 values two at a time (packed conversion)
+      const float2 r = __half22float2(__floats2half2_rn(x[j][e] * norm, x[j][e + 1] * norm));
+      x[j][e]     = r.x;
+      x[j][e + 1] = r.y;
+    }
 }
 
 template <int kWarps>
@@ -347,7 +352,7 @@ __global__ void __launch_bounds__(kBlock) quant_act_kernel(ActArgs a) {
 // ---------------------------------------------------------------------------------------------
 // (rotate) + quantise once per token into token-major stores, one per activation format in use
 template <int kWarps>
-__global__ void __launch_bounds__(kBlock) quant_tokens_kernel(TokenQuantArgs a) {
+__global__ void __launch_bounds__(kBlock, 3) quant_tokens_kernel(TokenQuantArgs a) {
   __shared__ float xch[kWarps > 1 ? kBlock * 8 : 1];
   __shared__ float red[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -396,7 +401,7 @@ __global__ void __launch_bounds__(kBlock) gather_rows_kernel(ActArgs a, TokenQua
 // h = silu(gate) * up, then quantise; one pass per routed row.  Values are fp16 after the product,
 // so they are kept as half2 (32 registers per thread for 64 values).
 template <int kWarps>
-__global__ void __launch_bounds__(kBlock) silu_mul_quant_kernel(ActArgs a) {
+__global__ void __launch_bounds__(kBlock, 5) silu_mul_quant_kernel(ActArgs a) {
   __shared__ float red[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_in_blk = warp / kWarps, w = warp % kWarps;

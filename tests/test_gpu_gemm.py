@@ -19,12 +19,18 @@ pytestmark = pytest.mark.gpu
 REL_L2 = 1e-3
 
 
-@pytest.fixture(autouse=True, params=["swap", "pair", "single"])
+@pytest.fixture(autouse=True, params=["swap", "swap-small", "pair", "single"])
 def gg_kernel(request, monkeypatch):
-    """Every test of this file runs once per kernel: swapped operands (128 channels x 192 tokens, 4-bit weights
-    through tensor memory), CTA pairs (256 x 256 tiles, cta_group::2) and single CTAs (128 x 256 tiles)."""
-    monkeypatch.setenv("MXMOE_GG_KERNEL", request.param)
-    yield request.param
+    """Every test of this file runs once per kernel: swapped operands (128 channels x up to 176 tokens, 4-bit
+    weights through tensor memory; "swap-small" forces its geometry for few rows - 32-token tiles, ring of 10 stages -
+    on every shape), CTA pairs (256 x 256 tiles, cta_group::2) and single CTAs (128 x 256 tiles)."""
+    kernel = request.param.split("-")[0]
+    monkeypatch.setenv("MXMOE_GG_KERNEL", kernel)
+    if request.param == "swap-small":
+        monkeypatch.setenv("MXMOE_GG_TILES", "small")
+    else:
+        monkeypatch.delenv("MXMOE_GG_TILES", raising=False)
+    yield kernel
 
 # (M, N, K): one tile / one k-block; ragged M; ragged N tile; several k-blocks; layer shapes
 SHAPES_INT = [(128, 256, 128), (1, 256, 128), (17, 256, 256), (129, 512, 384), (300, 2816, 2048), (77, 2048, 1408),
