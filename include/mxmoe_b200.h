@@ -103,7 +103,7 @@ typedef struct mxmoe_gg_plan {
   int32_t needs_cvt; /* kernel variant: 0 no 4-bit operand, 1 4-bit weights only, 2 packed 4-bit activations too */
   int32_t flags;     /* bit 0: a problem redirects its C rows (c_row0_dev): only the SWAP kernel can run it;
                         bit 1: SWAP kernel with token tiles of 32 rows and a ring of 10 stages (set by prepare when no
-                        problem has more than 192 rows; the caller may set or clear it before mxmoe_gg_run, e.g. set
+                        problem has more than 32 rows; the caller may set or clear it before mxmoe_gg_run, e.g. set
                         it when the row counts come from device memory and are known to be small on average) */
   int32_t reserved_;
 } mxmoe_gg_plan;

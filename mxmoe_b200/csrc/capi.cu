@@ -323,7 +323,7 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     plan->count     = kept;
     plan->needs_cvt = needs_cvt;
     // few rows in every problem: token tiles of 32 rows and a deeper ring (more weight bytes in flight per SM)
-    plan->flags     = (redirect ? 1 : 0) | (max_rows <= 192 ? 2 : 0);
+    plan->flags     = (redirect ? 1 : 0) | (max_rows <= 32 ? 2 : 0);
     plan->reserved_ = 0;
   }
   return MXMOE_OK;

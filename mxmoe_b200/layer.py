@@ -141,7 +141,7 @@ class ExpertCompute:
         self.gg1 = GroupedGemm(p1, device=dev)
         self.gg2 = GroupedGemm(p2, device=dev)
         # row counts live on the device; few rows per segment on average (a decode batch): small token tiles
-        if self.seg_expert and rows_cap / len(self.seg_expert) <= 32 and (shared is None or shared["tokens"] <= 192):
+        if self.seg_expert and rows_cap / len(self.seg_expert) <= 16 and (shared is None or shared["tokens"] <= 64):
             self.gg1.set_small_tiles(True)
             self.gg2.set_small_tiles(True)
         self.launches = 3 + (1 if shared is not None else 0)
