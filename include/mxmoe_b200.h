@@ -267,6 +267,14 @@ int mxmoe_route_topk(const mxmoe_route_args* args, void* stream);
  * It calls no cudaMalloc / cudaFree and no allocating library routine. */
 int mxmoe_route_topk_static(const mxmoe_route_args* args, void* stream);
 
+/* Router gate on the device: softmax over the expert logits of every token (fp32 arithmetic), the top-k
+ * probabilities and their experts, renormalised to sum 1 if `renormalize` (the softmax -> topk -> norm_topk_prob
+ * sequence of the MoE blocks the reference quantises; the reference itself takes the routing result from the
+ * framework, mxmoe/kernels/src/ref_bind.cu:47-64).  logits: fp32, or fp16 if `logits_fp16`, [T, E] with
+ * E <= 512; outputs [T, topk], topk <= 32; ties go to the lower expert index. */
+int mxmoe_gate_topk(const void* logits, int logits_fp16, int num_tokens, int num_experts, int topk, int renormalize,
+                    int32_t* topk_ids, float* topk_weights, void* stream);
+
 /* out[t] = sum_j topk_weights[t,j] * y[slot_row[t,j]] (+ y_shared[t]); y is the
  * fp16 [rows, hidden] output of the down projection, accumulation in fp32.  The
  * reference leaves this step unimplemented (`gg_unpermute_out(){}`,

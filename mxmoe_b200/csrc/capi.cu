@@ -613,6 +613,16 @@ int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk
 }
 
 
+int mxmoe_gate_topk(const void* logits, int logits_fp16, int num_tokens, int num_experts, int topk, int renormalize,
+                    int32_t* topk_ids, float* topk_weights, void* stream) {
+  if (!logits || !topk_ids || !topk_weights) return fail(MXMOE_ERR_INVALID, "null pointer in gate arguments");
+  if (num_tokens < 0 || num_experts <= 0 || num_experts > 512 || topk <= 0 || topk > 32 || topk > num_experts)
+    return fail(MXMOE_ERR_INVALID, "bad gate shape T=%d E=%d topk=%d (E <= 512, topk <= min(32, E))", num_tokens, num_experts, topk);
+  CUDA_TRY(mxb::launch_gate_topk(logits, logits_fp16 != 0, num_tokens, num_experts, topk, renormalize, topk_ids,
+                                 topk_weights, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
 int mxmoe_ep_plan(const mxmoe_ep_plan_args* a, void* stream) {
   if (!a) return fail(MXMOE_ERR_INVALID, "null args");
   if (a->world <= 0 || a->world > 64 || a->rank < 0 || a->rank >= a->world || a->num_experts <= 0 ||

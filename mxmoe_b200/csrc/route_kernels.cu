@@ -173,7 +173,77 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __half* __restr
   }
 }
 
+// Router gate: softmax over the expert logits of a token in fp32, the top-k probabilities and their experts,
+// optionally renormalised to sum 1 (the gate of the MoE blocks the reference quantises: softmax -> topk ->
+// norm_topk_prob).  One warp per token, up to 16 experts per lane; ties go to the lower expert index.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) gate_topk_kernel(const T* __restrict__ logits, int num_tokens, int E, int topk,
+                                                             int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (kThreads / 32) + warp;
+  if (t >= num_tokens) return;
+  constexpr int kPer = kMaxE / 32;
+  float v[kPer];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < E ? (float)logits[(int64_t)t * E + e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    v[i] = (i * 32 + lane) < E ? __expf(v[i] - mx) : -1.f;   // -1: not a candidate
+    sum += fmaxf(v[i], 0.f);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+  float picked = 0.f, mine_w = 0.f;
+  int mine_id = 0;
+  for (int j = 0; j < topk; ++j) {
+    // lane-local best, then the warp's best (larger value, then lower index)
+    float bv = -1.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int e = i * 32 + lane;
+      if (v[i] > bv) { bv = v[i]; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi   = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kPer; ++i)
+        if (i * 32 + lane == bi) v[i] = -1.f;
+    }
+    picked += bv * inv;
+    if (lane == j) { mine_w = bv * inv; mine_id = bi; }
+  }
+  if (lane < topk) {
+    ids[(int64_t)t * topk + lane] = mine_id;
+    wts[(int64_t)t * topk + lane] = renorm ? mine_w / picked : mine_w;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_gate_topk(const void* logits, bool fp16, int num_tokens, int num_experts, int topk, int renorm,
+                             int* ids, float* wts, cudaStream_t stream) {
+  if (num_tokens <= 0) return cudaSuccess;
+  if (num_experts > kMaxE || topk > 32 || topk > num_experts) return cudaErrorInvalidValue;
+  const int blocks = (num_tokens + kThreads / 32 - 1) / (kThreads / 32);
+  if (fp16) gate_topk_kernel<__half><<<blocks, kThreads, 0, stream>>>(static_cast<const __half*>(logits), num_tokens, num_experts, topk, renorm, ids, wts);
+  else      gate_topk_kernel<float><<<blocks, kThreads, 0, stream>>>(static_cast<const float*>(logits), num_tokens, num_experts, topk, renorm, ids, wts);
+  return cudaGetLastError();
+}
 
 size_t route_workspace_bytes(int num_tokens, int topk, int num_experts) {
   const long long n = (long long)num_tokens * topk;

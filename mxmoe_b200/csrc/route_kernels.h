@@ -23,6 +23,9 @@ cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream);
 // static-scratch variant (see route_kernels.cu)
 size_t route_static_scratch_ints();
 cudaError_t route_static_scratch_ptr(int** out);
+// softmax + top-k router gate (logits fp32 or fp16 [T, E]) -> expert ids and weights [T, topk]
+cudaError_t launch_gate_topk(const void* logits, bool fp16, int num_tokens, int num_experts, int topk, int renorm,
+                             int* ids, float* wts, cudaStream_t stream);
 cudaError_t launch_combine(const void* y, const int* slot_row, const float* topk_w, const void* y_shared, void* out,
                            int num_tokens, int topk, int hidden, cudaStream_t stream);
 

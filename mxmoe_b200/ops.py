@@ -329,3 +329,21 @@ def silu_mul_then_quant(inp: torch.Tensor, num_problems: int, num_experts: int, 
         out_list.append(out_store[qout_off:qout_off + m * K].view(m, K))
         qout_off += m * K
     return inp_list, inp_scale_list, out_list, inp_store, inp_scale_store, out_store
+
+
+def gate_topk(router_logits: torch.Tensor, topk: int, renormalize: bool = True):
+    """Router gate on the device (no counterpart in ``mxmoe_ops``, which receives the routing result from the
+    framework, ref_bind.cu:47-64): ``softmax(router_logits, dim=-1, dtype=float)`` -> top-k -> optional
+    renormalisation.  ``router_logits``: fp32 or fp16 ``[T, E]``.  Returns ``(topk_ids int32 [T, k],
+    topk_weights fp32 [T, k])``, ready for the routing and combine kernels."""
+    _check(router_logits.is_cuda and router_logits.dim() == 2, "router_logits must be a CUDA [T, E] tensor")
+    _check(router_logits.dtype in (torch.float32, torch.float16), "router_logits must be fp32 or fp16")
+    logits = router_logits.contiguous()
+    T, E = logits.shape
+    ids = torch.empty((T, topk), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, topk), dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.lib().mxmoe_gate_topk(logits.data_ptr(), 1 if logits.dtype == torch.float16 else 0, T, E, topk,
+                                              1 if renormalize else 0, ids.data_ptr(), wts.data_ptr(),
+                                              current_stream_ptr()))
+    return ids, wts

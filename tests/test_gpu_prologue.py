@@ -250,3 +250,20 @@ def test_device_exchange_plan_matches_host_plan(cuda_device, world, rank):
         assert t["total_recv"].tolist() == [plan.total_recv - 7, plan.total_recv]
         ends = (t["seg_row0"] + t["seg_m"]).max().item()
         assert ends <= plan.total_recv - 7
+
+
+@pytest.mark.parametrize("t,e,k,dtype,renorm", [(70, 60, 4, torch.float32, True), (33, 64, 6, torch.float16, False),
+                                                 (5, 8, 2, torch.float32, True), (129, 300, 8, torch.float32, True)])
+def test_gate_topk_matches_torch(cuda_device, t, e, k, dtype, renorm):
+    from mxmoe_b200 import ops
+    g = torch.Generator().manual_seed(e * 7 + k)
+    logits = (torch.randn(t, e, generator=g) * 2).to(dtype)
+    if dtype == torch.float16:   # distinct, exactly representable values: no ties to break
+        logits = torch.stack([torch.randperm(e, generator=g) for _ in range(t)]).to(torch.float16) / 8 - 4
+    ids, wts = ops.gate_topk(logits.to(cuda_device), k, renormalize=renorm)
+    prob = torch.softmax(logits.float(), dim=-1)
+    want_w, want_i = prob.topk(k, dim=-1)
+    if renorm:
+        want_w = want_w / want_w.sum(dim=-1, keepdim=True)
+    assert torch.equal(ids.cpu().long(), want_i), "expert ids differ from torch.topk"
+    assert torch.allclose(wts.cpu(), want_w, rtol=2e-5, atol=1e-7)
