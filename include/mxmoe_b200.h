@@ -224,6 +224,13 @@ int mxmoe_quant_tokens(const mxmoe_token_quant_args* args, void* stream);
 /* `rows` uses the tables of mxmoe_act_args (its `in` is ignored); every format tagged in
  * rows->exp_qtag must have its store in `stores` (tag 0 reads stores->f16, or stores->in if NULL). */
 int mxmoe_gather_rows(const mxmoe_act_args* rows, const mxmoe_token_quant_args* stores, void* stream);
+/* Both in one pass: every token's row is rotated and quantised once and written from registers to the
+ * expert-sorted slot of each of its topk routing slots (slot_row[t * topk + s] = sorted row of slot s of token t,
+ * as mxmoe_route_topk returns it; 1 <= topk <= 8; rows->rows_total == rows->rows_routed) in that expert's format,
+ * and to the token-major stores of `stores` that are not NULL (a shared expert reads those).  Bit-identical to
+ * mxmoe_quant_tokens followed by mxmoe_gather_rows; a store of a format only routed experts use may be NULL. */
+int mxmoe_quant_tokens_scatter(const mxmoe_token_quant_args* stores, const mxmoe_act_args* rows, const int32_t* slot_row,
+                               int32_t topk, void* stream);
 
 /* h = silu(gate) * up over gate_up rows ([rows, 2k] fp16, gate first), then
  * quantise per token and pack for the down projection.  Replaces

@@ -11,6 +11,8 @@
 //                    pure copy of each routed row into its expert's slot: with
 //                    top-k routing this does the arithmetic T times instead of
 //                    T*topk times
+//   quant_tokens_scatter  both in one pass (top-k <= 8): the token's packed words are
+//                    formed once in registers and stored to each of its routed slots
 //   silu_mul_quant   h = silu(gate) * up on the gate_up output, then quantise + pack
 //                    for the down projection
 //                    (`silu_mul_then_quant_kernel`, ref_bind.cu:701-716)
@@ -236,15 +238,25 @@ struct RowQuant {
 // Expanded int4 (tag 3) straight from the packed-half bit patterns of 8 consecutive codes (b01 = codes 0, 1; ...):
 // the same bytes store_codes produces for tag 3 - every code as the byte 16*q, high nibbles of the packed row's
 // bytes first - with shifts, masks and byte permutes only.
-__device__ __forceinline__ void store_expanded4(__half* q_dst, int ci, uint32_t b01, uint32_t b23, uint32_t b45,
-                                                uint32_t b67) {
+__device__ __forceinline__ void expanded4_words(uint32_t b01, uint32_t b23, uint32_t b45, uint32_t b67, uint32_t& d0,
+                                                uint32_t& d4) {
   const uint32_t x01 = (b01 << 4) & 0x00F000F0u, x23 = (b23 << 4) & 0x00F000F0u;   // byte 0: even code, byte 2: odd code
   const uint32_t x45 = (b45 << 4) & 0x00F000F0u, x67 = (b67 << 4) & 0x00F000F0u;
   const uint32_t ylo = __byte_perm(x23, x01, 0x6240);   // c2, c0, c3, c1
   const uint32_t yhi = __byte_perm(x67, x45, 0x6240);   // c6, c4, c7, c5
+  d0 = __byte_perm(ylo, yhi, 0x5410);                   // c2, c0, c6, c4
+  d4 = __byte_perm(ylo, yhi, 0x7632);                   // c3, c1, c7, c5
+}
+__device__ __forceinline__ void store_expanded4_words(__half* q_dst, int ci, uint32_t d0, uint32_t d4) {
   uint32_t* d = reinterpret_cast<uint32_t*>(q_dst) + 8 * (ci >> 2) + (ci & 3);
-  d[0] = __byte_perm(ylo, yhi, 0x5410);                 // c2, c0, c6, c4
-  d[4] = __byte_perm(ylo, yhi, 0x7632);                 // c3, c1, c7, c5
+  d[0] = d0;
+  d[4] = d4;
+}
+__device__ __forceinline__ void store_expanded4(__half* q_dst, int ci, uint32_t b01, uint32_t b23, uint32_t b45,
+                                                uint32_t b67) {
+  uint32_t d0, d4;
+  expanded4_words(b01, b23, b45, b67, d0, d4);
+  store_expanded4_words(q_dst, ci, d0, d4);
 }
 
 // pack 8 consecutive codes of a row and store them as chunk `ci` of the packed row
@@ -313,6 +325,57 @@ __device__ __forceinline__ void emit_row(const float (&x)[kJ][8], float amax, in
   }
 }
 
+// The same row written to several destinations: the packed words of each chunk are formed once and stored to
+// every destination d whose bit is set in `dst_mask`.  Lane d of the warp holds destination d: its packed row at
+// q_base + my_q and its scale at s_base + my_s (offsets in halfs; no scale if negative); the offsets are fetched
+// by shuffle where they are used, so that they cost no registers next to the row.  `dst_mask` is the same in
+// every lane.  Bits are those emit_row writes.
+constexpr int kMaxDst = 8;
+template <int kWarps>
+__device__ __forceinline__ void emit_row_multi(const float (&x)[kJ][8], float amax, int tag, __half* q_base, int my_q,
+                                               __half* s_base, int my_s, unsigned dst_mask, int nchunk, int w,
+                                               int lane) {
+  const RowQuant rq(amax, tag == 0 ? 1 : tag);
+  if (tag != 0) {
+    for (unsigned m = dst_mask; m; m &= m - 1) {
+      const int sd = __shfl_sync(0xffffffffu, my_s, __ffs(m) - 1);
+      if (w == 0 && lane == 0 && sd >= 0) s_base[sd] = rq.sc_h;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci  = chunk_of<kWarps>(w, j, lane);
+    const bool on = ci < nchunk;
+    if (chunk_of<kWarps>(w, j, 0) >= nchunk) break;   // no lane of the warp has this chunk
+    if (tag == 0) {
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(x[j][2 * e], x[j][2 * e + 1]);
+      for (unsigned m = dst_mask; m; m &= m - 1) {
+        const int qd = __shfl_sync(0xffffffffu, my_q, __ffs(m) - 1);
+        if (on) reinterpret_cast<uint4*>(q_base + qd)[ci] = o;
+      }
+    } else if (tag == 3) {
+      uint32_t d0, d4;
+      expanded4_words(rq.bits2(x[j][0], x[j][1]), rq.bits2(x[j][2], x[j][3]), rq.bits2(x[j][4], x[j][5]),
+                      rq.bits2(x[j][6], x[j][7]), d0, d4);
+      for (unsigned m = dst_mask; m; m &= m - 1) {
+        const int qd = __shfl_sync(0xffffffffu, my_q, __ffs(m) - 1);
+        if (on) store_expanded4_words(q_base + qd, ci, d0, d4);
+      }
+    } else {
+      int code[8];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) rq.code2(x[j][e], x[j][e + 1], code[e], code[e + 1]);
+      for (unsigned m = dst_mask; m; m &= m - 1) {
+        const int qd = __shfl_sync(0xffffffffu, my_q, __ffs(m) - 1);
+        if (on) store_codes(q_base + qd, ci, tag, code);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // fused gather + (rotate) + quantise, one pass per routed row (operator-API path, any top-k)
 template <int kWarps>
@@ -378,6 +441,60 @@ __global__ void __launch_bounds__(kBlock, 3) quant_tokens_kernel(TokenQuantArgs 
   if (a.q8) emit_row<kWarps>(x, amax, 1, a.q8 + (int64_t)tok * (a.k / 2), a.s8 + tok, nchunk, w, lane);
   if (a.q4) emit_row<kWarps>(x, amax, 2, a.q4 + (int64_t)tok * (a.k / 4), a.s4 + tok, nchunk, w, lane);
   if (a.q4x) emit_row<kWarps>(x, amax, 3, a.q4x + (int64_t)tok * (a.k / 2), a.s4 + tok, nchunk, w, lane);
+}
+
+// quant_tokens with the routed copies written by the same pass: the token's row goes to the expert-sorted slot
+// of each of its `topk` routing slots (slot_row[tok * topk + s], tables of `r` as for gather_rows) in that
+// expert's format, and to the token-major stores of `a` that are not null.  Same bits as quant_tokens followed
+// by gather_rows, without the second pass over the rows.
+template <int kWarps>
+__global__ void __launch_bounds__(kBlock, 2) quant_tokens_scatter_kernel(TokenQuantArgs a, ActArgs r, const int* slot_row,
+                                                                         int topk) {
+  __shared__ float xch[kWarps > 1 ? kBlock * 8 : 1];
+  __shared__ float red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_in_blk = warp / kWarps, w = warp % kWarps;
+  const int tok     = blockIdx.x * (8 / kWarps) + row_in_blk;
+  const bool row_ok = tok < a.num_tokens;
+  const int nchunk  = a.k >> 3;
+  // destinations first: their loads are in flight during the transform
+  // (as 32-bit offsets from the stores: the launcher checks that they fit)
+  const bool s_in_record = r.rec_stride > 0 && r.rec_scale_off >= 0;
+  __half* s_base         = s_in_record ? r.q_store : r.s_store;
+  int my_tag = -1, my_q = 0, my_s = -1;
+  if (row_ok && lane < topk) {
+    const int row = __ldg(slot_row + (int64_t)tok * topk + lane);
+    if (row >= 0 && row < r.rows_routed) {
+      const RowInfo ri = locate_row(r, row);
+      my_tag = ri.tag;
+      my_q   = (int)(ri.q_dst - r.q_store);
+      my_s   = ri.s_dst ? (int)(ri.s_dst - s_base) : -1;
+    }
+  }
+  float x[kJ][8];
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci = chunk_of<kWarps>(w, j, lane);
+    if (row_ok && ci < nchunk) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(a.in + (int64_t)tok * a.k) + ci), x[j]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[j][e] = 0.f;
+    }
+  }
+  if (a.rotate) rotate_row<kWarps>(x, a.signs, nchunk, a.k, w, lane, row_ok, xch);
+  const float amax = row_amax<kWarps>(x, warp, row_in_blk, lane, red);
+  if (!row_ok) return;   // a warp serves one row: it leaves as a whole
+  if (a.f16) emit_row<kWarps>(x, amax, 0, a.f16 + (int64_t)tok * a.k, nullptr, nchunk, w, lane);
+  if (a.q8) emit_row<kWarps>(x, amax, 1, a.q8 + (int64_t)tok * (a.k / 2), a.s8 + tok, nchunk, w, lane);
+  if (a.q4) emit_row<kWarps>(x, amax, 2, a.q4 + (int64_t)tok * (a.k / 4), a.s4 + tok, nchunk, w, lane);
+  if (a.q4x) emit_row<kWarps>(x, amax, 3, a.q4x + (int64_t)tok * (a.k / 2), a.s4 + tok, nchunk, w, lane);
+  unsigned by_tag[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) by_tag[t] = __ballot_sync(0xffffffffu, my_tag == t);
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+    if (by_tag[t]) emit_row_multi<kWarps>(x, amax, t, r.q_store, my_q, s_base, my_s, by_tag[t], nchunk, w, lane);
 }
 
 // copy every routed (and shared-expert) row from the token-major store of its expert's format into
@@ -514,6 +631,14 @@ cudaError_t launch_silu_mul_quant(const ActArgs& a, cudaStream_t stream) {
 cudaError_t launch_quant_tokens(const TokenQuantArgs& t, cudaStream_t stream) {
   if (t.num_tokens <= 0) return cudaSuccess;
   MXB_DISPATCH_WARPS(t.k, t.num_tokens, quant_tokens_kernel, t);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quant_tokens_scatter(const TokenQuantArgs& t, const ActArgs& r, const int* slot_row, int topk,
+                                        cudaStream_t stream) {
+  if (t.num_tokens <= 0) return cudaSuccess;
+  if (topk < 1 || topk > kMaxDst) return cudaErrorInvalidValue;
+  MXB_DISPATCH_WARPS(t.k, t.num_tokens, quant_tokens_scatter_kernel, t, r, slot_row, topk);
   return cudaGetLastError();
 }
 

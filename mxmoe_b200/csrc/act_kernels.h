@@ -53,6 +53,9 @@ struct TokenQuantArgs {
 cudaError_t launch_quant_tokens(const TokenQuantArgs& t, cudaStream_t stream);
 // rows of `a` (tables as for quant_act; a.in unused) are copied from the stores of `t`
 cudaError_t launch_gather_rows(const ActArgs& a, const TokenQuantArgs& t, cudaStream_t stream);
+// quant_tokens + gather_rows in one pass: rows of `r` (routed rows only) are written from registers, topk <= 8
+cudaError_t launch_quant_tokens_scatter(const TokenQuantArgs& t, const ActArgs& r, const int* slot_row, int topk,
+                                        cudaStream_t stream);
 cudaError_t launch_quant_act(const ActArgs& a, cudaStream_t stream);
 cudaError_t launch_silu_mul_quant(const ActArgs& a, cudaStream_t stream);
 

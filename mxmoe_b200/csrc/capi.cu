@@ -545,6 +545,28 @@ int mxmoe_gather_rows(const mxmoe_act_args* rows, const mxmoe_token_quant_args* 
   return MXMOE_OK;
 }
 
+int mxmoe_quant_tokens_scatter(const mxmoe_token_quant_args* stores, const mxmoe_act_args* rows, const int32_t* slot_row,
+                               int topk, void* stream) {
+  mxb::TokenQuantArgs t;
+  int rc = to_token_args(stores, &t);
+  if (rc) return rc;
+  if (!rows || !slot_row) return fail(MXMOE_ERR_INVALID, "null args");
+  if (topk < 1 || topk > 8) return fail(MXMOE_ERR_UNSUPPORTED, "the one-pass scatter serves top-k 1..8 (topk=%d): use mxmoe_quant_tokens + mxmoe_gather_rows", topk);
+  if (rows->rows_total != rows->rows_routed) return fail(MXMOE_ERR_INVALID, "the scatter writes routed rows only (rows_total must equal rows_routed)");
+  if (rows->k != stores->k) return fail(MXMOE_ERR_INVALID, "row length of the rows (%d) and of the tokens (%d) differ", rows->k, stores->k);
+  // destinations travel between lanes as 32-bit offsets (in fp16 elements) from the stores
+  const int64_t pitch = rows->rec_stride > 0 ? rows->rec_stride : rows->k;
+  if ((int64_t)rows->rows_routed * pitch >= (int64_t)1 << 31) return fail(MXMOE_ERR_UNSUPPORTED, "activation store beyond 2^31 elements: use mxmoe_quant_tokens + mxmoe_gather_rows");
+  mxmoe_act_args r = *rows;
+  r.in = stores->in;
+  r.rotate = 0;
+  mxb::ActArgs a;
+  rc = to_act_args(&r, &a, false);
+  if (rc) return rc;
+  CUDA_TRY(mxb::launch_quant_tokens_scatter(t, a, slot_row, topk, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
 int mxmoe_silu_mul_then_quant(const mxmoe_act_args* args, void* stream) {
   mxb::ActArgs a;
   int rc = to_act_args(args, &a, true);

@@ -3,8 +3,9 @@
 Pipeline of one forward (all on the current CUDA stream)::
 
     route_topk            counts / row offsets / permutation on the device
-    quant_tokens          (Hadamard) + per-token quantise + pack, once per token
-    gather_rows           copy each routed row into the expert-sorted record store
+    quant_tokens_scatter  (Hadamard) + per-token quantise + pack, once per token, written from registers
+                          into the expert-sorted record of each of the token's routed slots
+                          (top-k > 8: quant_tokens into token-major stores, then gather_rows)
     grouped GEMM          gate_up of every expert (+ shared expert), one launch
     silu_mul_then_quant   h = silu(gate) * up, quantise + pack
     grouped GEMM          down of every expert (+ shared expert), one launch
@@ -25,6 +26,7 @@ a store can be handed to another GPU as it is.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -245,7 +247,11 @@ class MoELayer:
         self._tag1 = tag1
         self.tag1 = torch.tensor(tag1, **i32)
         routed = [e for e in sorted(gate_up) if e < E]
-        self.tq = TokenQuant(T, H, {tag1[e] for e in gate_up}, rotate, signs, dev)
+        # top-k up to 8: one launch quantises every token and writes its routed rows; the token-major stores are
+        # then kept only for the shared expert, which reads them in place
+        self.one_pass_quant = 1 <= topk <= 8 and os.environ.get("MXMOE_QUANT_PASSES", "1") == "1"
+        store_tags = {tag1[e] for e in gate_up if e >= E} if self.one_pass_quant else {tag1[e] for e in gate_up}
+        self.tq = TokenQuant(T, H, store_tags, rotate, signs, dev)
         self.rec1 = record_stride(H, {tag1[e] for e in routed}) if routed else H
         self.q1 = torch.zeros(max(R, 1) * self.rec1, **f16)
         self.s1 = torch.zeros(max(R, 1), **f16)
@@ -297,8 +303,8 @@ class MoELayer:
         a.num_tokens, a.topk, a.num_experts = T, k, self.E
         _lib.check(_lib.lib().mxmoe_route_topk(C.byref(a), current_stream_ptr()))
 
-    def gather(self, t: _lib.TokenQuantArgs, rows: int, q_store: torch.Tensor, rec_stride: int,
-               s_store: torch.Tensor | None, rec_scale_off: int = -1) -> None:
+    def _row_args(self, rows: int, q_store: torch.Tensor, rec_stride: int, s_store: torch.Tensor | None,
+                  rec_scale_off: int = -1) -> _lib.ActArgs:
         a = _lib.ActArgs()
         a.q_store = q_store.data_ptr()
         a.s_store = None if s_store is None else s_store.data_ptr()
@@ -306,7 +312,19 @@ class MoELayer:
         a.exp_qtag = self.tag1.data_ptr()
         a.k, a.k_shared, a.rows_routed, a.rows_total, a.num_experts = self.H, self.H, rows, rows, self.E
         a.rec_stride, a.rec_scale_off = rec_stride, rec_scale_off
+        return a
+
+    def gather(self, t: _lib.TokenQuantArgs, rows: int, q_store: torch.Tensor, rec_stride: int,
+               s_store: torch.Tensor | None, rec_scale_off: int = -1) -> None:
+        a = self._row_args(rows, q_store, rec_stride, s_store, rec_scale_off)
         _lib.check(_lib.lib().mxmoe_gather_rows(C.byref(a), C.byref(t), current_stream_ptr()))
+
+    def quant_scatter(self, hidden: torch.Tensor, rows: int) -> None:
+        """Rotate + quantise every token once and write its row to each of its routed slots (one launch)."""
+        t = self.tq.fill(hidden)
+        a = self._row_args(rows, self.q1, self.rec1, self.s1)
+        _lib.check(_lib.lib().mxmoe_quant_tokens_scatter(C.byref(t), C.byref(a), self.slot_row.data_ptr(), self.topk,
+                                                         current_stream_ptr()))
 
     def forward(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor | None = None):
         """``[T, H]`` fp16 hidden states + ``[T, topk]`` int32 expert ids (+ fp32 gate weights) -> ``[T, H]`` fp16."""
@@ -319,8 +337,11 @@ class MoELayer:
                 assert hidden.data_ptr() == self._hidden_ptr, \
                     "an fp16 shared expert reads `hidden` in place: pass the same buffer every step"
             self.route(topk_ids)
-            t = self.tq.run(hidden)
-            self.gather(t, T * self.topk, self.q1, self.rec1, self.s1)
+            if self.one_pass_quant:
+                self.quant_scatter(hidden, T * self.topk)
+            else:
+                t = self.tq.run(hidden)
+                self.gather(t, T * self.topk, self.q1, self.rec1, self.s1)
             self._core.run(T * self.topk)
             out = self.out.view(self.T, self.H)
             _lib.check(_lib.lib().mxmoe_combine_topk(
@@ -350,7 +371,10 @@ class MoELayer:
         self._graph.replay()
         return self.out.view(self.T, self.H)
 
-    launches_per_step = 9   # route x3, quant_tokens, gather_rows, GEMM, silu, GEMM, combine (+1 with a shared expert)
+    # route x3, quant_tokens_scatter, GEMM, silu, GEMM, combine (+1 launch with the two-pass quantiser)
+    @property
+    def launches_per_step(self) -> int:
+        return 8 if self.one_pass_quant else 9
 
     def check(self) -> None:
         self._core.check()

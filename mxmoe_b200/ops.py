@@ -186,7 +186,7 @@ def _launch_act(fn, dev, **kw) -> None:
 
 def quant_inp_act(hidden: torch.Tensor, topk_ids: torch.Tensor, num_experts: int, N: int, num_shared_experts: int,
                   qparams_per_exp: Sequence[QParamsTuple], verbose: bool = False, *,
-                  rotate: bool = False, signs: torch.Tensor | None = None, fused: bool = False):
+                  rotate: bool = False, signs: torch.Tensor | None = None, fused: bool | str = False):
     """Permute tokens by expert and quantise + pack each row with its expert's activation scheme.
 
     Mirrors ``quant_inp_act`` (ref_bind.cu:434-592) including the nine-element return tuple
@@ -194,8 +194,9 @@ def quant_inp_act(hidden: torch.Tensor, topk_ids: torch.Tensor, num_experts: int
     recv_tokens_per_exp[CPU int64], perm_indices, dst_exp_sorted)``.  ``rotate`` / ``signs``
     (keyword-only, not in the reference) apply the Hadamard rotation of the hidden
     dimension before quantising.  By default rows are quantised once per token and then
-    copied to their experts; ``fused=True`` runs the single gather+quantise kernel instead
-    (same bits).
+    copied to their experts; ``fused=True`` runs the single gather+quantise kernel instead and
+    ``fused="scatter"`` (top-k up to 8) the once-per-token kernel that writes the routed rows itself
+    (same bits all three).
     """
     _check(hidden.dim() == 2 and hidden.is_cuda, "hidden must be a 2D cuda tensor")
     _check(hidden.dtype == torch.float16, "hidden must be fp16")
@@ -206,8 +207,8 @@ def quant_inp_act(hidden: torch.Tensor, topk_ids: torch.Tensor, num_experts: int
     dev = hidden.device
     hidden = hidden.contiguous()
 
-    dst_exp_sorted, perm_indices = torch.sort(topk_ids.reshape(-1), stable=True)
-    perm_indices = perm_indices.floor_divide(topk)
+    dst_exp_sorted, perm_slots = torch.sort(topk_ids.reshape(-1), stable=True)
+    perm_indices = perm_slots.floor_divide(topk)
     recv_tokens_per_exp = torch.bincount(dst_exp_sorted, minlength=num_experts).cpu()
     tokens = recv_tokens_per_exp.tolist()
 
@@ -227,7 +228,31 @@ def quant_inp_act(hidden: torch.Tensor, topk_ids: torch.Tensor, num_experts: int
                   row_expert=dst_exp_sorted, row_token=perm_indices,
                   exp_qtag=tables[0], exp_row_start=tables[1], exp_q_off=tables[2], exp_s_off=tables[3],
                   k=K, k_shared=K, rows_routed=num_tokens * topk, rows_total=alloc_tokens, num_experts=num_experts)
-    if fused:
+    if fused == "scatter":
+        # one pass per TOKEN: the routed rows are written from registers; the shared expert's rows map one-to-one
+        # onto tokens, so its slice of the stores IS the token-major store of its format
+        slot_row = torch.empty(num_tokens * topk, dtype=torch.int32, device=dev)
+        slot_row[perm_slots] = torch.arange(num_tokens * topk, dtype=torch.int32, device=dev)
+        t = _lib.TokenQuantArgs()
+        t.inp, t.k, t.num_tokens, t.rotate = hidden.data_ptr(), K, num_tokens, 1 if rotate else 0
+        t.signs = None if signs is None else signs.data_ptr()
+        if has_shared:
+            q_ptr = inp_store.data_ptr() + 2 * qoff[num_experts]
+            s_ptr = inp_scale_store.data_ptr() + 2 * soff[num_experts] if s_total else None
+            if tag[num_experts] == 0:
+                t.f16 = q_ptr
+            elif tag[num_experts] == 1:
+                t.q8, t.s8 = q_ptr, s_ptr
+            else:
+                t.q4, t.s4 = q_ptr, s_ptr
+        a = _lib.ActArgs()
+        for k_, v in dict(common, rows_total=num_tokens * topk).items():
+            setattr(a, k_, v.data_ptr() if isinstance(v, torch.Tensor) else v)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mxmoe_quant_tokens_scatter(C.byref(t), C.byref(a), slot_row.data_ptr(), topk,
+                                                             current_stream_ptr()))
+        slot_row.record_stream(torch.cuda.current_stream())
+    elif fused:
         _launch_act(_lib.lib().mxmoe_quant_act, dev, inp=hidden, in_shared=None, signs=signs,
                     rotate=1 if rotate else 0, **common)
     else:

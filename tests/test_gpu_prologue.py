@@ -25,7 +25,7 @@ def _unpack_rows(words, tag, k):
     return w.view(np.float16)
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "scatter"])
 @pytest.mark.parametrize("k", [256, 1408, 2048, 4096, 5632, 14336])
 def test_quant_inp_act_matches_quantiser(cuda_device, k, fused):
     """Codes and scales are bit-identical to the fp16 min/max quantiser (quant.py:40-84) for every tag."""
@@ -69,7 +69,7 @@ def test_quant_inp_act_matches_quantiser(cuda_device, k, fused):
     assert pidx == len(inp_list)
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "scatter"])
 @pytest.mark.parametrize("k", [256, 2048, 4096])
 def test_quant_inp_act_with_rotation(cuda_device, k, fused):
     """Rotated rows match matmul_hadU on (x * signs) to rel-L2 1e-3 after dequantisation of 8-bit codes;
