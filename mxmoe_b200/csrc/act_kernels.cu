@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(kBlock) gather_rows_kernel(ActArgs a, TokenQua
 // h = silu(gate) * up, then quantise; one pass per routed row.  Values are fp16 after the product,
 // so they are kept as half2 (32 registers per thread for 64 values).
 template <int kWarps>
-__global__ void __launch_bounds__(kBlock, 5) silu_mul_quant_kernel(ActArgs a) {
+__global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
   __shared__ float red[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_in_blk = warp / kWarps, w = warp % kWarps;
@@ -537,12 +537,23 @@ __global__ void __launch_bounds__(kBlock, 5) silu_mul_quant_kernel(ActArgs a) {
   }
   __half2 h[kJ][4];
   __half2 m2 = __float2half2_rn(0.f);
+  // every load of the row is issued before the first value is used: the kernel waits on memory, not on issue
+  // slots, and 24 warps per SM with all their loads in flight beat 40 warps that load chunk by chunk
+  uint4 gq[kJ], uq[kJ];
 #pragma unroll
   for (int j = 0; j < kJ; ++j) {
     const int ci = chunk_of<kWarps>(w, j, lane);
     if (row_ok && ci < nchunk) {
-      const uint4 g = __ldg(reinterpret_cast<const uint4*>(src) + ci);
-      const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + ri.k) + ci);
+      gq[j] = __ldg(reinterpret_cast<const uint4*>(src) + ci);
+      uq[j] = __ldg(reinterpret_cast<const uint4*>(src + ri.k) + ci);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int ci = chunk_of<kWarps>(w, j, lane);
+    if (row_ok && ci < nchunk) {
+      const uint4 g = gq[j];
+      const uint4 u = uq[j];
       const __half2* gh = reinterpret_cast<const __half2*>(&g);
       const __half2* uh = reinterpret_cast<const __half2*>(&u);
 #pragma unroll

@@ -167,7 +167,7 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
 // the weights come from (kV: 0 int8 / shared memory, 1 fp16 / shared memory, 2 int8 / tensor memory, 3 fp16 /
 // tensor memory) so that the issue sequence of a stage is straight-line code: a branch per MMA made the
 // issue of every MMA several times slower.  All lanes walk the loop and meet the named barrier of each
-// stage; lane 0 issues.  One MMA consumes 32 bytes of K per row: 8 TMEM columns of A or 32 bytes of a
+// stage; the elected lane issues.  One MMA consumes 32 bytes of K per row: 8 TMEM columns of A or 32 bytes of a
 // shared-memory row.
 template <int kV, typename G>
 __device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uint32_t d_tmem, uint32_t idesc,
@@ -178,7 +178,7 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uin
     nbar_sync(G::kBarStage0 + stage, 64);   // operands of this stage are in place
     const long long c1 = tick(prof_on);
     w_oper += c1 - c0;
-    if (lane == 0) {
+    if (elect_one_sync()) {
       tc_fence_after_sync();
       const uint32_t wslot   = ring_base + stage * G::kStageBytes;
       const uint64_t xdesc   = smem_desc_sw128(wslot + kWSlotBytes);
@@ -339,7 +339,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       }
     }
   } else if (warp == 1) {
-    // ===== MMA issuer (all lanes walk the loop and meet the named barriers, lane 0 issues) =====
+    // ===== MMA issuer (all lanes walk the loop and meet the named barriers, the elected lane issues) =====
     int stage = 0;
     int acc = 0;
     long long w_oper = 0, w_acc = 0, w_issue = 0;
@@ -362,7 +362,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       else if (variant == 1) mma_tile_loop<1, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
       else if (variant == 2) mma_tile_loop<2, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
       else                   mma_tile_loop<3, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      if (lane == 0) mma_commit(smem_u32(&ctrl->tfull[acc]));
+      if (elect_one_sync()) mma_commit(smem_u32(&ctrl->tfull[acc]));
       __syncwarp();
       acc ^= 1;
     }
