@@ -349,7 +349,10 @@ def main():
     # the step's inputs from pinned memory, the layer pass and the device -> host copy of its result; copies of
     # neighbouring steps overlap the compute on their own streams
     from mxmoe_b200.layer import HostPipeline
-    pipe = HostPipeline(layer, T, spec.hidden, spec.topk, device=dev, use_graph=use_graph)
+    # fed through the device tensors of the resident-input leg: a layer with an fp16 shared expert and no rotation is
+    # bound to the address of the hidden states it was first run on
+    pipe = HostPipeline(layer, T, spec.hidden, spec.topk, device=dev, use_graph=use_graph,
+                        inputs=(hidden, ids_d, wts_d))
     out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
 
     def step_e2e(i):

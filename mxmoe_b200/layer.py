@@ -406,7 +406,8 @@ class HostPipeline:
         pipe.drain()                                                  # out_host of every submitted step is complete
     """
 
-    def __init__(self, layer, tokens: int, hidden: int, topk: int, device=None, use_graph: bool = True):
+    def __init__(self, layer, tokens: int, hidden: int, topk: int, device=None, use_graph: bool = True,
+                 inputs=None):
         self.layer = layer
         self.device = torch.device(device) if device is not None else layer.device
         dev = self.device
@@ -418,9 +419,14 @@ class HostPipeline:
                           ev_in=torch.cuda.Event(), ev_comp=torch.cuda.Event(), ev_out=torch.cuda.Event())
                      for _ in range(2)]
         # the layer's graph bakes in the addresses of its inputs: one static set, filled by device copies
-        self.x = torch.empty(tokens, hidden, dtype=torch.float16, device=dev)
-        self.i = torch.empty(tokens, topk, dtype=torch.int32, device=dev)
-        self.w = torch.empty(tokens, topk, dtype=torch.float32, device=dev)
+        # (`inputs` = (hidden, ids, weights) device tensors the layer has already been run on: a layer with an fp16
+        # shared expert and no rotation reads `hidden` in place and is bound to that address)
+        if inputs is not None:
+            self.x, self.i, self.w = inputs
+        else:
+            self.x = torch.empty(tokens, hidden, dtype=torch.float16, device=dev)
+            self.i = torch.empty(tokens, topk, dtype=torch.int32, device=dev)
+            self.w = torch.empty(tokens, topk, dtype=torch.float32, device=dev)
         self.use_graph = use_graph and hasattr(layer, "forward_graph")
         self.step = 0
 

@@ -164,6 +164,34 @@ def test_host_pipeline_matches_forward(cuda_device):
         assert torch.equal(out, want)
 
 
+def test_host_pipeline_with_bound_inputs(cuda_device):
+    """A layer whose fp16 shared expert reads the hidden states in place is bound to their address: the serving
+    loop is then given the device tensors the layer was first run on and refills those."""
+    from mxmoe_b200.layer import HostPipeline
+    spec = workload.LayerSpec("tiny-shared16", 8, 2, 512, 256, 512, 48, "zipf", 1.0, False, False, "w4a16_g128_asym")
+    gate_up, down, signs, _ = workload.build_layer_weights(spec, device=cuda_device)
+    lay = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens,
+                   shared_inter=spec.shared_inter, device=cuda_device)
+    batches = []
+    for i in range(4):
+        ids, wts = workload.make_routing(spec, seed=60 + i)
+        batches.append((workload.make_hidden(spec, seed=70 + i).pin_memory(), ids.pin_memory(), wts.pin_memory(),
+                        torch.zeros(spec.tokens, spec.hidden, dtype=torch.float16).pin_memory()))
+    x, i_d, w_d = (t.to(cuda_device) for t in batches[0][:3])
+    wants = []
+    for h, i, w, _ in batches:
+        x.copy_(h); i_d.copy_(i); w_d.copy_(w)
+        wants.append(lay.forward(x, i_d, w_d).cpu())
+    pipe = HostPipeline(lay, spec.tokens, spec.hidden, spec.topk, device=cuda_device, inputs=(x, i_d, w_d))
+    for b in batches:
+        pipe.submit(*b)
+    pipe.drain()
+    torch.cuda.synchronize()
+    lay.check()
+    for (_, _, _, out), want in zip(batches, wants):
+        assert torch.equal(out, want)
+
+
 def test_layer_empty_experts_and_decode_batch(cuda_device):
     """Decode-sized batch: most experts receive no token."""
     spec = workload.LayerSpec("tiny-decode", 16, 2, 512, 256, 0, 3, "zipf", 1.0, False, False, "w4a16_g128_asym")
