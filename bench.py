@@ -177,7 +177,7 @@ def run_reference_arm(args, spec):
 # --------------------------------------------------------------------------- GPU arm
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (mean of the gate_up and the down
 # launch), from the ncu capture summarised in profiles/gg_swap_kernel_qwen15-w4a4-8192_ncu_full.md
-NCU_TRAFFIC_BYTES = {"qwen15-w4a4-8192": (410.8e6 + 243.1e6) / 2}
+NCU_TRAFFIC_BYTES = {"qwen15-w4a4-8192": (411.6e6 + 242.5e6) / 2}
 
 
 def class_pass(layer, spec, counts, peaks, reps: int = 10):
