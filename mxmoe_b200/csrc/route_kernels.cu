@@ -86,8 +86,12 @@ __global__ void __launch_bounds__(kScanThreads) route_scan_kernel(RouteArgs a, i
   for (int i = threadIdx.x; i < nblocks * E; i += kScanThreads) a.workspace[i] += start[i % E];
 }
 
+// kSingle: the whole input is this one block's chunk (a decode batch) - the block also produces the counts and
+// the row offsets itself, so the count and scan launches are not needed and no workspace is read.
+template <bool kSingle>
 __global__ void __launch_bounds__(kThreads) route_scatter_kernel(RouteArgs a) {
   __shared__ int wbase[kThreads / 32][kMaxE];
+  __shared__ int start[kSingle ? kMaxE + 1 : 1];
   const int n    = a.num_tokens * a.topk;
   const int E    = a.num_experts;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,9 +110,36 @@ __global__ void __launch_bounds__(kThreads) route_scatter_kernel(RouteArgs a) {
     __syncwarp();
   }
   __syncthreads();
+  if (kSingle) {
+    for (int e = threadIdx.x; e < E; e += kThreads) {
+      int t = 0;
+      for (int w = 0; w < kWarps; ++w) t += wbase[w][e];
+      start[e]    = t;
+      a.counts[e] = t;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int carry = 0;
+      for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int c = e < E ? start[e] : 0;
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int u = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += u;
+        }
+        if (e < E) start[e] = carry + incl - c;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) start[E] = carry;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += kThreads) a.row_start[e] = start[e];
+  }
   // exclusive prefix over the warps of the block, on top of the block's base
   for (int e = threadIdx.x; e < E; e += kThreads) {
-    int run = a.workspace[blockIdx.x * E + e];
+    int run = kSingle ? start[e] : a.workspace[blockIdx.x * E + e];
     for (int w = 0; w < kWarps; ++w) { const int c = wbase[w][e]; wbase[w][e] = run; run += c; }
   }
   __syncthreads();
@@ -255,9 +286,13 @@ cudaError_t launch_route(const RouteArgs& a, cudaStream_t stream) {
   const int n = a.num_tokens * a.topk;
   const int nblocks = (n + kChunk - 1) / kChunk;
   if (a.num_experts > kMaxE) return cudaErrorInvalidValue;
+  if (nblocks == 1) {   // a decode batch: one launch does all three steps
+    route_scatter_kernel<true><<<1, kThreads, 0, stream>>>(a);
+    return cudaGetLastError();
+  }
   if (nblocks > 0) route_count_kernel<<<nblocks, kThreads, 0, stream>>>(a);
   route_scan_kernel<<<1, kScanThreads, 0, stream>>>(a, nblocks);
-  if (nblocks > 0) route_scatter_kernel<<<nblocks, kThreads, 0, stream>>>(a);
+  if (nblocks > 0) route_scatter_kernel<false><<<nblocks, kThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

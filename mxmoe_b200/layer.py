@@ -371,10 +371,12 @@ class MoELayer:
         self._graph.replay()
         return self.out.view(self.T, self.H)
 
-    # route x3, quant_tokens_scatter, GEMM, silu, GEMM, combine (+1 launch with the two-pass quantiser)
+    # route (3 launches; 1 when all (token, slot) pairs fit one block of 1024), quant_tokens_scatter, GEMM, silu,
+    # GEMM, combine (+1 launch with the two-pass quantiser)
     @property
     def launches_per_step(self) -> int:
-        return 8 if self.one_pass_quant else 9
+        route = 1 if 0 < self.T * self.topk <= 1024 else 3
+        return route + (5 if self.one_pass_quant else 6)
 
     def check(self) -> None:
         self._core.check()
