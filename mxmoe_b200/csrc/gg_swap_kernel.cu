@@ -52,7 +52,11 @@ namespace {
 
 constexpr int kWSlotBytes  = kWT * kRowBytes;   // 16 KiB: plain weights, or 8 / 4 KiB of packed ones
 constexpr int kEpiStageS   = 2048;              // per epilogue warp: 16 token pairs x 32 channels x 4 bytes
+// Converter warps: groups of four (one warp per TMEM lane quarter) that take the stages in turn.  Measured on
+// 8 x [4096, 2816, 2048]: one group w4a4 1815 / w4a16 725 TFLOP/s, two groups 1974 / 924, three groups - / 830;
+// 8- and 16-bit tiles of a launch that also holds 4-bit weights lose 4-7 % per group that is present.
 constexpr int kCvtWarps    = 8;
+constexpr int kCvtGroups   = kCvtWarps / 4;
 constexpr uint32_t kASlotCols = 32;             // TMEM columns of one A slot (128 bytes of K per channel)
 constexpr int kCvtGroup    = 4;                 // warps per converter group (one per TMEM lane quarter)
 
@@ -559,16 +563,16 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       // at the head of every stage's chain of waits would bound the whole pipeline.
       const bool has_sz   = ti.scheme == SCH_W4A16G128 && gn < N;
       const __half2* szp  = reinterpret_cast<const __half2*>(pr->scale_b) + gn;
-      const int kb_first  = (int)((group - it) & 1u);          // first K block of this tile the group handles
+      const int kb_first  = (int)(((uint32_t)group + kCvtGroups - it % kCvtGroups) % kCvtGroups);   // first K block of this tile the group handles
       __half2 sz_next = __float2half2_rn(0.f);
       if (has_sz && kb_first < ti.nkb) sz_next = __ldg(szp + (int64_t)(kb_first >> 1) * N);
       for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
         const int s_cur       = stage;
         const uint32_t ph_cur = phase;
         if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
-        if ((int)(it & 1u) != group) continue;   // the other group's stage
+        if ((int)(it % kCvtGroups) != group) continue;   // another group's stage
         const __half2 sz = sz_next;
-        if (has_sz && kb + 2 < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + 2) >> 1) * N);
+        if (has_sz && kb + kCvtGroups < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + kCvtGroups) >> 1) * N);
         const long long c0 = tick(prof_on);
         const bool ok = warp_wait_bar(smem_u32(&ctrl->full[s_cur]), ph_cur, abort_flag, lane);
         const long long c1 = tick(prof_on);
