@@ -12,6 +12,8 @@
 
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 namespace mxb {
 namespace {
 
@@ -316,10 +318,12 @@ size_t route_static_scratch_ints() { return kStaticScratchInts; }
 // the address a kernel may use is looked up once per device, with that device current.
 cudaError_t route_static_scratch_ptr(int** out) {
   static int* ptrs[64] = {nullptr};
+  static std::mutex mu;   // host threads that make the first call on a device together
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
   if (ptrs[dev] == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_route_scratch);

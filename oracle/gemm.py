@@ -69,6 +69,23 @@ def wxax_epilogue(acc: np.ndarray, sa: np.ndarray, sb: np.ndarray) -> np.ndarray
     return (acc.astype(np.float32) * prod.astype(np.float32)).astype(np.float16)
 
 
+def ref_kernel_scale_b_index(n: int) -> np.ndarray:
+    """Which weight scale the reference's KERNEL applies to output channel c (a defect of the reference).
+
+    ``GlobalTileC::load_scale`` (mm_tile.cuh:461-464) fills the two per-channel scales of an 8-column MMA
+    fragment from ``smem_scale_b[8j + col]`` and ``[8j + col + 1]`` with ``col = lane % 4``, while the
+    thread's accumulator columns are ``8j + 2*col`` and ``8j + 2*col + 1``: channel ``c`` is scaled with
+    the weight scale of channel ``8*(c//8) + (c%8)//2 + c%2``.  Measured on a B200 with the reference's
+    own generated kernel: its w8a8 / w4a4 outputs are bit-identical to
+    ``wxax_epilogue(acc, sa, sb[ref_kernel_scale_b_index(N)])`` and differ from the fake-quant product
+    (rel-L2 0.5) unless the weight scales are constant over blocks of 8 channels.  The product kernels
+    apply ``sb[c]`` to channel ``c`` (what the reference's quantiser and its torch path mean); this map
+    exists so that the tests can show that nothing else differs.
+    """
+    c = np.arange(n)
+    return 8 * (c // 8) + (c % 8) // 2 + c % 2
+
+
 def wxax_epilogue_c(acc: np.ndarray, sa: np.ndarray, sb: np.ndarray) -> np.ndarray:
     lib = c_port()
     assert lib is not None

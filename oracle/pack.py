@@ -9,7 +9,7 @@ code, ``mxmoe/kernels/src/include/quantize.cuh``:
   weight-only schemes (w4a16): codes packed along N, fragment-permuted.
 * ``permute_scale``   (:299-315)  group scales / (scale, zero) pairs, group-major.
 
-``tests/test_oracle_pack.py`` pins every function here against golden words
+``tests/test_oracle_golden.py`` pins every function here against golden words
 produced by the reference's own functions.
 """
 from __future__ import annotations

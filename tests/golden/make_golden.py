@@ -1,9 +1,9 @@
 """Generate the golden vectors under tests/golden/ from the REFERENCE's own code.
 
-Run where the MxMoE checkout is mounted (default /root/reference) after
-``make -C oracle ref`` has compiled the reference's host packers:
+Run where the MxMoE checkout is mounted, after ``make -C oracle ref REF_ROOT=/path/to/MxMoE`` has
+compiled the reference's host packers:
 
-    python tests/golden/make_golden.py [/path/to/MxMoE]
+    python tests/golden/make_golden.py /path/to/MxMoE        (or REF_ROOT=/path/to/MxMoE)
 
 Sources of truth used here (nothing from this repository's oracle or product code):
   * ``mxmoe.quant.quant.quant_minmax`` / ``Quantizer``            (quant.py:40-109)
@@ -21,7 +21,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REF_ROOT")
+if not REF or not os.path.isdir(os.path.join(REF, "mxmoe")):
+    raise SystemExit("make_golden.py: pass the MxMoE checkout as the first argument (or set REF_ROOT)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, REF)

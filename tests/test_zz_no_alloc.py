@@ -8,8 +8,7 @@ inside the library.
 
 The test calls it through the C ABI twice in a row with different routings (the second call finds
 the first call's histograms still in the shared array) and requires the same integers as the
-workspace-taking entry point.  The file name sorts last so that a run stopping at the first
-failure has already executed every other test.
+workspace-taking entry point and as ``torch.sort(stable=True)`` / ``bincount``.
 """
 import ctypes as C
 
@@ -63,6 +62,42 @@ def test_static_scratch_routing_matches_workspace_routing(cuda_device):
             assert torch.equal(got[name], want[name]), name
         for name in ("row_expert", "row_token"):
             assert torch.equal(got[name][:valid], want[name][:valid]), name
+        # and against torch itself: stable sort of the (token, slot) pairs by expert, bincount of the experts
+        flat = torch.from_numpy(ids.reshape(-1).astype(np.int64))
+        ok = flat < e
+        srt, order = torch.sort(flat[ok], stable=True)
+        pairs = torch.nonzero(ok).reshape(-1)[order]
+        assert torch.equal(got["counts"].long(), torch.bincount(srt, minlength=e))
+        assert torch.equal(got["row_expert"][:valid].long(), srt)
+        assert torch.equal(got["row_token"][:valid], pairs // k)
+        inv = torch.full((t * k,), -1, dtype=torch.int64)
+        inv[pairs] = torch.arange(valid)
+        assert torch.equal(got["slot_row"].long(), inv)
+
+
+def test_static_scratch_routing_allocates_nothing(cuda_device):
+    """After the first call on the device (which looks up the address of the built-in array), a call leaves the
+    amount of free device memory unchanged: nothing is allocated behind the caller's back."""
+    rng = np.random.default_rng(5)
+    t, e, k = 4096, 60, 4
+    ids = torch.from_numpy(np.stack([rng.choice(e, k, replace=False) for _ in range(t)]).astype(np.int32)).to(cuda_device)
+    n = t * k
+    bufs = [torch.zeros(e, dtype=torch.int32, device=cuda_device), torch.zeros(e + 1, dtype=torch.int32, device=cuda_device),
+            torch.zeros(n, dtype=torch.int32, device=cuda_device), torch.zeros(n, dtype=torch.int64, device=cuda_device),
+            torch.zeros(n, dtype=torch.int32, device=cuda_device)]
+    a = _lib.RouteArgs()
+    a.topk_ids = ids.data_ptr()
+    a.counts, a.row_start, a.row_expert, a.row_token, a.slot_row = [b.data_ptr() for b in bufs]
+    a.num_tokens, a.topk, a.num_experts = t, k, e
+    stream = current_stream_ptr()
+    _lib.check(_lib.lib().mxmoe_route_topk_static(C.byref(a), stream))     # first call: set-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        _lib.check(_lib.lib().mxmoe_route_topk_static(C.byref(a), stream))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
 
 
 def test_static_scratch_limit_is_reported(cuda_device):
