@@ -132,12 +132,15 @@ class ExpertCompute:
             self.q2s = torch.zeros(T * self.rec2s, **f16)
             self.s2s = torch.zeros(T, **f16)
             self.o2s = torch.zeros(T * H, **f16)
-            # the shared expert reads the token-major store of its format directly: no copy
+            # the shared expert reads the token-major store of its format directly: no copy.  Its row count lives on
+            # the device like the routed experts' (always T; a benchmark that times a subset of the problems zeroes it)
+            self.shared_m = torch.tensor([T], dtype=torch.int32, device=dev)
             p1.append(Problem(A=shared["a_ptr"], B=w1.data, C=self.o1s, M=T, N=2 * Is, K=H, qparams=w1.qparams,
                               scale_a=shared["sa_ptr"] if self._tag1[E] else None, scale_b=w1.scale,
-                              a_expanded=1 if self._tag1[E] == 3 else 0))
+                              a_expanded=1 if self._tag1[E] == 3 else 0, m_dev=self.shared_m))
             p2.append(Problem(A=self.q2s, B=w2.data, C=self.o2s, M=T, N=H, K=Is, qparams=w2.qparams,
-                              scale_a=self.s2s if t2 else None, scale_b=w2.scale, a_expanded=1 if t2 == 3 else 0))
+                              scale_a=self.s2s if t2 else None, scale_b=w2.scale, a_expanded=1 if t2 == 3 else 0,
+                              m_dev=self.shared_m))
         else:
             self.o2s = None
         self.gg1 = GroupedGemm(p1, device=dev)
@@ -376,7 +379,7 @@ class MoELayer:
     @property
     def launches_per_step(self) -> int:
         route = 1 if 0 < self.T * self.topk <= 1024 else 3
-        return route + (5 if self.one_pass_quant else 6)
+        return route + (5 if self.one_pass_quant else 6) + (1 if self.has_shared else 0)   # + the shared expert's silu
 
     def check(self) -> None:
         self._core.check()
@@ -458,7 +461,9 @@ class HostPipeline:
         self.step += 1
 
     def drain(self) -> None:
-        """Make the compute stream wait for every copy that is still in flight."""
+        """Block the host until every submitted step has finished: its result is in ``out_host`` on return."""
         comp = torch.cuda.current_stream(self.device)
         comp.wait_stream(self.s_in)
         comp.wait_stream(self.s_out)
+        self.s_out.synchronize()
+        comp.synchronize()

@@ -117,6 +117,28 @@ def pack_along_n4(codes: torch.Tensor) -> torch.Tensor:
     return out.reshape(n // 4, k).to(torch.int16)
 
 
+def unpack_along_k(words: torch.Tensor, bits: int) -> torch.Tensor:
+    """Inverse of :func:`pack_along_k`: int16 ``[R, W]`` -> int8 codes ``[R, W*16/bits]`` (two's complement fields)."""
+    p = 16 // bits
+    w = words.to(torch.int32) & 0xFFFF
+    shifts = torch.tensor([bits * (p - 1 - i) for i in range(p)], dtype=torch.int32, device=words.device)
+    f = (w.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)
+    f = torch.where(f >= (1 << (bits - 1)), f - (1 << bits), f)
+    return f.reshape(words.shape[0], -1).to(torch.int8)
+
+
+def unpack_along_n4(words: torch.Tensor) -> torch.Tensor:
+    """Inverse of :func:`pack_along_n4`: int16 ``[N/4, K]`` -> int8 codes ``[N, K]`` in 0..15."""
+    n4, k = words.shape
+    n = n4 * 4
+    w = (words.to(torch.int32) & 0xFFFF).reshape(n // 32, 8, k // 16, 2, 8)     # nb r kb fh d
+    codes = torch.zeros((n // 32, 2, 2, 8, k // 16, 2, 8), dtype=torch.int32, device=words.device)  # nb fh fl r kb c d
+    for fl in range(2):
+        for cc in range(2):
+            codes[:, :, fl, :, :, cc, :] = ((w >> (4 * (2 * fl + cc))) & 0xF).permute(0, 3, 1, 2, 4)
+    return codes.reshape(n, k).to(torch.int8)
+
+
 def prepare_weight(w: torch.Tensor, scheme: str, keep_codes: bool = False) -> PackedWeight:
     """Quantise and pack one ``[N, K]`` fp16 weight for ``scheme``."""
     if w.dim() != 2:

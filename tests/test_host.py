@@ -163,3 +163,32 @@ def test_perf_table_schema_matches_the_solver_input():
     # int8 tiles must be cheaper than fp16 tiles of the same shape, 4-bit weight-only the most expensive
     inc = {s: next(iter(next(iter(v.values())).values()))["inc"] for s, v in table.items()}
     assert inc["w8a8_g-1_sym"] < inc["fp16"] < inc["w4a16_g128_asym"]
+
+
+def test_verify_decodes_the_stored_layouts():
+    """mxmoe_b200.verify reads activation rows and packed weights back into logical order: checked against the
+    oracle's packers (which are pinned to the reference's)."""
+    from oracle import pack as op
+    from mxmoe_b200 import verify
+    rng = np.random.default_rng(0)
+    q4 = rng.integers(-7, 8, (5, 256)).astype(np.int32)
+    q8 = rng.integers(-127, 128, (5, 256)).astype(np.int32)
+
+    def carrier(a):
+        return torch.from_numpy(a.copy()).view(torch.float16).reshape(-1)
+    got = verify.decode_rows(carrier(op.expand_k4(q4)), 128, 0, 5, 256, 3)
+    assert np.array_equal(got.numpy().astype(np.int32), q4)
+    got = verify.decode_rows(carrier(op.pack_k(q8, 8).view(np.int16)), 128, 0, 5, 256, 1)
+    assert np.array_equal(got.numpy().astype(np.int32), q8)
+    got = verify.decode_rows(carrier(op.pack_k(q4, 4).view(np.int16)), 64, 1, 3, 256, 2)
+    assert np.array_equal(got.numpy().astype(np.int32), q4[1:4])
+    w = (torch.randn(64, 256, generator=torch.Generator().manual_seed(0)) * 0.02).half()
+    for scheme in ("w4a4_g-1_sym", "w8a8_g-1_sym", "w4a16_g128_asym"):
+        pw = weights.prepare_weight(w, scheme, keep_codes=True)
+        vals, _ = verify.decode_weight(pw)
+        if scheme == "w4a16_g128_asym":
+            s = pw.scale[..., 0].t().repeat_interleave(128, dim=1).double()
+            z = pw.scale[..., 1].t().repeat_interleave(128, dim=1).double()
+            assert torch.equal(vals, (pw.codes.double() * s + z).half())
+        else:
+            assert torch.equal(vals, pw.codes.double())
