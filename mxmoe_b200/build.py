@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "-shared", "-Xcompiler", "-fPIC",
         "-Xptxas", "-v" if verbose else "-warn-spills",
         "-o", LIB + ".tmp",
-    ] + [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+    ] + os.environ.get("MXMOE_NVCC_FLAGS", "").split() + [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

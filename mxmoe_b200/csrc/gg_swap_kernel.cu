@@ -15,32 +15,40 @@
 // TMEM columns: [0,176) and [176,352) two accumulators (128 channels x up to 176 tokens, fp32/int32),
 // [352,512) five A-operand slots of 32 columns (128 channels x 128 bytes of K each), one per ring stage.
 //
-// One CTA (480 threads; 224 when no problem has 4-bit weights):
+// One CTA (608 threads; 352 when no problem has 4-bit weights):
 //   warp 0      TMA producer: weights (packed or plain) + activations into a ring of 5 stages.
 //   warp 1      MMA issuer.  It never touches shared memory: while the tensor core streams its operands
 //               from shared memory, a shared-memory round trip of a regular warp (an mbarrier.try_wait, a
 //               plain load) takes hundreds of cycles, and one of them between two batches of MMAs leaves
 //               the tensor pipe idle.  The warp is paced by NAMED barriers (bar.sync) instead.
-//   warps 2-5   epilogue: tcgen05.ld (lane = channel, columns = tokens) -> scales -> fp16 ->
-//               transposed through shared memory -> 16-byte global stores along the channel axis.
-//   warp 6      watcher: waits on the mbarriers the TMA unit and the converters complete (full[s],
-//               afull[s]) and forwards each stage to the MMA warp with bar.arrive.
-//   warps 7-14  converters: two groups of four warps that take alternate stages; thread = one weight row
+//   warps 2-5, 7-10   epilogue: tcgen05.ld (lane = channel, columns = tokens) -> scales -> fp16 ->
+//               transposed through shared memory -> 16-byte global stores along the channel axis.  Two warps
+//               per TMEM lane quarter take the 32-token chunks of a tile in turn: a chunk is a chain of three
+//               shared-memory round trips (scales, transpose out, transpose in) of several hundred cycles each
+//               while the tensor core streams operands, and with one warp per quarter a tile of few K blocks
+//               (the down projection) was bounded by its epilogue.
+//   warp 6      watcher: waits on the mbarriers the TMA unit completes (xfull[s]; wfull[s] too when the CTA has no
+//               converter warps) and forwards each stage to the MMA warp with bar.arrive.
+//   warps 11-18 converters: two groups of four warps that take alternate stages; thread = one weight row
 //               of the tile (its TMEM lane).  With packed 4-bit ACTIVATIONS in the launch (the reference
 //               operator API's input format; token tiles are then 128 rows) the group also expands the
 //               stage's packed activation rows into the swizzled int8 operand tile in shared memory.
 //
-// Barrier protocol (mbarriers).  full[s] "TMA bytes of stage s have landed"; afull[s] "the converters are
-// done with stage s" (converted weights in tensor memory, expanded activations in shared memory, or nothing
-// to convert); empty[s] "stage s may be refilled" = the MMAs of the stage have completed (tcgen05.commit) and
-// the stage's converter group has read its packed operands.  Every barrier completes once per use of its
-// stage, whatever the tile's scheme, so parities follow from the stage counter and no waiter can be lapped.
-// A slot s of tensor memory needs no barrier of its own: full[s] completes only after the producer saw
-// empty[s] of the previous use, i.e. after the MMAs that read the slot.  Named barriers: 1 + s "stage s is
-// ready" (watcher arrives, MMA warp syncs), 6 + b "accumulator b is drained" (epilogue warps arrive, MMA warp
-// syncs).  Every mbarrier wait is bounded (1 s of %globaltimer); a role whose wait ran out raises the abort
-// flag and keeps walking its loop without waiting or working, so that every bar.arrive another warp counts
-// on is still made and the kernel ends.
+// Barrier protocol (mbarriers).  wfull[s] "the weights of stage s (and packed activations, which the converters
+// expand) have landed"; xfull[s] "the activation tile of stage s has landed"; empty[s] "stage s may be refilled"
+// = the MMAs of the stage have completed (tcgen05.commit) and the stage's converter group has read its packed
+// operands.  Every barrier completes once per use of its stage, whatever the tile's scheme, so parities follow
+// from the stage counter and no waiter can be lapped.  A slot s of tensor memory needs no barrier of its own:
+// wfull[s] completes only after the producer saw empty[s] of the previous use, i.e. after the MMAs that read
+// the slot.  Named barriers: 1 + s "stage s is ready": the MMA warp syncs on it, the watcher arrives once the
+// activation tile is there, and the stage's converter group arrives itself as soon as the converted weights
+// are in tensor memory (no mbarrier and no third warp between the conversion and the MMA: the time from "weights
+// landed" to "MMA issued" is on the critical path of the ring, which is latency bound).  The weights have a
+// barrier of their own so that the conversion starts when the 4-16 KiB of weights are there, not when the
+// 22 KiB activation tile is.  6 + b "accumulator b is drained" (epilogue warps arrive, MMA warp syncs).  Every
+// mbarrier wait is bounded (1 s of %globaltimer); a role whose wait ran out raises the abort flag and keeps
+// walking its loop without waiting or working, so that every bar.arrive another warp counts on is still made
+// and the kernel ends.
 #include "gg_common.cuh"
 
 namespace mxb {
@@ -59,6 +67,7 @@ constexpr int kCvtWarps    = 8;
 constexpr int kCvtGroups   = kCvtWarps / 4;
 constexpr uint32_t kASlotCols = 32;             // TMEM columns of one A slot (128 bytes of K per channel)
 constexpr int kCvtGroup    = 4;                 // warps per converter group (one per TMEM lane quarter)
+constexpr int kEpiWarps    = 8;                 // two per TMEM lane quarter (warps 2-5 and 7-10)
 
 // Two geometries of the same kernel.  Large: token tiles of up to 176 rows, ring of 5 stages - for launches
 // with compute-bound problems.  Small: token tiles of up to 32 rows, ring of 10 stages - for launches whose
@@ -68,6 +77,7 @@ template <bool kSmall>
 struct Geo {
   static constexpr int kTok        = kSmall ? 32 : kTT;          // tokens per tile (tcgen05 N, any multiple of 16 up to this)
   static constexpr int kStages     = kSmall ? 10 : 5;
+  static constexpr int kEpiBufs    = kSmall ? 4 : kEpiWarps;     // transpose buffers: a 32-token tile has one chunk, the second warp of a quarter never stores
   static constexpr int kXSlotBytes = kTok * kRowBytes;           // 22 KiB / 4 KiB
   static constexpr int kStageBytes = kWSlotBytes + kXSlotBytes;
   static constexpr int kRingBytes  = kStages * kStageBytes;      // 190 KiB / 200 KiB
@@ -80,9 +90,14 @@ struct Geo {
   static_assert((kTok + 32) % 8 == 0, "sa_stage rows must stay 16-byte aligned");
 };
 
+constexpr int kFirstCvtWarp = 11;
+constexpr int kAccBarThreads = kEpiWarps * 32 + 32;   // "accumulator drained": epilogue warps arrive, MMA warp syncs
+
 template <int kMode>
 struct CfgS {
-  static constexpr int kThreads = 224 + (kMode ? kCvtWarps * 32 : 0);
+  static constexpr int kThreads = kFirstCvtWarp * 32 + (kMode ? kCvtWarps * 32 : 0);
+  // threads that meet at a "stage s is ready" named barrier: MMA warp + watcher (+ one converter group)
+  static constexpr int kStageBarThreads = 64 + (kMode ? kCvtGroup * 32 : 0);
 };
 
 // What every role needs to know about one tile, precomputed once per CTA: looking a tile up in the
@@ -102,20 +117,23 @@ struct TileS {
 
 template <typename G>
 struct CtrlS {
-  uint64_t full[G::kStages];
+  uint64_t wfull[G::kStages];
+  uint64_t xfull[G::kStages];
   uint64_t empty[G::kStages];
-  uint64_t afull[G::kStages];
   uint64_t tfull[2];
   uint32_t tmem_base;
   int abort_flag;
   int pad[2];
   Sched sched;
-  alignas(16) __half sa_stage[4][G::kTok + 32];   // per epilogue warp: per-token scales of the current tile (read 16 bytes at a time)
+  alignas(16) __half sa_stage[kEpiWarps][G::kTok + 32];   // per epilogue warp: per-token scales of the current tile (read 16 bytes at a time)
   alignas(16) TileRec recs[kMaxRecs];
 };
 
 template <typename G>
-constexpr int smem_bytes_swap() { return 1024 + G::kRingBytes + 4 * kEpiStageS + (int)sizeof(CtrlS<G>); }
+constexpr int smem_bytes_swap() { return 1024 + G::kRingBytes + G::kEpiBufs * kEpiStageS + (int)sizeof(CtrlS<G>); }
+
+static_assert(smem_bytes_swap<Geo<false>>() <= 232448 && smem_bytes_swap<Geo<true>>() <= 232448,
+              "dynamic shared memory of one CTA (227 KiB)");
 
 __device__ __forceinline__ void report_s(GGStatus* status, int role, int tile) {
   atomicCAS(&status->error, 0, kDevErrTimeout);
@@ -152,14 +170,25 @@ __device__ __forceinline__ TileS decode_rec(const TileRec& r) {
   return t;
 }
 
-// named barriers (ids in Geo): stage s is ready (watcher -> MMA warp, 64 threads); accumulator b is drained
-// (epilogue -> MMA warp, 160 threads)
+// named barriers (ids in Geo): stage s is ready (watcher and the stage's converter group -> MMA warp);
+// accumulator b is drained (epilogue warps -> MMA warp)
 __device__ __forceinline__ void nbar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 __device__ __forceinline__ void nbar_arrive(int id, int nthreads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+
+// Optional per-stage timeline of CTA 0 (compile with -DMXMOE_TRACE; debugging aid, not built by default): the clock
+// at which each role passed a point of stage `it` (stages counted from the start of the launch).
+#ifdef MXMOE_TRACE
+constexpr int kTraceEvents = 8, kTraceLen = 512;
+__device__ long long g_trace[kTraceEvents][kTraceLen];
+#define TRACE(ev, it) do { if (blockIdx.x == 0 && (it) < kTraceLen) g_trace[ev][it] = clock64(); } while (0)
+#else
+#define TRACE(ev, it) do { } while (0)
+#endif
+enum { TR_PROD_GOT = 0, TR_PROD_ISSUED, TR_CVT_GOT, TR_CVT_DONE, TR_WATCH, TR_MMA_GOT, TR_MMA_ISSUED, TR_EPI };
 
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
@@ -173,13 +202,14 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
 // issue of every MMA several times slower.  All lanes walk the loop and meet the named barrier of each
 // stage; the elected lane issues.  One MMA consumes 32 bytes of K per row: 8 TMEM columns of A or 32 bytes of a
 // shared-memory row.
-template <int kV, typename G>
+template <int kV, typename G, int kBarThreads>
 __device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uint32_t d_tmem, uint32_t idesc,
                                               uint32_t ring_base, uint32_t a_tmem0, uint32_t empty0, bool prof_on,
-                                              long long& w_oper, long long& w_issue) {
+                                              long long& w_oper, long long& w_issue, int& sidx) {
   for (int kb = 0; kb < nkb; ++kb) {
     const long long c0 = tick(prof_on);
-    nbar_sync(G::kBarStage0 + stage, 64);   // operands of this stage are in place
+    nbar_sync(G::kBarStage0 + stage, kBarThreads);   // operands of this stage are in place
+    if (lane == 0) TRACE(TR_MMA_GOT, sidx);
     const long long c1 = tick(prof_on);
     w_oper += c1 - c0;
     if (elect_one_sync()) {
@@ -215,6 +245,8 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uin
       mma_commit(empty0 + 8 * stage);
     }
     __syncwarp();
+    if (lane == 0) TRACE(TR_MMA_ISSUED, sidx);
+    ++sidx;
     w_issue += tick(prof_on) - c1;
     if (++stage == G::kStages) stage = 0;
   }
@@ -228,7 +260,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
   uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
-  CtrlS<G>* ctrl              = reinterpret_cast<CtrlS<G>*>(smem_gen + G::kRingBytes + 4 * kEpiStageS);
+  CtrlS<G>* ctrl              = reinterpret_cast<CtrlS<G>*>(smem_gen + G::kRingBytes + G::kEpiBufs * kEpiStageS);
   const uint32_t epi_base  = smem_base + G::kRingBytes;
   Sched* sc                = &ctrl->sched;
   volatile int* abort_flag = &ctrl->abort_flag;
@@ -248,9 +280,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   // ------------------------------------------------------------------ setup
   if (tid == 0) {
     for (int s = 0; s < G::kStages; ++s) {
-      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->wfull[s]), 1);
+      mbar_init(smem_u32(&ctrl->xfull[s]), 1);
       mbar_init(smem_u32(&ctrl->empty[s]), 1 + (kCvt ? kCvtGroup : 0));
-      mbar_init(smem_u32(&ctrl->afull[s]), kCvtGroup);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tfull[b]), 1);
@@ -314,25 +346,36 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           const long long c0 = tick(prof_on);
           const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag);
           w_prod += tick(prof_on) - c0;
+          TRACE(TR_PROD_GOT, (int)n_stage);
           ++n_stage;
           if (!got) {
             report_s(status, 1, t);
             ok = false;
             break;
           }
-          const uint32_t bar = smem_u32(&ctrl->full[stage]);
-          mbar_expect_tx(bar, wbytes + xbytes);
-          tma_load_2d(wslot(stage), &pr->tmW, bar, kb * wx_step, wy);
+          const uint32_t wbar = smem_u32(&ctrl->wfull[stage]);
+          const uint32_t bar  = smem_u32(&ctrl->xfull[stage]);
           if (kMode == 2 && ti.scheme == SCH_W4A4) {
             // packed activation rows (64 bytes of K each) go behind the packed weights; the converters expand them
+            mbar_expect_tx(wbar, wbytes + xbytes);
+            tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
             for (int b = 0; b < nbox; ++b)
-              tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, bar, kb * 64, x_row + b * kXBoxSmall);
-          } else if (big) {
+              tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, wbar, kb * 64, x_row + b * kXBoxSmall);
+            mbar_arrive(bar);                     // no activation tile of its own: complete the phase
+            TRACE(TR_PROD_ISSUED, (int)n_stage - 1);
+            if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          mbar_expect_tx(wbar, wbytes);
+          tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+          mbar_expect_tx(bar, xbytes);
+          if (big) {
             tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
           } else {
             for (int b = 0; b < nbox; ++b)
               tma_load_2d(xslot(stage) + b * kXBoxSmall * kRowBytes, &pr->tmXs, bar, kb * xx_step, x_row + b * kXBoxSmall);
           }
+          TRACE(TR_PROD_ISSUED, (int)n_stage - 1);
           if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -347,12 +390,13 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     int stage = 0;
     int acc = 0;
     long long w_oper = 0, w_acc = 0, w_issue = 0;
+    int sidx = 0;   // stages issued so far (timeline tracing only)
     TileRec nrec = tile_rec(0);
     for (int i = 0; i < my_tiles; ++i) {
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
       const long long ca = tick(prof_on);
-      if (i >= 2) nbar_sync(G::kBarAcc0 + acc, 160);     // the epilogue has drained this accumulator (tile i - 2)
+      if (i >= 2) nbar_sync(G::kBarAcc0 + acc, kAccBarThreads);     // the epilogue has drained this accumulator (tile i - 2)
       w_acc += tick(prof_on) - ca;
       const int npad        = (ti.ntok + 15) & ~15;
       const uint32_t d_tmem = tmem_base + acc * G::kAccCols;
@@ -362,28 +406,31 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const int variant     = (from_tmem ? 2 : 0) + (is_int ? 0 : 1);
       const uint32_t a_tmem0 = tmem_base + G::kASlotCol0;
       const uint32_t empty0  = smem_u32(&ctrl->empty[0]);
-      if (variant == 0)      mma_tile_loop<0, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      else if (variant == 1) mma_tile_loop<1, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      else if (variant == 2) mma_tile_loop<2, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
-      else                   mma_tile_loop<3, G>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue);
+      if (variant == 0)      mma_tile_loop<0, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
+      else if (variant == 1) mma_tile_loop<1, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
+      else if (variant == 2) mma_tile_loop<2, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
+      else                   mma_tile_loop<3, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
       if (elect_one_sync()) mma_commit(smem_u32(&ctrl->tfull[acc]));
       __syncwarp();
       acc ^= 1;
     }
     // consume the "drained" arrivals of the last two tiles, so that no named barrier is left half-way
-    for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(G::kBarAcc0 + (i & 1), 160);
+    for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(G::kBarAcc0 + (i & 1), kAccBarThreads);
     if (blockIdx.x == 0 && lane == 0) {
       status->prof[PROF_MMA_WAIT_OPER] = w_oper;
       status->prof[PROF_MMA_WAIT_ACC]  = w_acc;
       status->prof[PROF_MMA_ISSUE]     = w_issue;
     }
-  } else if (warp < 6) {
+  } else if (warp < 6 || (warp > 6 && warp < kFirstCvtWarp)) {
     // ===== epilogue (TMEM lane quarter = warp % 4; lane = output channel, columns = tokens) =====
-    const int q = warp & 3;
+    // warps 2-5 take the even 32-token chunks of a tile, warps 7-10 the odd ones
+    const int q    = warp & 3;
+    const int half = warp > 6 ? 1 : 0;
+    const int ew   = half ? warp - 7 + 4 : warp - 2;
     int acc = 0;
     uint32_t acc_phase = 0;
-    __half* saw        = ctrl->sa_stage[warp - 2];
-    const uint32_t stg = epi_base + (warp - 2) * kEpiStageS;
+    __half* saw        = ctrl->sa_stage[ew];
+    const uint32_t stg = epi_base + ew * kEpiStageS;
     long long w_epi = 0, w_store = 0;
     bool dead = false;   // a wait ran out: walk the remaining tiles without waiting or working
     TileRec nrec = tile_rec(0);
@@ -400,7 +447,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
       const int n_ch      = ti.n_tile * kWT + q * 32 + lane;                                // this thread's channel
       __half2 sb2 = __float2half2_rn(0.f);
-      if (!dead && is_int && out_mode == OUT_FP16) {
+      if (!dead && is_int && out_mode == OUT_FP16 && half * 32 < ntok) {
         // everything that does not depend on the accumulator is fetched before waiting for it
         if (n_ch < N) sb2 = __half2half2(__ldg(pr->scale_b + n_ch));
         __syncwarp();
@@ -418,7 +465,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       }
       if (dead) {
         // keep the MMA warp's bar.sync on this accumulator balanced, do nothing else
-        nbar_arrive(G::kBarAcc0 + acc, 160);
+        nbar_arrive(G::kBarAcc0 + acc, kAccBarThreads);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
         continue;
@@ -451,9 +498,16 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         }
       };
 #pragma unroll 1
-      for (int ch = 0; ch < nchunk; ++ch) {
+      for (int ch = half; ch < nchunk; ch += 2) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + ch * 32, v);
+        // the chunk's per-token scales travel from shared memory while the accumulator load is in flight
+        uint4 sv4[4];
+        if (is_int && out_mode == OUT_FP16) {
+          const uint4* sap = reinterpret_cast<const uint4*>(saw + ch * 32);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) sv4[g] = sap[g];
+        }
         tmem_ld_wait();
         if (out_mode == OUT_ACC) {
           // raw accumulators (int32 / fp32): element (token, channel), used by the bit-exactness tests
@@ -470,10 +524,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         uint32_t h[16];
         if (is_int) {
           // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
-          const uint4* sap = reinterpret_cast<const uint4*>(saw + ch * 32);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const uint4 sv    = sap[g];
+            const uint4 sv    = sv4[g];
             const __half2* s2 = reinterpret_cast<const __half2*>(&sv);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -501,7 +554,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         store_chunk(stg, ch);
       }
       tc_fence_before_sync();
-      nbar_arrive(G::kBarAcc0 + acc, 160);
+      nbar_arrive(G::kBarAcc0 + acc, kAccBarThreads);
       w_store += tick(prof_on) - c1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -515,6 +568,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     int stage = 0;
     uint32_t phase = 0;
     bool dead = false;
+    int wit = 0;   // stages forwarded so far (timeline tracing only)
     TileRec nrec = tile_rec(0);
     for (int i = 0; i < my_tiles; ++i) {
       const int t    = blockIdx.x + i * gridDim.x;
@@ -522,16 +576,18 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);
       for (int kb = 0; kb < ti.nkb; ++kb) {
         if (!dead) {
-          bool ok = warp_wait_bar(smem_u32(&ctrl->full[stage]), phase, abort_flag, lane);
-          // with converter warps in the CTA, afull[s] completes on every stage (converted weights in place,
-          // or nothing to convert)
-          if (ok && kCvt) ok = warp_wait_bar(smem_u32(&ctrl->afull[stage]), phase, abort_flag, lane);
+          // with converter warps in the CTA the stage's converter group waits for the weights (and arrives at the
+          // named barrier itself); without them this warp does
+          bool ok = warp_wait_bar(smem_u32(&ctrl->xfull[stage]), phase, abort_flag, lane);
+          if (ok && !kCvt) ok = warp_wait_bar(smem_u32(&ctrl->wfull[stage]), phase, abort_flag, lane);
           if (!ok) {
             if (lane == 0) report_s(status, 3, t);
             dead = true;
           }
         }
-        nbar_arrive(G::kBarStage0 + stage, 64);   // always: the MMA warp's bar.sync must complete
+        if (lane == 0) TRACE(TR_WATCH, wit);
+        ++wit;
+        nbar_arrive(G::kBarStage0 + stage, CfgS<kMode>::kStageBarThreads);   // always: the MMA warp's bar.sync must complete
         if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -539,18 +595,19 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     // ===== converters: two groups of four warps take alternate stages, so that the chain of shared-memory
     // round trips of one stage (wait, load, store to tensor memory, arrive) overlaps the next stage's.
     // Thread = weight row (channel) 32*q + lane of the tile = its TMEM lane; it converts the row's 128 bytes
-    // of K of the stage into A slot `stage`.  The slot is free when full[stage] has completed: the producer
-    // refilled the stage only after the MMAs of its previous use (which read the slot) had completed.
+    // of K of the stage into A slot `stage`.  The slot is free when wfull[stage] has completed: the producer
+    // refilled the stage only after the MMAs of its previous use (which read the slot) had completed.  When the
+    // converted weights are in tensor memory the group arrives at the stage's named barrier itself.
     const int q     = warp & 3;               // TMEM lane quarter this warp may write
-    const int group = (warp - 7) / kCvtGroup;
+    const int group = (warp - kFirstCvtWarp) / kCvtGroup;
     const int row   = q * 32 + lane;
     int stage = 0;
     uint32_t phase = 0;
     uint32_t it = 0;                          // stages walked so far
-    bool alive = true;
+    bool dead = false;   // a wait ran out: walk the remaining stages without waiting or working, but keep arriving
     long long w_cwait = 0, w_cwork = 0;
     TileRec nrec = tile_rec(0);
-    for (int i = 0; alive && i < my_tiles; ++i) {
+    for (int i = 0; i < my_tiles; ++i) {
       const int t    = blockIdx.x + i * gridDim.x;
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);
@@ -574,14 +631,20 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         const __half2 sz = sz_next;
         if (has_sz && kb + kCvtGroups < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + kCvtGroups) >> 1) * N);
         const long long c0 = tick(prof_on);
-        const bool ok = warp_wait_bar(smem_u32(&ctrl->full[s_cur]), ph_cur, abort_flag, lane);
+        if (!dead) {
+          const bool ok = warp_wait_bar(smem_u32(&ctrl->wfull[s_cur]), ph_cur, abort_flag, lane);
+          if (!ok) {
+            if (lane == 0) report_s(status, convert ? 5 : 6, t);
+            dead = true;
+          }
+        }
+        if (dead) {
+          nbar_arrive(G::kBarStage0 + s_cur, CfgS<kMode>::kStageBarThreads);   // the MMA warp's bar.sync must complete
+          continue;
+        }
         const long long c1 = tick(prof_on);
         w_cwait += c1 - c0;
-        if (!ok) {
-          if (lane == 0) report_s(status, convert ? 5 : 6, t);
-          alive = false;
-          break;
-        }
+        if (q == 0 && lane == 0) TRACE(TR_CVT_GOT, (int)it);
         if (convert) {
           tc_fence_after_sync();
           uint32_t o[32];
@@ -636,10 +699,11 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           __syncwarp();
           w_cwork += tick(prof_on) - c1;
         }
-        if (lane == 0) mbar_arrive(smem_u32(&ctrl->afull[s_cur]));
+        if (q == 0 && lane == 0) TRACE(TR_CVT_DONE, (int)it);
+        nbar_arrive(G::kBarStage0 + s_cur, CfgS<kMode>::kStageBarThreads);
       }
     }
-    if (blockIdx.x == 0 && warp == 7 && lane == 0) {
+    if (blockIdx.x == 0 && warp == kFirstCvtWarp && lane == 0) {
       status->prof[PROF_CVT_WAIT] = w_cwait;
       status->prof[PROF_CVT_WORK] = w_cwork;
     }
@@ -672,6 +736,12 @@ void launch_one(const GGSwapProblemDev* problems, int count, GGStatus* status, i
   gg_swap_kernel<kMode, kSmall><<<num_ctas, CfgS<kMode>::kThreads, smem_bytes_swap<Geo<kSmall>>(), stream>>>(problems, count, status);
 }
 }  // namespace
+
+#ifdef MXMOE_TRACE
+extern "C" int mxmoe_gg_trace(long long* out) {   // out[kTraceEvents][kTraceLen]
+  return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+}
+#endif
 
 cudaError_t gg_configure_swap() {
   cudaError_t e;
