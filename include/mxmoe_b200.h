@@ -105,7 +105,8 @@ typedef struct mxmoe_gg_plan {
                         bit 1: SWAP kernel with token tiles of 32 rows and a ring of 10 stages (set by prepare when no
                         problem has more than 32 rows; the caller may set or clear it before mxmoe_gg_run, e.g. set
                         it when the row counts come from device memory and are known to be small on average) */
-  int32_t reserved_;
+  int32_t kernel;    /* the kernel mxmoe_gg_run launches (an mxmoe_gg_kernel value): chosen by mxmoe_gg_prepare from the
+                        environment variable MXMOE_GG_KERNEL (swap | single | pair; default swap) */
 } mxmoe_gg_plan;
 
 /* Validate the problem list, encode the TMA descriptors on the host and copy the
@@ -116,10 +117,9 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
                      void* stream, mxmoe_gg_plan* plan);
 
 /* Launch the persistent kernel over a prepared workspace; may be called any number of times after
- * one prepare.  `num_ctas` == 0: the default kernel on every SM; > 0: the default kernel with that
- * many CTAs; < 0: the CTA-pair kernel with -num_ctas CTAs (rounded down to even).  The default kernel
- * is named by the environment variable MXMOE_GG_KERNEL (swap | single | pair, read at every call).
- * All kernels give identical results. */
+ * one prepare.  `num_ctas` == 0: the plan's kernel on every SM; > 0: the plan's kernel with that
+ * many CTAs; < 0: the CTA-pair kernel with -num_ctas CTAs (rounded down to even).  Nothing on this
+ * path reads the environment or allocates.  All kernels give identical results. */
 int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void* stream);
 
 /* The same with the kernel named explicitly. */
@@ -137,8 +137,17 @@ int mxmoe_gg_launch(const mxmoe_gg_problem* problems, int problem_count, void* w
                     void* stream);
 
 /* Synchronise `stream` and read the device status block of the workspace:
- * MXMOE_OK, or MXMOE_ERR_DEVICE with the detail in mxmoe_last_error(). */
+ * MXMOE_OK, or MXMOE_ERR_DEVICE with the detail in mxmoe_last_error().  A reported error is cleared,
+ * so that the workspace can be launched again. */
 int mxmoe_gg_check(void* workspace, void* stream);
+
+/* Test hook for the bounded waits of the kernel with swapped operands (no counterpart in the reference, whose
+ * kernels cannot time out).  `timeout_ms` > 0 replaces the 1000 ms limit of every device-side wait of later
+ * launches over `workspace`; `skip_stage` >= 0 makes the producer of CTA 0 leave out the weight load of that
+ * pipeline stage (counted from the start of its work), so that the wait for it runs out: the launch then ends
+ * by itself and mxmoe_gg_check reports MXMOE_ERR_DEVICE with the role and the tile.  (0, -1) restores the
+ * defaults.  Synchronises `stream`. */
+int mxmoe_gg_debug(void* workspace, int timeout_ms, int skip_stage, void* stream);
 
 /* Built-in tracing: cycle counters (clock64 deltas) that CTA 0 recorded during the last launch over
  * `workspace`.  counters[16]: 0 kernel body, 1 producer waiting for a free stage, 2 MMA issuer waiting

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libmxmoe_b200.so")
 # every symbol include/mxmoe_b200.h declares
 EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
-    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_dispatch_rows", "mxmoe_gate_topk", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile",
+    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_dispatch_rows", "mxmoe_gate_topk", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile", "mxmoe_gg_debug",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows", "mxmoe_quant_tokens_scatter",
     "mxmoe_silu_mul_then_quant",
     "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
@@ -46,7 +46,7 @@ class GGProblem(C.Structure):
 
 
 class GGPlan(C.Structure):
-    _fields_ = [("count", C.c_int32), ("needs_cvt", C.c_int32), ("flags", C.c_int32), ("reserved_", C.c_int32)]
+    _fields_ = [("count", C.c_int32), ("needs_cvt", C.c_int32), ("flags", C.c_int32), ("kernel", C.c_int32)]
 
 
 class EpPlanArgs(C.Structure):
@@ -118,6 +118,7 @@ def lib() -> C.CDLL:
         l.mxmoe_gg_launch.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
         l.mxmoe_gg_check.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_gg_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        l.mxmoe_gg_debug.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         l.mxmoe_groupgemm_hz_fused.argtypes = [C.c_void_p] * 14 + [C.c_int]
         l.mxmoe_quant_act.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_silu_mul_then_quant.argtypes = [C.c_void_p, C.c_void_p]

@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstddef>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -138,6 +139,14 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   if (!p.row0_dev && a_rows < (uint64_t)p.row0 + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
 
   const uint64_t K = (uint64_t)p.K, N = (uint64_t)p.N;
+  {
+    // the kernels pack (channel tiles, K blocks, scheme) of a problem into one word: 15 and 12 bits
+    const int kelems = (scheme == mxb::SCH_FP16 || scheme == mxb::SCH_W4A16G128) ? 64 : 128;
+    if ((p.K + kelems - 1) / kelems > 4095)
+      return fail(MXMOE_ERR_UNSUPPORTED, "problem %d: K=%d exceeds the limit of %d for this scheme", idx, p.K, 4095 * kelems);
+    if ((p.N + mxb::kWT - 1) / mxb::kWT > 32767)
+      return fail(MXMOE_ERR_UNSUPPORTED, "problem %d: N=%d exceeds the limit of %d", idx, p.N, 32767 * mxb::kWT);
+  }
   switch (scheme) {
     case mxb::SCH_FP16:
       if (p.K % 8) return fail(MXMOE_ERR_INVALID, "problem %d: fp16 needs K %% 8 == 0 (K=%d)", idx, p.K);
@@ -236,8 +245,8 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
 
 enum GGKernel { GGK_DEFAULT = 0, GGK_SINGLE = 1, GGK_PAIR = 2, GGK_SWAP = 3 };
 
-// which kernel a launch that does not name one uses: MXMOE_GG_KERNEL = swap | single | pair (read at every call,
-// so that a test can switch it)
+// which kernel a launch that does not name one uses: MXMOE_GG_KERNEL = swap | single | pair, read when a workspace
+// is prepared (never on the launch path) and kept in the plan
 int default_kernel() {
   const char* e = getenv("MXMOE_GG_KERNEL");
   if (e && !strcmp(e, "pair")) return GGK_PAIR;
@@ -246,12 +255,13 @@ int default_kernel() {
   return GGK_SWAP;
 }
 
-// token-tile geometry of the SWAP kernel: the plan's flag unless MXMOE_GG_TILES = small | large overrides it
-bool small_tiles(int plan_flags) {
+// token-tile geometry of the SWAP kernel: chosen from the row counts unless MXMOE_GG_TILES = small | large overrides
+// it (read when a workspace is prepared)
+bool small_tiles_at_prepare(bool few_rows) {
   const char* e = getenv("MXMOE_GG_TILES");
   if (e && !strcmp(e, "small")) return true;
   if (e && !strcmp(e, "large")) return false;
-  return (plan_flags & 2) != 0;
+  return few_rows;
 }
 
 struct ShimScratch {
@@ -310,7 +320,7 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
     ++kept;
   }
-  status->pad[0]    = getenv("MXMOE_GG_PROFILE") ? atoi(getenv("MXMOE_GG_PROFILE")) : 0;   // per-role counters on
+  status->prof_on   = getenv("MXMOE_GG_PROFILE") ? atoi(getenv("MXMOE_GG_PROFILE")) : 0;   // per-role counters on
   status->count     = kept;
   status->needs_cvt = needs_cvt;
   // pageable source: the runtime stages the bytes before returning, so `host` may go out of scope
@@ -323,8 +333,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     plan->count     = kept;
     plan->needs_cvt = needs_cvt;
     // few rows in every problem: token tiles of 32 rows and a deeper ring (more weight bytes in flight per SM)
-    plan->flags     = (redirect ? 1 : 0) | (max_rows <= 32 ? 2 : 0);
-    plan->reserved_ = 0;
+    plan->flags     = (redirect ? 1 : 0) | (small_tiles_at_prepare(max_rows <= 32) ? 2 : 0);
+    plan->kernel    = default_kernel();
   }
   return MXMOE_OK;
 }
@@ -343,7 +353,7 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   auto* probs  = reinterpret_cast<const mxb::GGProblemDev*>(base);
   auto* swp    = reinterpret_cast<const mxb::GGSwapProblemDev*>(base + sizeof(mxb::GGProblemDev) * (size_t)count);
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (kernel == GGK_DEFAULT) kernel = default_kernel();
+  if (kernel == GGK_DEFAULT) kernel = (plan->kernel >= GGK_SINGLE && plan->kernel <= GGK_SWAP) ? plan->kernel : GGK_SWAP;
   if (plan->flags & 1) {
     if (kernel != GGK_SWAP) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows run on the SWAP kernel only");
   }
@@ -351,7 +361,7 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
   if (kernel == GGK_PAIR && n < 2) kernel = GGK_SINGLE;
   if (kernel == GGK_PAIR)       CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
-  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, small_tiles(plan->flags), n, cs);
+  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, (plan->flags & 2) != 0, n, cs);
   else                          mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
   CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;
@@ -385,10 +395,23 @@ int mxmoe_gg_check(void* workspace, void* stream) {
   if (words[0] != 0) {
     static const char* roles[] = {"?", "producer", "mma(accumulator)", "mma(operands)", "epilogue", "converter", "converter(pacing)"};
     const int role = (words[1] >> 24) & 0xff;
+    // the report is taken: clear it, so that the workspace can be launched again
+    CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(words), static_cast<cudaStream_t>(stream)));
     return fail(MXMOE_ERR_DEVICE, "kernel reported error %d (%s) in role %s at tile %d", words[0],
                 words[0] == mxb::kDevErrTimeout ? "bounded wait ran out" : "too many problems",
                 role < 7 ? roles[role] : "?", words[1] & 0xffffff);
   }
+  return MXMOE_OK;
+}
+
+int mxmoe_gg_debug(void* workspace, int timeout_ms, int skip_stage, void* stream) {
+  if (!workspace) return fail(MXMOE_ERR_WORKSPACE, "null workspace");
+  if (timeout_ms < 0 || skip_stage < -1) return fail(MXMOE_ERR_INVALID, "bad debug setting");
+  int words[2] = {timeout_ms, skip_stage + 1};
+  auto* base = static_cast<unsigned char*>(workspace) + offsetof(mxb::GGStatus, timeout_ms);
+  static_assert(offsetof(mxb::GGStatus, skip_stage) == offsetof(mxb::GGStatus, timeout_ms) + sizeof(int), "status layout");
+  CUDA_TRY(cudaMemcpyAsync(base, words, sizeof(words), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));   // `words` lives on this stack frame
   return MXMOE_OK;
 }
 

@@ -11,7 +11,9 @@ using namespace ptx;
 
 constexpr uint64_t kTimeoutNs = 1000000000ull;
 
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int backoff_ns = 0) {
+// `timeout_ns`: how long the wait may last (the launch's limit, GGStatus::timeout_ms, default 1 s)
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int backoff_ns = 0,
+                                         uint64_t timeout_ns = kTimeoutNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t it       = 0;
@@ -20,7 +22,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((++it & 63u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kTimeoutNs) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
         *abort_flag = 1;
         return false;
       }
@@ -31,9 +33,10 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 // The same for a whole warp: lane 0 polls (every polling thread is one more access to the mbarrier in shared
 // memory), the outcome is broadcast.  __shfl_sync orders the lanes' later shared-memory reads after lane 0's
 // observation of the barrier.
-__device__ __forceinline__ bool warp_wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
+__device__ __forceinline__ bool warp_wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane,
+                                              uint64_t timeout_ns = kTimeoutNs) {
   int ok = 1;
-  if (lane == 0) ok = wait_bar(bar, parity, abort_flag) ? 1 : 0;
+  if (lane == 0) ok = wait_bar(bar, parity, abort_flag, 0, timeout_ns) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 

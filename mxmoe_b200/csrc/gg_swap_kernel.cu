@@ -310,7 +310,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   __syncthreads();
   tc_fence_after_sync();
 
-  const bool prof_on = status->pad[0] != 0;   // per-role cycle counters wanted (costs a few percent)
+  const bool prof_on = status->prof_on != 0;   // per-role cycle counters wanted (costs a few percent)
+  const uint64_t tmo = status->timeout_ms > 0 ? (uint64_t)status->timeout_ms * 1000000ull : kTimeoutNs;
+  const int skip_stage = blockIdx.x == 0 ? status->skip_stage - 1 : -1;   // test hook, see GGStatus
   const long long prof_t0  = clock64();
   const uint32_t tmem_base = ctrl->tmem_base;
 
@@ -344,7 +346,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;   // (packed int4: see below)
         for (int kb = 0; kb < ti.nkb; ++kb) {
           const long long c0 = tick(prof_on);
-          const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag);
+          const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag, 0, tmo);
           w_prod += tick(prof_on) - c0;
           TRACE(TR_PROD_GOT, (int)n_stage);
           ++n_stage;
@@ -366,8 +368,10 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
             continue;
           }
-          mbar_expect_tx(wbar, wbytes);
-          tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+          if ((int)n_stage - 1 != skip_stage) {
+            mbar_expect_tx(wbar, wbytes);
+            tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+          }
           mbar_expect_tx(bar, xbytes);
           if (big) {
             tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
@@ -457,7 +461,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       }
       const long long c0 = tick(prof_on);
       if (!dead) {
-        const bool ok = warp_wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag, lane);
+        const bool ok = warp_wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag, lane, tmo);
         if (!ok) {
           if (lane == 0) report_s(status, 4, t);
           dead = true;
@@ -501,13 +505,6 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       for (int ch = half; ch < nchunk; ch += 2) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + ch * 32, v);
-        // the chunk's per-token scales travel from shared memory while the accumulator load is in flight
-        uint4 sv4[4];
-        if (is_int && out_mode == OUT_FP16) {
-          const uint4* sap = reinterpret_cast<const uint4*>(saw + ch * 32);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) sv4[g] = sap[g];
-        }
         tmem_ld_wait();
         if (out_mode == OUT_ACC) {
           // raw accumulators (int32 / fp32): element (token, channel), used by the bit-exactness tests
@@ -524,9 +521,11 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         uint32_t h[16];
         if (is_int) {
           // C = fp16_rn( float(acc) * float( fp16_rn(sa * sb) ) )   (mm_tile.cuh:490-493)
+          // (loading the chunk's scales before waiting for the accumulator load was measured slower)
+          const uint4* sap = reinterpret_cast<const uint4*>(saw + ch * 32);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const uint4 sv    = sv4[g];
+            const uint4 sv    = sap[g];
             const __half2* s2 = reinterpret_cast<const __half2*>(&sv);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -578,8 +577,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         if (!dead) {
           // with converter warps in the CTA the stage's converter group waits for the weights (and arrives at the
           // named barrier itself); without them this warp does
-          bool ok = warp_wait_bar(smem_u32(&ctrl->xfull[stage]), phase, abort_flag, lane);
-          if (ok && !kCvt) ok = warp_wait_bar(smem_u32(&ctrl->wfull[stage]), phase, abort_flag, lane);
+          bool ok = warp_wait_bar(smem_u32(&ctrl->xfull[stage]), phase, abort_flag, lane, tmo);
+          if (ok && !kCvt) ok = warp_wait_bar(smem_u32(&ctrl->wfull[stage]), phase, abort_flag, lane, tmo);
           if (!ok) {
             if (lane == 0) report_s(status, 3, t);
             dead = true;
@@ -632,7 +631,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         if (has_sz && kb + kCvtGroups < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + kCvtGroups) >> 1) * N);
         const long long c0 = tick(prof_on);
         if (!dead) {
-          const bool ok = warp_wait_bar(smem_u32(&ctrl->wfull[s_cur]), ph_cur, abort_flag, lane);
+          const bool ok = warp_wait_bar(smem_u32(&ctrl->wfull[s_cur]), ph_cur, abort_flag, lane, tmo);
           if (!ok) {
             if (lane == 0) report_s(status, convert ? 5 : 6, t);
             dead = true;

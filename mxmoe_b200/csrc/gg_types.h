@@ -79,7 +79,11 @@ struct alignas(256) GGStatus {
   int needs_cvt;   // any problem needs the converter warps
   // cycle counters of CTA 0 of the last launch (clock64 deltas), see GGProf
   unsigned long long prof[16];
-  int pad[28];
+  int prof_on;      // per-role cycle counters wanted (costs a few percent)
+  int timeout_ms;   // limit of every bounded wait of the kernel with swapped operands; 0 = 1000 ms
+  int skip_stage;   // test hook: 1 + the pipeline stage (counted from the start of CTA 0's work) whose weight
+                    // load CTA 0's producer leaves out, so that the wait for it runs out; 0 = none
+  int pad[25];
 };
 
 // indices into GGStatus::prof

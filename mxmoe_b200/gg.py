@@ -116,6 +116,11 @@ class GroupedGemm:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().mxmoe_gg_check(self._ws, current_stream_ptr()))
 
+    def debug(self, timeout_ms: int = 0, skip_stage: int = -1) -> None:
+        """Test hook (mxmoe_gg_debug): shorter limit for the device-side waits; leave out one weight load."""
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().mxmoe_gg_debug(self._ws, timeout_ms, skip_stage, current_stream_ptr()))
+
 
 KERNELS = {"default": 0, "single": 1, "pair": 2, "swap": 3}
 
