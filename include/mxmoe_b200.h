@@ -46,6 +46,8 @@ typedef struct mxmoe_qparams {
  *   w8a8   (8,8,-1,sym)     A u16 [M,K/2],           B u16 [N,K/2]   scale_a fp16 [M], scale_b fp16 [N]
  *   w4a4   (4,4,-1,sym)     A u16 [M,K/4],           B u16 [N,K/4]   scale_a fp16 [M], scale_b fp16 [N]
  *   w4a16  (16,4,128,asym)  A fp16 [M,K],            B u16 [N/4,K]   scale_b fp16 [K/128][N][2] (scale, zero)
+ *   w4a16  (16,4,-1,asym)   A fp16 [M,K],            B u16 [N/4,K]   scale_b fp16 [N][2] (scale, zero), one pair per channel
+ *                           (the reference's per-channel weight-only branch, cta_gemm.cuh:112-286; default kernel only)
  * C is fp16 [M,N] (row pitch ldc elements, 0 = N).  With out_mode 1 the raw
  * accumulators are stored instead (int32 for w8a8/w4a4, fp32 otherwise).
  *
@@ -101,7 +103,7 @@ size_t mxmoe_gg_workspace_bytes(int problem_count);
 typedef struct mxmoe_gg_plan {
   int32_t count;     /* problems kept (empty ones are dropped) */
   int32_t needs_cvt; /* kernel variant: 0 no 4-bit operand, 1 4-bit weights only, 2 packed 4-bit activations too */
-  int32_t flags;     /* bit 0: a problem redirects its C rows (c_row0_dev): only the SWAP kernel can run it;
+  int32_t flags;     /* bit 0: a problem redirects its C rows (c_row0_dev) or uses w4a16_g-1_asym: only the SWAP kernel can run it;
                         bit 1: SWAP kernel with token tiles of 32 rows and a ring of 10 stages (set by prepare when no
                         problem has more than 32 rows; the caller may set or clear it before mxmoe_gg_run, e.g. set
                         it when the row counts come from device memory and are known to be small on average) */
@@ -245,6 +247,18 @@ int mxmoe_quant_tokens_scatter(const mxmoe_token_quant_args* stores, const mxmoe
  * quantise per token and pack for the down projection.  Replaces
  * `silu_mul_then_quant_kernel` (launched at mxmoe/kernels/src/ref_bind.cu:701-716). */
 int mxmoe_silu_mul_then_quant(const mxmoe_act_args* args, void* stream);
+
+/* Online Hadamard rotation of fp16 rows whose length n = k * m is not a power of two: `had_k` is a k x k Hadamard
+ * matrix (fp16 +-1, row-major, device memory), m a power of two.  Replaces `matmul_hadU_cuda`
+ * (mxmoe/quant/hadamard_utils.py:96-105), which the reference applies to the down-projection input when its online
+ * rotation is on (mxmoe/quant/rotation.py:403-421):
+ *     out[r, a*m + t] = scale * sum_a' had_k[a, a'] * z[r, a'*m + t]
+ * with z = the rows after the natural-order Walsh-Hadamard transform over every group of m contiguous elements.
+ * `fwht8` != 0 (m == 8 only): that transform is done here and scale is 1/sqrt(n); otherwise the caller has
+ * already transformed the groups (mxmoe_quant_tokens with rotate over [rows * k, m], which scales by 1/sqrt(m))
+ * and scale is 1/sqrt(k).  k <= 176; in == out is allowed. */
+int mxmoe_hadamard_kron(const void* in, void* out, const void* had_k, int rows, int k, int m, float scale, int fwht8,
+                        void* stream);
 
 /* ---- device-side routing and combine -------------------------------------------
  * Stable counting sort of the (token, slot) pairs by expert, entirely on the

@@ -16,7 +16,7 @@ EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
     "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_dispatch_rows", "mxmoe_gate_topk", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile", "mxmoe_gg_debug",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows", "mxmoe_quant_tokens_scatter",
-    "mxmoe_silu_mul_then_quant",
+    "mxmoe_silu_mul_then_quant", "mxmoe_hadamard_kron",
     "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
 )
 
@@ -125,6 +125,7 @@ def lib() -> C.CDLL:
         l.mxmoe_quant_tokens.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_gather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_quant_tokens_scatter.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        l.mxmoe_hadamard_kron.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
         l.mxmoe_ep_plan.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_gate_topk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_ep_dispatch_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]

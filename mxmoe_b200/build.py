@@ -16,8 +16,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmxmoe_b200.so")
-SOURCES = ["capi.cu", "gg_kernel.cu", "gg_pair_kernel.cu", "gg_swap_kernel.cu", "act_kernels.cu", "route_kernels.cu", "ep_kernels.cu"]
-HEADERS = ["ptx.cuh", "gg_common.cuh", "gg_types.h", "act_kernels.h", "route_kernels.h", "ep_kernels.h", os.path.join("..", "..", "include", "mxmoe_b200.h")]
+SOURCES = ["capi.cu", "gg_kernel.cu", "gg_pair_kernel.cu", "gg_swap_kernel.cu", "act_kernels.cu", "had_kernels.cu", "route_kernels.cu", "ep_kernels.cu"]
+HEADERS = ["ptx.cuh", "gg_common.cuh", "gg_types.h", "act_kernels.h", "had_kernels.h", "route_kernels.h", "ep_kernels.h", os.path.join("..", "..", "include", "mxmoe_b200.h")]
 
 
 def _nvcc() -> str:

@@ -21,6 +21,7 @@
 #include "gg_types.h"
 #include "ep_kernels.h"
 #include "route_kernels.h"
+#include "had_kernels.h"
 
 namespace {
 
@@ -88,8 +89,8 @@ int scheme_of(const mxmoe_qparams& q, int* scheme) {
   if (q.a_bits >= 16 && q.w_bits >= 16) { *scheme = mxb::SCH_FP16; return MXMOE_OK; }
   if (q.a_bits == 8 && q.w_bits == 8 && q.gsize == -1 && q.sym) { *scheme = mxb::SCH_W8A8; return MXMOE_OK; }
   if (q.a_bits == 4 && q.w_bits == 4 && q.gsize == -1 && q.sym) { *scheme = mxb::SCH_W4A4; return MXMOE_OK; }
-  if (q.a_bits >= 16 && q.w_bits == 4 && q.gsize == 128 && !q.sym) { *scheme = mxb::SCH_W4A16G128; return MXMOE_OK; }
-  return fail(MXMOE_ERR_UNSUPPORTED, "unsupported scheme w%da%d_g%d_%s (built: fp16, w8a8_g-1_sym, w4a4_g-1_sym, w4a16_g128_asym)",
+  if (q.a_bits >= 16 && q.w_bits == 4 && (q.gsize == 128 || q.gsize == -1) && !q.sym) { *scheme = mxb::SCH_W4A16G128; return MXMOE_OK; }
+  return fail(MXMOE_ERR_UNSUPPORTED, "unsupported scheme w%da%d_g%d_%s (built: fp16, w8a8_g-1_sym, w4a4_g-1_sym, w4a16_g128_asym, w4a16_g-1_asym)",
               q.w_bits, q.a_bits, q.gsize, q.sym ? "sym" : "asym");
 }
 
@@ -169,7 +170,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
       if ((rc = encode_2d(enc, &d->tmB, p.B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, 64, mxb::kBN / 2, CU_TENSOR_MAP_SWIZZLE_NONE, "B", idx))) return rc;
       break;
     case mxb::SCH_W4A16G128:
-      if (p.K % 128) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs K %% 128 == 0 (K=%d)", idx, p.K);
+      if (p.K % (p.q.gsize == 128 ? 128 : 64)) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16 needs K %% %d == 0 (K=%d)", idx, p.q.gsize == 128 ? 128 : 64, p.K);
       if (p.N % 32) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs N %% 32 == 0 (N=%d)", idx, p.N);
       if (!p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w4a16_g128 needs scale_b (scale, zero) pairs", idx);
       if ((reinterpret_cast<uintptr_t>(p.scale_b) & 3) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 4-byte aligned", idx);
@@ -240,6 +241,7 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   o->M = d.M; o->N = d.N; o->K = d.K; o->row0 = d.row0;
   o->scheme = d.scheme; o->out_mode = d.out_mode; o->ldc = d.ldc; o->sa_stride = d.sa_stride;
   o->c_row0_dev = p.c_row0_dev;
+  o->one_group  = (d.scheme == mxb::SCH_W4A16G128 && p.q.gsize == -1) ? 1 : 0;
   return MXMOE_OK;
 }
 
@@ -314,7 +316,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     if (rc) return rc;
     rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept]);
     if (rc) return rc;
-    if (problems[i].c_row0_dev) redirect = true;
+    // redirected C rows and the per-channel 4-bit weight-only scheme exist in the SWAP kernel only
+    if (problems[i].c_row0_dev || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1)) redirect = true;
     if (problems[i].M > max_rows) max_rows = problems[i].M;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
@@ -355,7 +358,7 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   if (kernel == GGK_DEFAULT) kernel = (plan->kernel >= GGK_SINGLE && plan->kernel <= GGK_SWAP) ? plan->kernel : GGK_SWAP;
   if (plan->flags & 1) {
-    if (kernel != GGK_SWAP) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows run on the SWAP kernel only");
+    if (kernel != GGK_SWAP) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows or use w4a16_g-1_asym run on the SWAP kernel only");
   }
   int n = num_ctas;
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
@@ -665,6 +668,20 @@ int mxmoe_gate_topk(const void* logits, int logits_fp16, int num_tokens, int num
     return fail(MXMOE_ERR_INVALID, "bad gate shape T=%d E=%d topk=%d (E <= 512, topk <= min(32, E))", num_tokens, num_experts, topk);
   CUDA_TRY(mxb::launch_gate_topk(logits, logits_fp16 != 0, num_tokens, num_experts, topk, renormalize, topk_ids,
                                  topk_weights, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+int mxmoe_hadamard_kron(const void* in, void* out, const void* had_k, int rows, int k, int m, float scale, int fwht8,
+                        void* stream) {
+  if (!in || !out || !had_k) return fail(MXMOE_ERR_INVALID, "null pointer in Hadamard arguments");
+  if (rows < 0 || k < 1 || k > 176 || m < 8 || (m & (m - 1)) != 0)
+    return fail(MXMOE_ERR_UNSUPPORTED, "Hadamard factor K=%d (1..176) with m=%d (a power of two >= 8) is not supported", k, m);
+  if (fwht8 && m != 8) return fail(MXMOE_ERR_INVALID, "the fused 8-point transform needs m == 8 (m=%d)", m);
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return fail(MXMOE_ERR_INVALID, "Hadamard rows must be 16-byte aligned");
+  CUDA_TRY(mxb::launch_had_kron(static_cast<const __half*>(in), static_cast<__half*>(out),
+                                static_cast<const __half*>(had_k), rows, k, m, scale, fwht8 != 0,
+                                static_cast<cudaStream_t>(stream)));
   return MXMOE_OK;
 }
 

@@ -619,16 +619,19 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       // at the head of every stage's chain of waits would bound the whole pipeline.
       const bool has_sz   = ti.scheme == SCH_W4A16G128 && gn < N;
       const __half2* szp  = reinterpret_cast<const __half2*>(pr->scale_b) + gn;
+      // K blocks per (scale, zero) group as a shift: 1 for groups of 128 (two 64-k stages); the per-channel scheme
+      // (cta_gemm.cuh:112-286) has one group for the whole of K
+      const int gsh       = pr->one_group ? 30 : 1;
       const int kb_first  = (int)(((uint32_t)group + kCvtGroups - it % kCvtGroups) % kCvtGroups);   // first K block of this tile the group handles
       __half2 sz_next = __float2half2_rn(0.f);
-      if (has_sz && kb_first < ti.nkb) sz_next = __ldg(szp + (int64_t)(kb_first >> 1) * N);
+      if (has_sz && kb_first < ti.nkb) sz_next = __ldg(szp + (int64_t)(kb_first >> gsh) * N);
       for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
         const int s_cur       = stage;
         const uint32_t ph_cur = phase;
         if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
         if ((int)(it % kCvtGroups) != group) continue;   // another group's stage
         const __half2 sz = sz_next;
-        if (has_sz && kb + kCvtGroups < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + kCvtGroups) >> 1) * N);
+        if (has_sz && kb + kCvtGroups < ti.nkb) sz_next = __ldg(szp + (int64_t)((kb + kCvtGroups) >> gsh) * N);
         const long long c0 = tick(prof_on);
         if (!dead) {
           const bool ok = warp_wait_bar(smem_u32(&ctrl->wfull[s_cur]), ph_cur, abort_flag, lane, tmo);

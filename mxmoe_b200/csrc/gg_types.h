@@ -67,7 +67,8 @@ struct alignas(128) GGSwapProblemDev {
   int M, N, K, row0;
   int scheme, out_mode, ldc, sa_stride;
   const int* c_row0_dev;   // optional: rows of C start at *c_row0_dev instead of at row0
-  int pad[12];
+  int one_group;           // w4a16: one (scale, zero) pair per channel for the whole of K (per-channel scheme)
+  int pad[11];
 };
 static_assert(sizeof(GGSwapProblemDev) == 512, "GGSwapProblemDev layout");
 

@@ -391,4 +391,8 @@ class EPMoELayer:
         if self.transport == "p2p":
             wanted = int(self.total_recv[1].item())
             if wanted:
+                # the report is taken: clear it, so that later steps that fit are not blamed for this one.  The rows
+                # beyond the capacity were dropped by their senders, so the outputs of the steps since the last
+                # check() are not valid for the tokens that were routed here.
+                self.total_recv[1].zero_()
                 raise RuntimeError(f"rank {self.rank} was sent {wanted} rows, capacity is {self.R_recv}: raise capacity_factor")

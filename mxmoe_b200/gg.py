@@ -75,9 +75,18 @@ class Problem:
 class GroupedGemm:
     """A prepared grouped launch.  ``run()`` enqueues the persistent kernel on the current stream."""
 
+    MAX_PROBLEMS = 256   # problems one launch can walk (kMaxProblems of the kernels)
+
     def __init__(self, problems: Sequence[Problem], device=None):
         self.problems = list(problems)   # keeps the operand tensors alive
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self._parts = None
+        if len(self.problems) > self.MAX_PROBLEMS:
+            # the reference launcher takes any problem_count (kernel_sketch.py:82-145); a longer list is walked by
+            # several launches of at most MAX_PROBLEMS problems each
+            m = self.MAX_PROBLEMS
+            self._parts = [GroupedGemm(self.problems[i:i + m], device=self.device) for i in range(0, len(self.problems), m)]
+            return
         lib = _lib.lib()
         n = len(self.problems)
         self._arr = (_lib.GGProblem * max(n, 1))()
@@ -95,15 +104,25 @@ class GroupedGemm:
 
     @property
     def kept(self) -> int:
+        if self._parts is not None:
+            return sum(p.kept for p in self._parts)
         return self._plan.count
 
     def set_small_tiles(self, on: bool) -> None:
         """Override the library's choice of token-tile geometry (32-row tiles and a deeper ring: for launches whose
         problems hold few rows each, e.g. a decode batch whose row counts only exist on the device)."""
+        if self._parts is not None:
+            for p in self._parts:
+                p.set_small_tiles(on)
+            return
         self._plan.flags = (self._plan.flags | 2) if on else (self._plan.flags & ~2)
 
     def run(self, num_ctas: int = 0, kernel: str | None = None) -> None:
         """Launch; ``kernel`` in KERNELS names the kernel, None leaves the choice to the library."""
+        if self._parts is not None:
+            for p in self._parts:
+                p.run(num_ctas, kernel)
+            return
         with torch.cuda.device(self.device):
             if kernel is None:
                 _lib.check(_lib.lib().mxmoe_gg_run(self._ws, C.byref(self._plan), num_ctas, current_stream_ptr()))
@@ -113,6 +132,10 @@ class GroupedGemm:
 
     def check(self) -> None:
         """Synchronise the current stream and raise if the kernel recorded an error."""
+        if self._parts is not None:
+            for p in self._parts:
+                p.check()
+            return
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().mxmoe_gg_check(self._ws, current_stream_ptr()))
 

@@ -80,7 +80,8 @@ class ExpertCompute:
                  seg_expert, seg_m: torch.Tensor, seg_row0: torch.Tensor, row_expert: torch.Tensor,
                  q1: torch.Tensor, rec1: int, scale1_ptr: int, scale1_stride: int, device,
                  shared: dict | None = None, shared_inter: int = 0, tag_fn=internal_tag,
-                 down_out: list | None = None, rows_dev: torch.Tensor | None = None):
+                 down_out: list | None = None, rows_dev: torch.Tensor | None = None,
+                 online_had: torch.Tensor | None = None):
         self.E, self.H, self.I, self.Is = num_experts, hidden, inter, shared_inter
         self.R, self.device = rows_cap, device
         self.gate_up, self.down = gate_up, down
@@ -91,6 +92,9 @@ class ExpertCompute:
         # rows_dev: live row count on the device (sizes the work of the second quantiser)
         self.rows_dev = rows_dev
         dev, R, H, I = device, rows_cap, hidden, inter
+        # online rotation of the down-projection input of the routed experts (rotation.py:403-421): a K x K Hadamard
+        # factor (fp16, on the device); the down weights must have been rotated with the same matrix offline
+        self.had_k = None if online_had is None else online_had.to(device=dev, dtype=torch.float16).contiguous()
         f16 = dict(dtype=torch.float16, device=dev)
         local = sorted(set(self.seg_expert))
 
@@ -108,6 +112,10 @@ class ExpertCompute:
         self.q2 = torch.zeros(max(R, 1) * self.rec2, **f16)    # down input records
         self.s2 = torch.zeros(max(R, 1), **f16)
         self.o2 = torch.zeros(max(R, 1) * H, **f16)            # down output rows [R, H]
+        if self.had_k is not None:
+            self.h16 = torch.zeros(max(R, 1), I, **f16)        # silu(gate) * up rows, rotated in place
+            self.tag0 = torch.zeros(num_experts + 1, dtype=torch.int32, device=dev)
+            self.row_ident = torch.arange(max(R, 1), dtype=torch.int64, device=dev)
 
         p1, p2 = [], []
         for i, e in enumerate(self.seg_expert):
@@ -155,11 +163,25 @@ class ExpertCompute:
         """``rows``: upper bound of the rows in use this step (sizes the silu launch)."""
         lib = _lib.lib()
         self.gg1.run()
-        _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.q2, s_store=self.s2,
-                  row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
-                  exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
-                  rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1,
-                  rows_dev=self.rows_dev)
+        if self.had_k is None:
+            _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.q2, s_store=self.s2,
+                      row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
+                      exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
+                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1,
+                      rows_dev=self.rows_dev)
+        else:
+            # h = silu(gate) * up as fp16 rows -> h (had_K (x) H_m) / sqrt(I) in place -> quantise per expert format
+            from .hadamard import hadamard_kron
+            _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.h16, s_store=self.s2,
+                      row_expert=self.row_expert, row_token=None, exp_qtag=self.tag0, exp_row_start=None,
+                      exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
+                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.I, rec_scale_off=-1,
+                      rows_dev=self.rows_dev)
+            hadamard_kron(self.h16[:rows], self.had_k, out=self.h16[:rows])
+            _act_call(lib.mxmoe_quant_act, inp=self.h16, in_shared=None, q_store=self.q2, s_store=self.s2,
+                      row_expert=self.row_expert, row_token=self.row_ident, exp_qtag=self.tag2, exp_row_start=None,
+                      exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
+                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1)
         if self.shared is not None:
             T = self.shared["tokens"]
             _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1s, in_shared=self.o1s, q_store=self.q2s,
@@ -222,12 +244,13 @@ class MoELayer:
 
     def __init__(self, num_experts: int, topk: int, hidden: int, inter: int, gate_up: dict, down: dict,
                  max_tokens: int, shared_inter: int = 0, signs: torch.Tensor | None = None, rotate: bool = False,
-                 device=None):
+                 device=None, online_had: torch.Tensor | None = None):
         self.E, self.topk, self.H, self.I, self.Is = num_experts, topk, hidden, inter, shared_inter
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.T = max_tokens
         self.has_shared = shared_inter > 0 and num_experts in gate_up
         self.rotate = rotate
+        self.online_had = online_had     # K x K Hadamard factor of the online rotation of the down-projection input
         self.gate_up, self.down = gate_up, down
         dev = self.device
         i32 = dict(dtype=torch.int32, device=dev)
@@ -275,7 +298,7 @@ class MoELayer:
         assert self._routed == list(range(len(self._routed))), "single-GPU layer owns experts 0..E-1"
         self._core = ExpertCompute(self.E, self.H, self.I, self.gate_up, self.down, self.R, self._routed, seg_m,
                                    seg_row0, self.row_expert, self.q1, self.rec1, self.s1.data_ptr(), 1, self.device,
-                                   shared=shared, shared_inter=self.Is)
+                                   shared=shared, shared_inter=self.Is, online_had=self.online_had)
         self.gg1, self.gg2 = self._core.gg1, self._core.gg2
 
     # buffers of the compute core, exposed for tests and benchmarks
@@ -379,7 +402,8 @@ class MoELayer:
     @property
     def launches_per_step(self) -> int:
         route = 1 if 0 < self.T * self.topk <= 1024 else 3
-        return route + (5 if self.one_pass_quant else 6) + (1 if self.has_shared else 0)   # + the shared expert's silu
+        return (route + (5 if self.one_pass_quant else 6) + (1 if self.has_shared else 0)   # + the shared expert's silu
+                + (2 if self.online_had is not None else 0))                               # + rotation, quantiser
 
     def check(self) -> None:
         self._core.check()

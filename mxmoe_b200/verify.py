@@ -61,6 +61,7 @@ def decode_weight(w) -> tuple[torch.Tensor, torch.Tensor | None]:
     if a_bits < 16:
         return unpack_along_k(w.data.reshape(w.n, -1), w_bits).double(), w.scale
     q = unpack_along_n4(w.data.reshape(w.n // 4, w.k)).to(torch.float16)
+    gsize = w.k if gsize == -1 else gsize
     sz = w.scale.reshape(w.k // gsize, w.n, 2)
     s = sz[..., 0].t().repeat_interleave(gsize, dim=1)
     z = sz[..., 1].t().repeat_interleave(gsize, dim=1)

@@ -15,7 +15,8 @@ import dataclasses
 
 import torch
 
-SCHEMES = ("fp16", "w8a8_g-1_sym", "w4a4_g-1_sym", "w4a16_g128_asym")
+SCHEMES = ("fp16", "w8a8_g-1_sym", "w4a4_g-1_sym", "w4a16_g128_asym")     # the schemes of the benchmark configurations
+EXTRA_SCHEMES = ("w4a16_g-1_asym",)                                        # per-channel weight-only (cta_gemm.cuh:112-286)
 
 
 def parse_scheme(name: str) -> tuple[int, int, int, bool]:
@@ -146,20 +147,21 @@ def prepare_weight(w: torch.Tensor, scheme: str, keep_codes: bool = False) -> Pa
     a_bits, w_bits, g, sym = parse_scheme(scheme)
     n, k = w.shape
     name = scheme_name(a_bits, w_bits, g, sym)
-    if name not in SCHEMES:
-        raise ValueError(f"scheme {scheme!r} is not supported (supported: {SCHEMES})")
+    if name not in SCHEMES + EXTRA_SCHEMES:
+        raise ValueError(f"scheme {scheme!r} is not supported (supported: {SCHEMES + EXTRA_SCHEMES})")
     if name == "fp16":
         return PackedWeight(name, n, k, w.to(torch.float16).contiguous(), None)
     codes, scale, zero = quantize_minmax(w, w_bits, g, sym)
     if name in ("w8a8_g-1_sym", "w4a4_g-1_sym"):
         data = pack_along_k(codes, w_bits)
         sc = scale.reshape(n).to(torch.float16).contiguous()
-    else:  # w4a16_g128_asym
-        if k % 128:
-            raise ValueError(f"group-128 scheme needs K % 128 == 0 (K={k})")
+    else:  # w4a16_g128_asym, w4a16_g-1_asym (one group = the whole row)
+        gs = k if g == -1 else g
+        if k % gs or k % 64:
+            raise ValueError(f"scheme {name} needs K % {max(gs if g != -1 else 64, 64)} == 0 (K={k})")
         data = pack_along_n4(codes)
-        ng = k // 128
+        ng = k // gs
         s = scale.reshape(n, ng).to(torch.float16)
         z = zero.reshape(n, ng).to(torch.float16)
-        sc = torch.stack((s.t(), z.t()), dim=-1).contiguous()        # [K/128, N, 2] (quantize.cuh:299-315)
+        sc = torch.stack((s.t(), z.t()), dim=-1).contiguous()        # [K/g, N, 2] (quantize.cuh:299-315)
     return PackedWeight(name, n, k, data.contiguous(), sc, codes.to(torch.int8) if keep_codes else None)

@@ -193,14 +193,16 @@ def expert_weights_fp16(spec: LayerSpec, e: int, seed: int = 1000, device="cpu")
 
 
 def build_layer_weights(spec: LayerSpec, experts=None, seed: int = 1000, scheme_seed: int = 3, sign_seed: int = 4,
-                        gen_device="cpu", device="cpu", keep_codes: bool = False):
+                        gen_device="cpu", device="cpu", keep_codes: bool = False, online_had=None):
     """Quantised + packed weights of the layer: ``(gate_up: dict e -> PackedWeight, down: dict, signs, (gu, dn))``.
 
     ``experts`` restricts the routed experts that are materialised (expert parallelism);
     the shared expert, if the layer has one, is always included under key ``num_experts``.
     With ``spec.rotate`` every gate_up weight is rotated over the hidden dim offline (``W Q``), whatever
     its scheme, and the activation prologue rotates every row (``x Q``), as in a rotated model where
-    the residual stream itself is rotated.
+    the residual stream itself is rotated.  ``online_had`` (a K x K Hadamard factor, ``inter = K * m``): the down
+    weights of the routed experts are rotated over their input dimension offline, for a layer that rotates the
+    down-projection input online (apply_exact_had_to_linear + the hook of rotation.py:403-421).
     """
     gu_s, dn_s = draw_schemes(spec, scheme_seed)
     signs = rotation_signs(spec, sign_seed)
@@ -212,6 +214,9 @@ def build_layer_weights(spec: LayerSpec, experts=None, seed: int = 1000, scheme_
         wgu, wdn = expert_weights_fp16(spec, e, seed, gen_device)
         if signs is not None:
             wgu = rotate_rows(wgu, signs)
+        if online_had is not None and e < spec.num_experts:
+            from .hadamard import rotate_rows_kron
+            wdn = rotate_rows_kron(wdn, online_had)
         gate_up[e] = prepare_weight(wgu, gu_s[e], keep_codes).to(device)
         down[e] = prepare_weight(wdn, dn_s[e], keep_codes).to(device)
     return gate_up, down, signs, (gu_s, dn_s)

@@ -1,7 +1,8 @@
 """Hadamard rotation restatement (TEST INFRASTRUCTURE ONLY).
 
-Power-of-two sizes only (the 2048- and 4096-point rotations of the hidden
-dimension).  Follows ``mxmoe/quant/hadamard_utils.py:62-83`` (``matmul_hadU``,
+Power-of-two sizes (the 2048- and 4096-point rotations of the hidden dimension) and
+sizes n = K * 2^j with a K x K Hadamard factor (``hadamard_kron_rows``: the online
+rotation of the down-projection input, 1408 = 176 x 8, 14336 = 28 x 512).  Follows ``mxmoe/quant/hadamard_utils.py:62-83`` (``matmul_hadU``,
 K == 1 branch: a radix-2 butterfly over adjacent pairs, i.e. the natural-order
 Sylvester transform, divided by ``torch.tensor(n).sqrt()``, which is an *fp32*
 square root) and ``:89-94`` (``random_hadamard_matrix``: the transform applied
@@ -38,6 +39,21 @@ def hadamard_rows(x: torch.Tensor) -> torch.Tensor:
     n = x.shape[-1]
     # the reference divides by an fp32-rounded sqrt(n) (0-dim float32 tensor)
     return fwht_rows(x) / torch.tensor(n).sqrt()
+
+
+def hadamard_kron_rows(x: torch.Tensor, had_k: torch.Tensor) -> torch.Tensor:
+    """``matmul_hadU(x)`` for ``n = K * m``, m a power of two, with the K x K factor ``had_k`` that
+    ``get_hadK(n)`` returns (hadamard_utils.py:5-59, :62-83; the CUDA form ``matmul_hadU_cuda`` :96-105 computes
+    the same thing): the row is viewed as ``[K, m]``, the natural-order Walsh-Hadamard transform runs over
+    the m contiguous elements, ``had_k`` mixes the K groups, and the result is divided by the fp32 ``sqrt(n)``:
+    ``y[a*m + t] = sum_a' had_k[a, a'] * sum_l (-1)^popcount(t & l) * x[a'*m + l] / sqrt(n)``."""
+    n = x.shape[-1]
+    k = had_k.shape[0]
+    m = n // k
+    assert k * m == n and _is_pow2(m)
+    z = fwht_rows(x.reshape(-1, k, m))                       # over the contiguous m
+    y = torch.einsum("ab,rbt->rat", had_k.to(x.dtype), z)
+    return (y.reshape(x.shape)) / torch.tensor(n).sqrt()
 
 
 def random_hadamard(n: int, generator: torch.Generator | None = None) -> torch.Tensor:

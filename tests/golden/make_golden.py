@@ -70,6 +70,22 @@ def golden_hadamard():
     np.savez_compressed(os.path.join(HERE, "hadamard.npz"), **out)
 
 
+def golden_hadamard_kron():
+    """Sizes that are not powers of two: ``matmul_hadU`` with the Kronecker factor ``get_hadK`` picks
+    (hadamard_utils.py:5-59): 1408 = 176 x 8 (Qwen1.5-MoE expert intermediate) and 14336 = 28 x 512 (Mixtral).
+    Stores the reference's K x K factor (+-1), the inputs and the transformed rows."""
+    g = torch.Generator().manual_seed(15)
+    out = {}
+    for n in (1408, 14336):
+        had, k = hu.get_hadK(n)
+        x = torch.randn(3, n, generator=g, dtype=torch.float64)
+        out[f"k{n}"] = np.array(k)
+        out[f"had{n}"] = had.numpy().astype(np.int8)
+        out[f"x{n}"] = x.numpy()
+        out[f"y{n}"] = hu.matmul_hadU(x).numpy()
+    np.savez_compressed(os.path.join(HERE, "hadamard_kron.npz"), **out)
+
+
 def golden_pack():
     rng = np.random.default_rng(13)
     out = {}
@@ -135,6 +151,7 @@ def golden_layer():
 if __name__ == "__main__":
     golden_quant()
     golden_hadamard()
+    golden_hadamard_kron()
     golden_pack()
     golden_layer()
     for f in sorted(os.listdir(HERE)):

@@ -274,3 +274,14 @@ def test_redirected_c_rows(cuda_device, gg_kernel):
         assert np.array_equal(got[c0:c0 + m].view(np.uint16), ref.view(np.uint16))
         written[c0:c0 + m] = True
     assert np.isnan(got[~written].astype(np.float32)).all(), "rows outside the redirected ranges were written"
+
+
+def test_more_problems_than_one_launch_walks(cuda_device):
+    """A list longer than the 256 problems one launch can walk (a 256-expert layer plus its shared expert) is
+    split into several launches by GroupedGemm; the reference launcher takes any problem count."""
+    rng = np.random.default_rng(257)
+    cases = [util.WxAxCase(rng, 1 + (i % 5), 128, 128, 8) for i in range(257)]
+    g = util.run([c.problem(cuda_device) for c in cases])
+    assert g.kept == 257
+    for i in (0, 100, 255, 256):
+        assert np.array_equal(cases[i].C.cpu().numpy().view(np.uint16), cases[i].ref.view(np.uint16)), i

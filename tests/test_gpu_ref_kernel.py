@@ -5,7 +5,7 @@ sm_100a into ``oracle/_ref/libref_gg.so`` (``make -C oracle refgg``) and run by 
 (``tests/ref_gg_worker.py``) on the seeded cases of ``tests/ref_cases.py``; this process runs the same cases
 through the C ABI and compares:
 
-* fp16 and w4a16 group-128: rel-L2 <= 1e-3 (the bound stated for fp16 outputs against the reference's
+* fp16, w4a16 group-128 and w4a16 per-channel: rel-L2 <= 1e-3 (the bound stated for fp16 outputs against the reference's
   GroupGEMM; the two kernels accumulate in fp32 in different orders);
 * w8a8 / w4a4: the same bits.  The reference kernel scales channel c with the weight scale of channel
   ``8*(c//8) + (c%8)//2 + c%2`` (oracle.gemm.ref_kernel_scale_b_index), so the comparison is made (a) with
@@ -31,7 +31,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB = os.path.join(ROOT, "oracle", "_ref", "libref_gg.so")
-SCHEMES = ("fp16", "w8a8_g-1_sym", "w4a4_g-1_sym", "w4a16_g128_asym")
+SCHEMES = ("fp16", "w8a8_g-1_sym", "w4a4_g-1_sym", "w4a16_g128_asym", "w4a16_g-1_asym")
 REL_L2 = 1e-3
 
 
@@ -65,7 +65,7 @@ def run_ours(c: dict, dev, remap_sb: bool = False) -> np.ndarray:
     else:
         t = [util.t16(c["a"], dev), util.t16(op.pack_n4(c["qb"]), dev),
              util.t16(op.group_major_scales(c["sb"], c["zb"]), dev)]
-        p = gg.Problem(A=t[0], B=t[1], C=C, M=m, N=n, K=k, qparams=util.Q_W4A16, scale_b=t[2])
+        p = gg.Problem(A=t[0], B=t[1], C=C, M=m, N=n, K=k, qparams=(16, 4, gsize, False), scale_b=t[2])
     keep.append(t)
     util.run([p])
     return C.cpu().numpy()

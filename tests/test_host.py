@@ -62,7 +62,7 @@ def test_argument_validation_without_device():
     assert lib.mxmoe_route_topk(ctypes.byref(r), None) == 1
 
 
-@pytest.mark.parametrize("scheme", weights.SCHEMES)
+@pytest.mark.parametrize("scheme", weights.SCHEMES + weights.EXTRA_SCHEMES)
 def test_prepare_weight_matches_oracle_layouts(scheme):
     g = torch.Generator().manual_seed(5)
     w = (torch.randn(64, 256, generator=g) * 0.02).half()
@@ -75,7 +75,7 @@ def test_prepare_weight_matches_oracle_layouts(scheme):
     codes, scale, zero = oq.minmax_quantize(w, wb, gs, sym)
     assert torch.equal(pw.codes.to(torch.float16), codes)
     packed = pw.data.numpy().view(np.uint16)
-    if gs == -1:
+    if a < 16:
         assert np.array_equal(packed, op.pack_k(codes.numpy().astype(np.int32), wb))
         assert np.array_equal(pw.scale.numpy().view(np.uint16), scale.reshape(-1).numpy().view(np.uint16))
     else:

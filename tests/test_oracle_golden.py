@@ -37,6 +37,16 @@ def test_hadamard_matches_reference():
     assert np.allclose(q.numpy() @ q.numpy().T, np.eye(128), atol=1e-6)
 
 
+def test_hadamard_kron_matches_reference():
+    """Sizes with a Kronecker factor (1408 = 176 x 8, 14336 = 28 x 512) against the reference's matmul_hadU."""
+    z = np.load(os.path.join(G, "hadamard_kron.npz"))
+    for n in (1408, 14336):
+        had = torch.from_numpy(z[f"had{n}"].astype(np.float64))
+        assert had.shape[0] == int(z[f"k{n}"]) and torch.equal(had @ had.t(), had.shape[0] * torch.eye(had.shape[0], dtype=torch.float64))
+        y = oh.hadamard_kron_rows(torch.from_numpy(z[f"x{n}"]), had)
+        assert np.allclose(y.numpy(), z[f"y{n}"], rtol=0, atol=1e-12), n
+
+
 def test_pack_matches_reference_packers():
     z = np.load(os.path.join(G, "pack.npz"))
     for bits in (4, 8):
