@@ -344,6 +344,24 @@ typedef struct mxmoe_ep_dispatch_args {
   int32_t reserved_;
 } mxmoe_ep_dispatch_args;
 
+/* Stream-ordered barrier between the ranks (one process per GPU): every rank's earlier kernels on its stream, their
+ * stores to peer memory included, have completed before any rank's later kernels start.  Each rank owns a "sync
+ * block" of int32 in peer-mapped (symmetric) memory, zero-initialised once: [0, 64) arrival flags by rank, [64] error
+ * word, [65] epoch, [128, 128 + world * payload_cap) payload slots by rank (mxmoe_ep_sync_block_ints gives the
+ * size).  With `payload` set, payload_len int32 of this rank are written into slot `rank` of every peer before the
+ * barrier: the all-gather of the per-expert row counts.  The wait for the peers is bounded (timeout_ms, 0 = 2000 ms);
+ * when it runs out, local_sync[64] is set to 1 + the missing rank and the kernel returns.  No NCCL call, no host
+ * involvement: a step built from it can be captured in a CUDA graph.  The ranks must run on different GPUs. */
+typedef struct mxmoe_ep_sync_args {
+  const uint64_t* peer_sync; /* [world] device array: every rank's sync block as mapped here */
+  int32_t* local_sync;       /* this rank's sync block */
+  const int32_t* payload;    /* optional */
+  int32_t world, rank, payload_len, payload_cap;
+  int32_t timeout_ms;
+  int32_t reserved_;
+} mxmoe_ep_sync_args;
+
+int mxmoe_ep_sync(const mxmoe_ep_sync_args* args, void* stream);
 int mxmoe_ep_plan(const mxmoe_ep_plan_args* args, void* stream);
 int mxmoe_ep_dispatch_rows(const mxmoe_ep_dispatch_args* args, const mxmoe_token_quant_args* stores, void* stream);
 

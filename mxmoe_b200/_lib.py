@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libmxmoe_b200.so")
 # every symbol include/mxmoe_b200.h declares
 EXPORTS = (
     "mxmoe_last_error", "mxmoe_version", "mxmoe_device_sm_count",
-    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_dispatch_rows", "mxmoe_gate_topk", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile", "mxmoe_gg_debug",
+    "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_sync", "mxmoe_ep_dispatch_rows", "mxmoe_gate_topk", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile", "mxmoe_gg_debug",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows", "mxmoe_quant_tokens_scatter",
     "mxmoe_silu_mul_then_quant", "mxmoe_hadamard_kron",
     "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
@@ -57,6 +57,12 @@ class EpPlanArgs(C.Structure):
         ("seg_m", C.c_void_p), ("seg_row0", C.c_void_p), ("seg_src_row0", C.c_void_p), ("recv_row_expert", C.c_void_p),
         ("total_recv", C.c_void_p), ("dst_row0", C.c_void_p), ("exp_owner", C.c_void_p),
     ]
+
+
+class EpSyncArgs(C.Structure):
+    _fields_ = [("peer_sync", C.c_void_p), ("local_sync", C.c_void_p), ("payload", C.c_void_p),
+                ("world", C.c_int32), ("rank", C.c_int32), ("payload_len", C.c_int32), ("payload_cap", C.c_int32),
+                ("timeout_ms", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class EpDispatchArgs(C.Structure):
@@ -127,6 +133,7 @@ def lib() -> C.CDLL:
         l.mxmoe_quant_tokens_scatter.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         l.mxmoe_hadamard_kron.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
         l.mxmoe_ep_plan.argtypes = [C.c_void_p, C.c_void_p]
+        l.mxmoe_ep_sync.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_gate_topk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_ep_dispatch_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         l.mxmoe_route_workspace_bytes.restype = C.c_size_t

@@ -701,6 +701,19 @@ int mxmoe_ep_plan(const mxmoe_ep_plan_args* a, void* stream) {
   return MXMOE_OK;
 }
 
+int mxmoe_ep_sync(const mxmoe_ep_sync_args* a, void* stream) {
+  if (!a) return fail(MXMOE_ERR_INVALID, "null args");
+  if (a->world <= 0 || a->world > 64 || a->rank < 0 || a->rank >= a->world || a->payload_len < 0 ||
+      a->payload_len > a->payload_cap || !a->peer_sync || !a->local_sync)
+    return fail(MXMOE_ERR_INVALID, "bad barrier arguments world=%d rank=%d payload=%d/%d", a->world, a->rank,
+                a->payload_len, a->payload_cap);
+  static_assert(sizeof(mxmoe_ep_sync_args) == sizeof(mxb::EpSyncArgs), "sync args layout");
+  mxb::EpSyncArgs k;
+  std::memcpy(&k, a, sizeof(k));
+  CUDA_TRY(mxb::launch_ep_sync(k, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
 int mxmoe_ep_dispatch_rows(const mxmoe_ep_dispatch_args* a, const mxmoe_token_quant_args* stores, void* stream) {
   if (!a) return fail(MXMOE_ERR_INVALID, "null args");
   mxb::TokenQuantArgs t;

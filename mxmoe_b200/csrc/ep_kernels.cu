@@ -62,6 +62,55 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
   }
 }
 
+// One block.  Epoch e of the barrier: publish the payload into every peer, fence, write e into flag `rank` of every
+// peer, then wait until all of this rank's flags show e.  The wait is bounded: when it runs out the error word of
+// the local sync block is set and the kernel returns (the host reads the word; later kernels run on whatever
+// arrived).  The ranks run on different GPUs, one process each, so the waiting kernels never share a GPU.
+constexpr int kSyncFlags = 64, kSyncErr = 64, kSyncEpoch = 65, kSyncPayload0 = 128;
+
+__device__ __forceinline__ uint64_t ep_globaltimer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(256) ep_sync_kernel(EpSyncArgs a) {
+  const int tid = threadIdx.x;
+  __shared__ int s_epoch;
+  if (tid == 0) s_epoch = a.local_sync[kSyncEpoch] + 1;
+  __syncthreads();
+  const int epoch = s_epoch;
+  if (a.payload && a.payload_len > 0) {
+    for (int i = tid; i < a.world * a.payload_len; i += blockDim.x) {
+      const int d = i / a.payload_len, j = i - d * a.payload_len;
+      int* dst = reinterpret_cast<int*>(a.peer_sync[d]) + kSyncPayload0 + a.rank * a.payload_cap + j;
+      *dst = a.payload[j];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < a.world) {
+    volatile int* flag = reinterpret_cast<int*>(a.peer_sync[tid]) + a.rank;
+    *flag = epoch;
+  }
+  if (tid < a.world) {
+    volatile int* mine = a.local_sync + tid;
+    const uint64_t limit = (a.timeout_ms > 0 ? (uint64_t)a.timeout_ms : 2000ull) * 1000000ull;
+    const uint64_t t0 = ep_globaltimer();
+    unsigned spins = 0;
+    // signed distance: a peer that is already one barrier ahead has written a larger epoch
+    while (*mine - epoch < 0) {
+      if ((++spins & 255u) == 0 && ep_globaltimer() - t0 > limit) {
+        atomicExch(a.local_sync + kSyncErr, 1 + tid);      // 1 + the rank that did not arrive
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) a.local_sync[kSyncEpoch] = epoch;
+}
+
 // block = segment: expert of every received row (the second quantiser picks its format by expert)
 __global__ void ep_fill_row_expert_kernel(EpPlanArgs a) {
   const int lo = a.range_lo[a.rank], el = a.range_lo[a.rank + 1] - lo;
@@ -93,6 +142,11 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs d, Toke
 }
 
 }  // namespace
+
+cudaError_t launch_ep_sync(const EpSyncArgs& a, cudaStream_t stream) {
+  ep_sync_kernel<<<1, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_ep_plan(const EpPlanArgs& a, cudaStream_t stream) {
   ep_plan_kernel<<<1, kPlanThreads, 0, stream>>>(a);

@@ -37,6 +37,21 @@ struct EpDispatchArgs {
   int pad_;
 };
 
+// Barrier between the ranks of an expert-parallel group that lives on the stream: every rank's kernels launched
+// before it (their stores to peer memory included) have completed before any rank's kernels launched after it
+// start.  Optionally carries a small payload (this rank's per-expert row counts) to every peer first, which makes it
+// the all-gather of the counts as well.  All buffers are peer-mapped (symmetric) int32 memory.
+struct EpSyncArgs {
+  const uint64_t* peer_sync;   // [world] device array: address of every rank's sync block as mapped here
+  int* local_sync;             // this rank's sync block: [0, 64) arrival flags by rank, [64] error word, [65] epoch,
+                               // [128, 128 + world * payload_cap) payload slots by rank
+  const int* payload;          // optional: payload_len int32 this rank publishes into slot `rank` of every peer
+  int world, rank, payload_len, payload_cap;
+  int timeout_ms;              // limit of the wait for the peers' flags; 0 = 2000 ms
+  int pad_;
+};
+
+cudaError_t launch_ep_sync(const EpSyncArgs& a, cudaStream_t stream);
 cudaError_t launch_ep_plan(const EpPlanArgs& a, cudaStream_t stream);
 cudaError_t launch_ep_dispatch(const EpDispatchArgs& d, const TokenQuantArgs& t, cudaStream_t stream);
 

@@ -7,16 +7,20 @@ Two transports move the rows:
 
     route_topk (global expert ids)  ->  rows sorted by expert = grouped by destination rank
     quant_tokens                    ->  token-major quantised stores
-    all_gather(counts)              ->  every rank knows every split size, on the device
+    ep_sync(counts)                 ->  every rank's counts written into every peer + flag barrier: every rank knows
+                                        every split size, on the device, without a library collective
     ep_plan (device)                ->  receive-side segment tables, send-side row offsets
     ep_dispatch_rows                ->  packed row + scale written straight into the owner's receive store
                                         (plain stores to peer memory over NVLink)
-    barrier                         ->  a one-element all-reduce, stream ordered
+    ep_sync                         ->  flag barrier in peer-mapped memory, stream ordered, bounded wait
     grouped GEMM, silu*mul+quantise, grouped GEMM
                                     ->  one problem per (source rank, local expert); the epilogue of the down
                                         projection stores every segment straight into the buffer of the rank its
                                         rows came from, at their place in that rank's order (peer stores again)
-    barrier, combine_topk (+ shared expert, computed locally on the rank's own tokens)
+    ep_sync, combine_topk (+ shared expert, computed locally on the rank's own tokens)
+
+The p2p step contains no NCCL call and never returns to the host, so it is replayed from a CUDA graph
+(``forward_graph``).
 
 ``nccl`` - ``all_to_all_single`` for both exchanges; NCCL needs the split sizes on the host, which costs one
 device->host copy and a stream synchronisation per step.
@@ -219,7 +223,14 @@ class EPMoELayer:
             self.peer_recv = torch.tensor([int(p) for p in self._h_recv.buffer_ptrs], dtype=torch.int64, device=dev)
             self.peer_ret = [int(p) for p in self._h_ret.buffer_ptrs]
             self.send = None
-            self._bar = torch.zeros(1, dtype=torch.float32, device=dev)
+            # sync block: arrival flags, error word, epoch, and one payload slot per rank that receives the ranks'
+            # per-expert row counts (see mxmoe_ep_sync)
+            self.sync = symm.empty((128 + self.world * E,), dtype=torch.int32, device=dev)
+            self.sync.zero_()
+            self._h_sync = symm.rendezvous(self.sync, grp)
+            self.peer_sync = torch.tensor([int(p) for p in self._h_sync.buffer_ptrs], dtype=torch.int64, device=dev)
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=group)        # every rank's sync block is zeroed before anybody's first barrier
         else:
             self.send = torch.zeros(self.R_send, self.rec, **f16)
             self.recv = torch.zeros(self.R_recv, self.rec, **f16)
@@ -231,7 +242,8 @@ class EPMoELayer:
         self.seg_tab_host = torch.zeros(2, max(nseg, 1), dtype=torch.int32).pin_memory()
         self.seg_expert_dev = torch.tensor(self.seg_expert or [0], **i32)
         self.recv_row_expert = torch.zeros(self.R_recv, **i32)
-        self.counts_all = torch.zeros(self.world * E, **i32)
+        # all ranks' per-expert row counts: the payload slots of the sync block (p2p) or an all-gather buffer (nccl)
+        self.counts_all = self.sync[128:] if self.transport == "p2p" else torch.zeros(self.world * E, **i32)
         self.counts_host = torch.zeros(self.world, E, dtype=torch.int32).pin_memory()
         self.ids_new = torch.zeros(T, k, **i32)
         # device-side plan of the p2p transport
@@ -280,10 +292,17 @@ class EPMoELayer:
         virt = torch.index_select(self.vbase, 0, flat) + torch.remainder(self.slot_token, torch.index_select(self.vrep, 0, flat))
         torch.index_select(self.remap, 0, virt, out=self.ids_new.view(-1))
 
-    def _barrier(self):
+    def _sync(self, payload: torch.Tensor | None = None):
         """Every rank's earlier kernels on this stream (their peer stores included) are complete before any
-        rank's later kernels start: a one-element all-reduce, ordered on the stream, no host involvement."""
-        dist.all_reduce(self._bar, group=self.group)
+        rank's later kernels start: flags in peer-mapped memory, ordered on the stream, no host involvement and
+        no library collective.  ``payload``: this rank's per-expert counts, delivered to every rank on the way."""
+        a = _lib.EpSyncArgs()
+        a.peer_sync, a.local_sync = self.peer_sync.data_ptr(), self.sync.data_ptr()
+        a.payload = None if payload is None else payload.data_ptr()
+        a.world, a.rank = self.world, self.rank
+        a.payload_len, a.payload_cap = (0 if payload is None else payload.numel()), self.E
+        a.timeout_ms = 0
+        _lib.check(_lib.lib().mxmoe_ep_sync(C.byref(a), current_stream_ptr()))
 
     def _forward_p2p(self, hidden, topk_ids, topk_weights):
         spec, f = self.spec, self.front
@@ -298,7 +317,7 @@ class EPMoELayer:
             f.route(self.ids_new)
             t = self.tq.run(hidden)
             self._mark(marks, "route+quant")
-            dist.all_gather_into_tensor(self.counts_all, f.counts, group=self.group)
+            self._sync(payload=f.counts)
             lo, hi = self.ranges[self.rank]
             pa = _lib.EpPlanArgs()
             pa.counts_all, pa.range_lo = self.counts_all.data_ptr(), self.range_lo.data_ptr()
@@ -315,11 +334,11 @@ class EPMoELayer:
             da.rows, da.k, da.rec_bytes, da.scale_off_bytes, da.recv_capacity = T * k, H, self.rec * 2, self.P * 2, self.R_recv
             _lib.check(lib.mxmoe_ep_dispatch_rows(C.byref(da), C.byref(t), current_stream_ptr()))
             self._mark(marks, "plan+dispatch")
-            self._barrier()
+            self._sync()
             self._mark(marks, "barrier")
             self._core.run(self.R_recv)
             self._mark(marks, "experts")
-            self._barrier()
+            self._sync()
             self._mark(marks, "barrier2")
             _lib.check(lib.mxmoe_combine_topk(
                 self.ret.data_ptr(), f.slot_row.data_ptr(),
@@ -386,9 +405,34 @@ class EPMoELayer:
                     self.phase_ms.setdefault(name, []).append(a.elapsed_time(b))
         return self.out
 
+    def forward_graph(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor | None = None):
+        """Same as :meth:`forward` with the ``p2p`` transport, replayed from a CUDA graph: the step never returns to
+        the host (its two collectives, the all-gather of the counts and the barriers, are stream-ordered and are
+        captured with the kernels), so its ~20 launches become one.  Captured once per set of argument buffers."""
+        if self.transport != "p2p":
+            return self.forward(hidden, topk_ids, topk_weights)
+        key = (hidden.data_ptr(), topk_ids.data_ptr(), None if topk_weights is None else topk_weights.data_ptr())
+        if getattr(self, "_graph_key", None) != key:
+            with torch.cuda.device(self.device):
+                profile, self.profile = self.profile, False
+                for _ in range(2):
+                    self.forward(hidden, topk_ids, topk_weights)        # builds descriptors, warms up the collectives
+                self.check()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.forward(hidden, topk_ids, topk_weights)
+                self._graph, self._graph_key, self.profile = g, key, profile
+        self._graph.replay()
+        return self.out
+
     def check(self) -> None:
         self._core.check()
         if self.transport == "p2p":
+            missing = int(self.sync[64].item())
+            if missing:
+                self.sync[64].zero_()
+                raise RuntimeError(f"rank {self.rank}: a barrier gave up waiting for rank {missing - 1}")
             wanted = int(self.total_recv[1].item())
             if wanted:
                 # the report is taken: clear it, so that later steps that fit are not blamed for this one.  The rows
