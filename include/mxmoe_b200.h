@@ -145,8 +145,8 @@ int mxmoe_gg_check(void* workspace, void* stream);
 
 /* Test hook for the bounded waits of the kernel with swapped operands (no counterpart in the reference, whose
  * kernels cannot time out).  `timeout_ms` > 0 replaces the 1000 ms limit of every device-side wait of later
- * launches over `workspace`; `skip_stage` >= 0 makes the producer of CTA 0 leave out the weight load of that
- * pipeline stage (counted from the start of its work), so that the wait for it runs out: the launch then ends
+ * launches over `workspace`; `skip_stage` >= 0 makes the producer of CTA 0 announce more weight bytes than it
+ * loads for that pipeline stage (counted from the start of its work), so that the wait for them runs out: the launch then ends
  * by itself and mxmoe_gg_check reports MXMOE_ERR_DEVICE with the role and the tile.  (0, -1) restores the
  * defaults.  Synchronises `stream`. */
 int mxmoe_gg_debug(void* workspace, int timeout_ms, int skip_stage, void* stream);

@@ -82,8 +82,8 @@ struct alignas(256) GGStatus {
   unsigned long long prof[16];
   int prof_on;      // per-role cycle counters wanted (costs a few percent)
   int timeout_ms;   // limit of every bounded wait of the kernel with swapped operands; 0 = 1000 ms
-  int skip_stage;   // test hook: 1 + the pipeline stage (counted from the start of CTA 0's work) whose weight
-                    // load CTA 0's producer leaves out, so that the wait for it runs out; 0 = none
+  int skip_stage;   // test hook: 1 + the pipeline stage (counted from the start of CTA 0's work) for which CTA 0's
+                    // producer announces more weight bytes than it loads, so that the wait for them runs out; 0 = none
   int pad[25];
 };
 
