@@ -143,7 +143,13 @@ __device__ __forceinline__ void report_s(GGStatus* status, int role, int tile) {
 __device__ __forceinline__ bool is_int_scheme(int s) { return s != SCH_FP16 && s != SCH_W4A16G128; }
 __device__ __forceinline__ bool is_cvt_scheme(int s) { return s == SCH_W4A4_XA || s == SCH_W4A16G128 || s == SCH_W4A4; }
 
+// Per-role cycle counters (mxmoe_gg_profile) are compiled in with -DMXMOE_PROF only: every tick is a branch inside
+// the per-stage loops of the producer and of the MMA warp, which are on the critical path of the ring.
+#ifdef MXMOE_PROF
 __device__ __forceinline__ long long tick(bool on) { return on ? clock64() : 0ll; }
+#else
+__device__ __forceinline__ long long tick(bool) { return 0ll; }
+#endif
 
 // bytes per stage of a weight tile and its coordinates (x step per K block, y) in the weight tensor map
 __device__ __forceinline__ void weight_coords(int scheme, int w_row, uint32_t& wbytes, int& wx_step, int& wy) {
@@ -323,7 +329,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      long long w_prod = 0, n_stage = 0, n_tile = 0;
+      long long w_prod = 0;
+      int n_stage = 0, n_tile = 0;
+      const uint32_t empty0 = smem_u32(&ctrl->empty[0]), wfull0 = smem_u32(&ctrl->wfull[0]), xfull0 = smem_u32(&ctrl->xfull[0]);
       TileRec nrec = tile_rec(0);
       for (int i = 0; ok && i < my_tiles; ++i) {
         const int t    = blockIdx.x + i * gridDim.x;
@@ -344,45 +352,57 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         int wx_step, wy;
         weight_coords(ti.scheme, w_row, wbytes, wx_step, wy);
         const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;   // (packed int4: see below)
-        for (int kb = 0; kb < ti.nkb; ++kb) {
-          const long long c0 = tick(prof_on);
-          const bool got = wait_bar(smem_u32(&ctrl->empty[stage]), phase ^ 1u, abort_flag, 0, tmo);
-          w_prod += tick(prof_on) - c0;
-          TRACE(TR_PROD_GOT, (int)n_stage);
-          ++n_stage;
-          if (!got) {
-            report_s(status, 1, t);
-            ok = false;
-            break;
-          }
-          const uint32_t wbar = smem_u32(&ctrl->wfull[stage]);
-          const uint32_t bar  = smem_u32(&ctrl->xfull[stage]);
-          if (kMode == 2 && ti.scheme == SCH_W4A4) {
-            // packed activation rows (64 bytes of K each) go behind the packed weights; the converters expand them
-            mbar_expect_tx(wbar, wbytes + xbytes);
-            tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
-            for (int b = 0; b < nbox; ++b)
-              tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, wbar, kb * 64, x_row + b * kXBoxSmall);
-            mbar_arrive(bar);                     // no activation tile of its own: complete the phase
-            TRACE(TR_PROD_ISSUED, (int)n_stage - 1);
+        // this tile's K block for which the test hook (GGStatus::skip_stage) announces more weight bytes than will
+        // arrive.  A select, not a branch: one more branch per stage in these loops cost the w4a4 layer 3.5 %, and the
+        // per-role cycle counters (two more) another 3.5 %; a second producer thread for the activation tiles was
+        // measured too and is no faster than one lean loop.
+        const int skip_kb = (skip_stage >= n_stage && skip_stage < n_stage + ti.nkb) ? skip_stage - n_stage : -1;
+        const bool packed_x = kMode == 2 && ti.scheme == SCH_W4A4;
+        if (big && !packed_x) {
+          // the common case (a full token tile), straight-line: wait, announce, two loads
+          for (int kb = 0; kb < ti.nkb; ++kb) {
+            const long long c0 = tick(prof_on);
+            const bool got = wait_bar(empty0 + 8 * stage, phase ^ 1u, abort_flag, 0, tmo);
+            w_prod += tick(prof_on) - c0;
+            TRACE(TR_PROD_GOT, n_stage + kb);
+            if (!got) { report_s(status, 1, t); ok = false; break; }
+            mbar_expect_tx(wfull0 + 8 * stage, wbytes + (kb == skip_kb ? 16u : 0u));
+            tma_load_2d(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy);
+            mbar_expect_tx(xfull0 + 8 * stage, xbytes);
+            tma_load_2d(xslot(stage), &pr->tmX, xfull0 + 8 * stage, kb * xx_step, x_row);
+            TRACE(TR_PROD_ISSUED, n_stage + kb);
             if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
-            continue;
           }
-          // (test hook, GGStatus::skip_stage: more weight bytes announced than will arrive - a select, not a branch:
-          // one more branch per stage in this loop cost the w4a4 layer 3.5 %; a second producer thread for the
-          // activation tiles was measured too and is no faster than this one)
-          mbar_expect_tx(wbar, wbytes + ((int)n_stage - 1 == skip_stage ? 16u : 0u));
-          tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
-          mbar_expect_tx(bar, xbytes);
-          if (big) {
-            tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
-          } else {
-            for (int b = 0; b < nbox; ++b)
-              tma_load_2d(xslot(stage) + b * kXBoxSmall * kRowBytes, &pr->tmXs, bar, kb * xx_step, x_row + b * kXBoxSmall);
+        } else {
+          for (int kb = 0; kb < ti.nkb; ++kb) {
+            const long long c0 = tick(prof_on);
+            const bool got = wait_bar(empty0 + 8 * stage, phase ^ 1u, abort_flag, 0, tmo);
+            w_prod += tick(prof_on) - c0;
+            if (!got) { report_s(status, 1, t); ok = false; break; }
+            const uint32_t wbar = wfull0 + 8 * stage;
+            const uint32_t bar  = xfull0 + 8 * stage;
+            if (packed_x) {
+              // packed activation rows (64 bytes of K each) go behind the packed weights; the converters expand them
+              mbar_expect_tx(wbar, wbytes + xbytes);
+              tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+              for (int b = 0; b < nbox; ++b)
+                tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, wbar, kb * 64, x_row + b * kXBoxSmall);
+              mbar_arrive(bar);                     // no activation tile of its own: complete the phase
+            } else {
+              mbar_expect_tx(wbar, wbytes + (kb == skip_kb ? 16u : 0u));
+              tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+              mbar_expect_tx(bar, xbytes);
+              if (big) {
+                tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
+              } else {
+                for (int b = 0; b < nbox; ++b)
+                  tma_load_2d(xslot(stage) + b * kXBoxSmall * kRowBytes, &pr->tmXs, bar, kb * xx_step, x_row + b * kXBoxSmall);
+              }
+            }
+            if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
           }
-          TRACE(TR_PROD_ISSUED, (int)n_stage - 1);
-          if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
         }
+        n_stage += ti.nkb;
       }
       if (blockIdx.x == 0) {
         status->prof[PROF_PROD_WAIT] = w_prod;
