@@ -202,59 +202,90 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
 
 }  // namespace
 
+// One pipeline stage = four MMAs (32 bytes of K each) and the commit that releases the stage, as ONE block of
+// straight-line PTX: the issuing warp shares its scheduler with an epilogue warp and converter warps of the same
+// TMEM lane quarter, so every instruction it does not need (a predicate set-up per MMA, descriptor arithmetic
+// recomputed per stage) delays the issue of the next stage.  `first` == 0: the first MMA overwrites D.
+//   kV 0 int8 / weights from shared memory, 1 fp16 / shared memory, 2 int8 / tensor memory, 3 fp16 / tensor memory.
+#define MXB_MMA_STAGE_SS(KIND)                                                                              \
+  asm volatile(                                                                                             \
+      "{\n\t"                                                                                               \
+      ".reg .pred p, t;\n\t"                                                                                \
+      ".reg .b64 w0, w1, w2, w3, x0, x1, x2, x3;\n\t"                                                       \
+      ".reg .b32 a1, a2, a3, b1, b2, b3;\n\t"                                                               \
+      "setp.ne.b32 p, %5, 0;\n\t"                                                                           \
+      "setp.eq.b32 t, 0, 0;\n\t"                                                                            \
+      "add.u32 a1, %1, 2;  add.u32 a2, %1, 4;  add.u32 a3, %1, 6;\n\t"                                      \
+      "add.u32 b1, %2, 2;  add.u32 b2, %2, 4;  add.u32 b3, %2, 6;\n\t"                                      \
+      "mov.b64 w0, {%1, %3}; mov.b64 w1, {a1, %3}; mov.b64 w2, {a2, %3}; mov.b64 w3, {a3, %3};\n\t"         \
+      "mov.b64 x0, {%2, %3}; mov.b64 x1, {b1, %3}; mov.b64 x2, {b2, %3}; mov.b64 x3, {b3, %3};\n\t"         \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], w0, x0, %4, p;\n\t"                                    \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], w1, x1, %4, t;\n\t"                                    \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], w2, x2, %4, t;\n\t"                                    \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], w3, x3, %4, t;\n\t"                                    \
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"                     \
+      "}"                                                                                                   \
+      :                                                                                                     \
+      : "r"(d_tmem), "r"(wlo), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar)               \
+      : "memory")
+#define MXB_MMA_STAGE_TS(KIND)                                                                              \
+  asm volatile(                                                                                             \
+      "{\n\t"                                                                                               \
+      ".reg .pred p, t;\n\t"                                                                                \
+      ".reg .b64 x0, x1, x2, x3;\n\t"                                                                       \
+      ".reg .b32 a1, a2, a3, b1, b2, b3;\n\t"                                                               \
+      "setp.ne.b32 p, %5, 0;\n\t"                                                                           \
+      "setp.eq.b32 t, 0, 0;\n\t"                                                                            \
+      "add.u32 a1, %1, 8;  add.u32 a2, %1, 16;  add.u32 a3, %1, 24;\n\t"                                    \
+      "add.u32 b1, %2, 2;  add.u32 b2, %2, 4;  add.u32 b3, %2, 6;\n\t"                                      \
+      "mov.b64 x0, {%2, %3}; mov.b64 x1, {b1, %3}; mov.b64 x2, {b2, %3}; mov.b64 x3, {b3, %3};\n\t"         \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [%1], x0, %4, p;\n\t"                                  \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [a1], x1, %4, t;\n\t"                                  \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [a2], x2, %4, t;\n\t"                                  \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [a3], x3, %4, t;\n\t"                                  \
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"                     \
+      "}"                                                                                                   \
+      :                                                                                                     \
+      : "r"(d_tmem), "r"(a_tmem), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar)            \
+      : "memory")
+
+template <int kV>
+__device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t wlo, uint32_t a_tmem, uint32_t xlo, uint32_t desc_hi,
+                                          uint32_t idesc, uint32_t first, uint32_t empty_bar) {
+  if (kV == 0)      { MXB_MMA_STAGE_SS("i8"); }
+  else if (kV == 1) { MXB_MMA_STAGE_SS("f16"); }
+  else if (kV == 2) { MXB_MMA_STAGE_TS("i8"); }
+  else              { MXB_MMA_STAGE_TS("f16"); }
+}
+
 // The MMA warp's main loop over the K blocks of one tile, specialised on the operand kind and on where
-// the weights come from (kV: 0 int8 / shared memory, 1 fp16 / shared memory, 2 int8 / tensor memory, 3 fp16 /
-// tensor memory) so that the issue sequence of a stage is straight-line code: a branch per MMA made the
+// the weights come from so that the issue sequence of a stage is straight-line code: a branch per MMA made the
 // issue of every MMA several times slower.  All lanes walk the loop and meet the named barrier of each
 // stage; the elected lane issues.  One MMA consumes 32 bytes of K per row: 8 TMEM columns of A or 32 bytes of a
-// shared-memory row.
+// shared-memory row.  The per-stage addresses (descriptor low words, A slot, barrier) are carried in registers and
+// advanced by their strides.
+struct MmaCursor {
+  int stage;
+  uint32_t wlo, xlo, a_tmem, ebar;
+};
 template <int kV, typename G, int kBarThreads>
-__device__ __forceinline__ void mma_tile_loop(int nkb, int& stage, int lane, uint32_t d_tmem, uint32_t idesc,
-                                              uint32_t ring_base, uint32_t a_tmem0, uint32_t empty0, bool prof_on,
-                                              long long& w_oper, long long& w_issue, int& sidx) {
+__device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCursor& c0, int lane, uint32_t d_tmem,
+                                              uint32_t idesc, uint32_t desc_hi, int& sidx) {
   for (int kb = 0; kb < nkb; ++kb) {
-    const long long c0 = tick(prof_on);
-    nbar_sync(G::kBarStage0 + stage, kBarThreads);   // operands of this stage are in place
+    nbar_sync(G::kBarStage0 + c.stage, kBarThreads);   // operands of this stage are in place
     if (lane == 0) TRACE(TR_MMA_GOT, sidx);
-    const long long c1 = tick(prof_on);
-    w_oper += c1 - c0;
     if (elect_one_sync()) {
       tc_fence_after_sync();
-      const uint32_t wslot   = ring_base + stage * G::kStageBytes;
-      const uint64_t xdesc   = smem_desc_sw128(wslot + kWSlotBytes);
-      const uint32_t accum0  = kb > 0 ? 1u : 0u;
-      if (kV == 0) {
-        const uint64_t wdesc = smem_desc_sw128(wslot);
-        mma_i8_ss(d_tmem, wdesc, xdesc, idesc, accum0);
-        mma_i8_ss(d_tmem, wdesc + 2, xdesc + 2, idesc, 1u);
-        mma_i8_ss(d_tmem, wdesc + 4, xdesc + 4, idesc, 1u);
-        mma_i8_ss(d_tmem, wdesc + 6, xdesc + 6, idesc, 1u);
-      } else if (kV == 1) {
-        const uint64_t wdesc = smem_desc_sw128(wslot);
-        mma_f16_ss(d_tmem, wdesc, xdesc, idesc, accum0);
-        mma_f16_ss(d_tmem, wdesc + 2, xdesc + 2, idesc, 1u);
-        mma_f16_ss(d_tmem, wdesc + 4, xdesc + 4, idesc, 1u);
-        mma_f16_ss(d_tmem, wdesc + 6, xdesc + 6, idesc, 1u);
-      } else if (kV == 2) {
-        const uint32_t a_tmem = a_tmem0 + stage * kASlotCols;   // A slot = ring stage
-        mma_i8_ts(d_tmem, a_tmem, xdesc, idesc, accum0);
-        mma_i8_ts(d_tmem, a_tmem + 8, xdesc + 2, idesc, 1u);
-        mma_i8_ts(d_tmem, a_tmem + 16, xdesc + 4, idesc, 1u);
-        mma_i8_ts(d_tmem, a_tmem + 24, xdesc + 6, idesc, 1u);
-      } else {
-        const uint32_t a_tmem = a_tmem0 + stage * kASlotCols;
-        mma_f16_ts(d_tmem, a_tmem, xdesc, idesc, accum0);
-        mma_f16_ts(d_tmem, a_tmem + 8, xdesc + 2, idesc, 1u);
-        mma_f16_ts(d_tmem, a_tmem + 16, xdesc + 4, idesc, 1u);
-        mma_f16_ts(d_tmem, a_tmem + 24, xdesc + 6, idesc, 1u);
-      }
-      mma_commit(empty0 + 8 * stage);
+      mma_stage<kV>(d_tmem, c.wlo, c.a_tmem, c.xlo, desc_hi, idesc, kb > 0 ? 1u : 0u, c.ebar);
     }
     __syncwarp();
     if (lane == 0) TRACE(TR_MMA_ISSUED, sidx);
     ++sidx;
-    w_issue += tick(prof_on) - c1;
-    if (++stage == G::kStages) stage = 0;
+    if (++c.stage == G::kStages) {
+      c = c0;
+    } else {
+      c.wlo += G::kStageBytes >> 4; c.xlo += G::kStageBytes >> 4; c.a_tmem += kASlotCols; c.ebar += 8;
+    }
   }
 }
 
@@ -412,10 +443,20 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     }
   } else if (warp == 1) {
     // ===== MMA issuer (all lanes walk the loop and meet the named barriers, the elected lane issues) =====
-    int stage = 0;
     int acc = 0;
     long long w_oper = 0, w_acc = 0, w_issue = 0;
     int sidx = 0;   // stages issued so far (timeline tracing only)
+    // stage 0: low words of the two shared-memory descriptors (the high word is the same for every tile of the
+    // ring: 128-byte swizzle, 1024 bytes between 8-row groups), first A slot, first "stage may be refilled" barrier
+    const uint64_t desc0 = smem_desc_sw128(smem_base);
+    const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+    MmaCursor cur0;
+    cur0.stage  = 0;
+    cur0.wlo    = (uint32_t)desc0;
+    cur0.xlo    = (uint32_t)smem_desc_sw128(smem_base + kWSlotBytes);
+    cur0.a_tmem = tmem_base + G::kASlotCol0;
+    cur0.ebar   = smem_u32(&ctrl->empty[0]);
+    MmaCursor cur = cur0;
     TileRec nrec = tile_rec(0);
     for (int i = 0; i < my_tiles; ++i) {
       const TileS ti = decode_rec(nrec);
@@ -429,12 +470,10 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const bool from_tmem  = kCvt && is_cvt_scheme(ti.scheme);
       const uint32_t idesc  = is_int ? idesc_i8(kWT, npad) : idesc_f16(kWT, npad);
       const int variant     = (from_tmem ? 2 : 0) + (is_int ? 0 : 1);
-      const uint32_t a_tmem0 = tmem_base + G::kASlotCol0;
-      const uint32_t empty0  = smem_u32(&ctrl->empty[0]);
-      if (variant == 0)      mma_tile_loop<0, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
-      else if (variant == 1) mma_tile_loop<1, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
-      else if (variant == 2) mma_tile_loop<2, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
-      else                   mma_tile_loop<3, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, stage, lane, d_tmem, idesc, smem_base, a_tmem0, empty0, prof_on, w_oper, w_issue, sidx);
+      if (variant == 0)      mma_tile_loop<0, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else if (variant == 1) mma_tile_loop<1, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else if (variant == 2) mma_tile_loop<2, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else                   mma_tile_loop<3, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
       if (elect_one_sync()) mma_commit(smem_u32(&ctrl->tfull[acc]));
       __syncwarp();
       acc ^= 1;
