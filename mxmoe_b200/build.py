@@ -54,5 +54,35 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+OPS_LIB = os.path.join(HERE, "mxmoe_ops.so")
+
+
+def build_torch_ext(force: bool = False) -> str:
+    """Compile ``mxmoe_b200/mxmoe_ops.so``, the torch C++ extension with the reference's operator names
+    (csrc/torch_ops.cpp), against the torch this interpreter imports and link it to ``libmxmoe_b200.so``."""
+    src = os.path.join(CSRC, "torch_ops.cpp")
+    if not force and os.path.exists(OPS_LIB) and os.path.getmtime(OPS_LIB) > max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        return OPS_LIB
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    inc = [f"-I{d}" for d in ce.include_paths()] + [f"-I{sysconfig.get_paths()['include']}"]
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = (["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-DTORCH_EXTENSION_NAME=mxmoe_ops",
+            f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+           + inc + [f"-I{cuda_inc}", src, "-o", OPS_LIB + ".tmp", f"-L{HERE}", "-l:libmxmoe_b200.so",
+                    f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10", "-lc10_cuda", "-ltorch_cuda",
+                    "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"])
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr[-6000:])
+        raise RuntimeError("building mxmoe_ops.so failed (see stderr)")
+    os.replace(OPS_LIB + ".tmp", OPS_LIB)
+    return OPS_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--ops" in sys.argv:
+        print(build_torch_ext(force="--force" in sys.argv))

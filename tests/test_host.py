@@ -192,3 +192,13 @@ def test_verify_decodes_the_stored_layouts():
             assert torch.equal(vals, (pw.codes.double() * s + z).half())
         else:
             assert torch.equal(vals, pw.codes.double())
+
+
+def test_torch_extension_exposes_the_reference_operator_names():
+    """mxmoe_ops.so (torch C++ extension over the C ABI) loads without a GPU and has the five functions of the
+    reference's pybind module (ref_bind.cu:759-768)."""
+    mxmoe_ops = pytest.importorskip("mxmoe_b200.mxmoe_ops")
+    for name in ("gg_cutlass", "gg_cutlass_share_fused", "gg_mxmoe_share_fused", "quant_inp_act", "silu_mul_then_quant"):
+        assert callable(getattr(mxmoe_ops, name))
+    with pytest.raises(RuntimeError):                      # TORCH_CHECK -> Python exception, as in the reference
+        mxmoe_ops.gg_mxmoe_share_fused([], [], [], [], [], 1, 1, 0, 0, [], torch.zeros(1, dtype=torch.int64), False)
