@@ -25,15 +25,23 @@ import os
 import sys
 
 
+# Twins of the reference's dataclasses (tile_config.py:117-207) with the same class names, field names, field order
+# and defaults, so that ``repr`` gives the very string the solver uses as a key.
 @dataclasses.dataclass
 class NO_QUANT:
-    pass
+    T_PACK: str = "half"
+    QBITS: int = 16
+    GSIZE: int = -1
+    SYM: bool = True
+    PACK_DIM: str = "PackDim::K"
+    USE_FP: bool = False
+    T_SCALE: str = "half"
 
 
 @dataclasses.dataclass
 class QConfig:
     T_PACK: str = "half"
-    QBITS: int = 4
+    QBITS: int = 16
     GSIZE: int = -1
     SYM: bool = True
     PACK_DIM: str = "PackDim::K"
@@ -70,6 +78,13 @@ def b200_tile(scheme: str) -> TileConfig:
                       QCFGB=QConfig(QBITS=w, GSIZE=g, SYM=sym, PACK_DIM="PackDim::MN"))
 
 
+def get_best_tile_configs(batch_range: int, strategy_list: list[str]) -> dict:
+    """B200 counterpart of the solver's hard-coded shortlist (bits_solver.py:425-515): the candidate tiles per scheme
+    for a batch range.  The sm_100a kernel has one tile per scheme whatever the batch (its token tile adapts to the
+    rows an expert has: up to 176, in steps of 16), so every batch range maps to the same single candidate."""
+    return {s: [b200_tile(s)] for s in strategy_list}
+
+
 def subkey(scheme: str) -> str:
     return "1" if "a16" in scheme or scheme == "fp16" else "3"
 
@@ -88,11 +103,11 @@ def _fit(tiles, ms):
 def profile(schemes=None, shapes=((2816, 2048), (2048, 1408)), iters: int = 20) -> dict:
     import torch
     from . import gg, _lib
-    from .weights import parse_scheme, SCHEMES
+    from .weights import parse_scheme, SCHEMES, EXTRA_SCHEMES
     dev = torch.device("cuda", torch.cuda.current_device())
     sms = _lib.lib().mxmoe_device_sm_count()
     table = {}
-    for scheme in (schemes or SCHEMES):
+    for scheme in (schemes or SCHEMES + EXTRA_SCHEMES):
         a_bits, w_bits, g, sym = parse_scheme(scheme)
         entry = {"inc_by_nk": {}}
         for (N, K) in shapes:

@@ -86,6 +86,23 @@ def golden_hadamard_kron():
     np.savez_compressed(os.path.join(HERE, "hadamard_kron.npz"), **out)
 
 
+def golden_tile_repr():
+    """``repr`` of the reference's TileConfig dataclass (mxmoe/kernels/tile_config.py:195-207) - the key of
+    perf/performance_table.json that bits_solver.py:541 looks up - for the tile numbers of the B200 kernel, with the
+    quantisation descriptors the solver attaches (``set_qcfg(QCFG_MAP[scheme])``, bits_solver.py:519)."""
+    import json
+    from mxmoe.kernels.tile_config import QCFG_MAP, TileConfig
+    sys.path.insert(0, ROOT)
+    from mxmoe_b200 import perf_table
+    out = {}
+    for scheme in ("fp16", "w8a8_g-1_sym", "w4a4_g-1_sym", "w4a16_g128_asym", "w4a16_g-1_asym"):
+        t = perf_table.b200_tile(scheme)
+        ref = TileConfig(BM=t.BM, BN=t.BN, BK=t.BK, WM=t.WM, WN=t.WN, WK=t.WK, STAGE=t.STAGE, SPLITK=t.SPLITK, MMA=t.MMA)
+        out[scheme] = repr(ref.set_qcfg(QCFG_MAP[scheme]))
+    with open(os.path.join(HERE, "tile_repr.json"), "w") as f:
+        json.dump(out, f, indent=1)
+
+
 def golden_pack():
     rng = np.random.default_rng(13)
     out = {}
@@ -152,6 +169,7 @@ if __name__ == "__main__":
     golden_quant()
     golden_hadamard()
     golden_hadamard_kron()
+    golden_tile_repr()
     golden_pack()
     golden_layer()
     for f in sorted(os.listdir(HERE)):

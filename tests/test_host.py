@@ -152,7 +152,12 @@ def test_perf_table_schema_matches_the_solver_input():
     from mxmoe_b200 import perf_table
     path = os.path.join(ROOT, "mxmoe_b200", "perf", "performance_table.json")
     table = json.load(open(path))
-    assert set(table) == set(weights.SCHEMES)
+    assert set(table) == set(weights.SCHEMES + weights.EXTRA_SCHEMES)
+    # the key is the very string the reference's TileConfig.__repr__ gives (golden made from the reference's dataclass)
+    golden = json.load(open(os.path.join(ROOT, "tests", "golden", "tile_repr.json")))
+    for scheme in table:
+        assert repr(perf_table.b200_tile(scheme)) == golden[scheme]
+    assert perf_table.get_best_tile_configs(8192, ["fp16", "w4a4_g-1_sym"])["w4a4_g-1_sym"] == [perf_table.b200_tile("w4a4_g-1_sym")]
     for scheme, by_key in table.items():
         sk = "1" if ("a16" in scheme or scheme == "fp16") else "3"
         assert list(by_key) == [sk]
@@ -202,3 +207,24 @@ def test_torch_extension_exposes_the_reference_operator_names():
         assert callable(getattr(mxmoe_ops, name))
     with pytest.raises(RuntimeError):                      # TORCH_CHECK -> Python exception, as in the reference
         mxmoe_ops.gg_mxmoe_share_fused([], [], [], [], [], 1, 1, 0, 0, [], torch.zeros(1, dtype=torch.int64), False)
+
+
+def test_workload_and_qconfig_files_round_trip(tmp_path):
+    """The reference's two JSON formats: a qconfig (qconfig.py:66-80) decides the schemes of a workload file
+    (gen_workload.py:86-101), and the workload file parses back into the problem lists the bench runs."""
+    from mxmoe_b200 import run_gg
+    spec = workload.CONFIGS["qwen15-mixed-8192"]
+    gu, dn = workload.draw_schemes(spec)
+    qpath, wpath = tmp_path / "q.json", tmp_path / "w.json"
+    qpath.write_text(run_gg.qconfig_json(spec, gu, dn, layer=11))
+    q = json.loads(qpath.read_text())
+    assert set(q["11"]["experts"]["0"]) == {"gate", "up", "down"}
+    assert set(q["11"]["experts"]["0"]["gate"]) == {"w_bits", "w_gsize", "w_sym", "w_clip", "a_bits", "a_gsize", "a_sym", "a_clip"}
+    assert run_gg.qconfig_schemes(str(qpath), "11", 61) == (gu, dn)
+    run_gg.write_workload("qwen15-mixed-8192", str(qpath), str(wpath), layer=11)
+    layers = run_gg.parse_workload(str(wpath))
+    assert list(layers) == ["11"] and len(layers["11"]["gate_up"]) == 61
+    p = layers["11"]["down"][-1]
+    assert p["shape"] == [8192, 2048, 5632]
+    a, w, g, sym = weights.parse_scheme(dn[60])
+    assert (p["a_bits"], p["w_bits"], p["gsize"], p["sym"]) == (a, w, g, sym)
