@@ -206,7 +206,7 @@ def problem_bytes(m: int, n: int, k: int, w) -> float:
     return m * k * a_bits / 8 + w.nbytes() + m * n * 2 + (m * 2 if a_bits < 16 else 0)
 
 
-def class_pass(layer, spec, counts, peaks, reps: int = 10):
+def class_pass(layer, spec, counts, peaks, reps: int = 10, only: str | None = None):
     """Per-class roofline of the grouped GEMM: every (expert, linear block) problem is classified compute- or
     memory-bound from its algorithmic flops and bytes against the measured peaks, and each class's problem
     subset is launched alone (the other problems' device-side row counts zeroed) and timed with CUDA events."""
@@ -238,7 +238,7 @@ def class_pass(layer, spec, counts, peaks, reps: int = 10):
                 out[cls]["problems"] += 1
                 out[cls]["peak_flops_weighted"] += fl * peak / 1e12      # flop-weighted peak of a mixed class
             for cls in ("compute", "memory"):
-                if not any(mask[cls]):
+                if not any(mask[cls]) or (only is not None and cls != only):
                     continue
                 layer.counts.copy_(orig * torch.tensor(mask[cls][:E], dtype=orig.dtype, device=orig.device))
                 if has_shared:
@@ -401,6 +401,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-extra", action="store_true", help="skip the short runs of the other benchmark configurations")
     ap.add_argument("--no-parity", action="store_true", help="skip the correctness check of the timed workload")
+    ap.add_argument("--only-class", choices=["compute", "memory"], default=None,
+                    help="after the warm-up, launch the two grouped GEMMs over the compute-bound or the memory-bound "
+                         "problems alone a few times and exit (the launches an ncu capture of one class looks at)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -479,6 +482,12 @@ def main():
                       "virtual_experts": layer.E}
             del full, out_full
             torch.cuda.empty_cache()
+
+    if args.only_class and world == 1:
+        counts = layer.counts.cpu().tolist()
+        res = class_pass(layer, spec, counts, peaks, reps=3, only=args.only_class)
+        print(json.dumps({"only_class": args.only_class, **res[args.only_class]}), flush=True)
+        return
 
     sampler = ClockSampler(local)
     barrier()
