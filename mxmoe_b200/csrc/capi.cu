@@ -198,7 +198,7 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
 // The same problem for the kernel with swapped operands: tensor maps with its boxes (weights: 128 channels per
 // box; activations: 176-row and 32-row boxes).  `d` has been validated by build_problem already.
 int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, const mxb::GGProblemDev& d,
-                       mxb::GGSwapProblemDev* o) {
+                       mxb::GGSwapProblemDev* o, bool bulk_everywhere) {
   int rc;
   const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
   const uint64_t lda    = p.lda_bytes > 0 ? (uint64_t)p.lda_bytes : 0;
@@ -242,6 +242,9 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   o->scheme = d.scheme; o->out_mode = d.out_mode; o->ldc = d.ldc; o->sa_stride = d.sa_stride;
   o->c_row0_dev = p.c_row0_dev;
   o->one_group  = (d.scheme == mxb::SCH_W4A16G128 && p.q.gsize == -1) ? 1 : 0;
+  // results addressed through c_row0_dev are the expert-parallel combine: they land in a peer's buffer
+  const bool aligned = p.N % 8 == 0 && d.ldc % 8 == 0 && ((uintptr_t)d.C & 15) == 0;
+  o->bulk_out = (d.out_mode == mxb::OUT_FP16 && aligned && (p.c_row0_dev != nullptr || bulk_everywhere)) ? 1 : 0;
   return MXMOE_OK;
 }
 
@@ -309,12 +312,16 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   if (problem_count) std::memset(swp.data(), 0, swp.size() * sizeof(mxb::GGSwapProblemDev));
   int kept = 0, needs_cvt = 0;
   bool redirect = false;
+  // MXMOE_GG_STORES = rows: every fp16 result leaves as whole rows through the copy engine, not only those that go
+  // to a peer (read here, when the workspace is prepared)
+  const char* stores_env     = getenv("MXMOE_GG_STORES");
+  const bool bulk_everywhere = stores_env && !strcmp(stores_env, "rows");
   int max_rows = 0;
   for (int i = 0; i < problem_count; ++i) {
     if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
     rc = build_problem(st->encode, problems[i], i, dev + kept);
     if (rc) return rc;
-    rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept]);
+    rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept], bulk_everywhere);
     if (rc) return rc;
     // redirected C rows and the per-channel 4-bit weight-only scheme exist in the SWAP kernel only
     if (problems[i].c_row0_dev || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1)) redirect = true;

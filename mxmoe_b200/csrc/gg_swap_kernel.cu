@@ -85,8 +85,10 @@ struct Geo {
   static constexpr uint32_t kASlotCol0 = 2 * kTok;               // A slot s (one per ring stage) at kASlotCol0 + 32 s
   static constexpr int kBarStage0 = 1;                           // named barriers 1 .. kStages: stage s is ready
   static constexpr int kBarAcc0   = 1 + kStages;                 // two more: accumulator b is drained
+  static constexpr int kBarEpi0   = 3 + kStages;                 // two per group of four epilogue warps (row-wide stores)
+  static constexpr int kEpiGroups = kEpiBufs / 4;
   static_assert(kASlotCol0 + kStages * kASlotCols <= 512, "tensor memory budget");
-  static_assert(kBarAcc0 + 1 <= 15, "named barrier budget");
+  static_assert(kBarEpi0 + 2 * kEpiGroups - 1 <= 15, "named barrier budget");
   static_assert((kTok + 32) % 8 == 0, "sa_stage rows must stay 16-byte aligned");
 };
 
@@ -196,6 +198,16 @@ __device__ long long g_trace[kTraceEvents][kTraceLen];
 #endif
 enum { TR_PROD_GOT = 0, TR_PROD_ISSUED, TR_CVT_GOT, TR_CVT_DONE, TR_WATCH, TR_MMA_GOT, TR_MMA_ISSUED, TR_EPI };
 
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
+}
+// one row of the output tile, shared memory -> global memory (this GPU's or a peer's), by the copy engine
+__device__ __forceinline__ void bulk_store_row(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -507,6 +519,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const int64_t grow0 = ti.x_row;   // buffer row of token 0 of the tile (A, scale_a)
       const int64_t crow0 = ti.c_row;   // its row in C
       const int N = pr->N, ldc = pr->ldc, out_mode = pr->out_mode;
+      const bool bulk     = pr->bulk_out != 0;
       const bool is_int   = is_int_scheme(ti.scheme);
       const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
       const int n_ch      = ti.n_tile * kWT + q * 32 + lane;                                // this thread's channel
@@ -604,6 +617,33 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             h[j]      = *reinterpret_cast<uint32_t*>(&r);
           }
         }
+        if (bulk) {
+          // Row-wide stores: the four warps of a group (one per TMEM lane quarter) lay the chunk down as 32 token
+          // rows of 256 bytes (128 channels) in their joint 8 KiB buffer and hand every row to the copy engine as
+          // one piece.  This is the form for outputs that cross NVLink (the down projection of an expert-parallel
+          // layer stores into the peers' buffers): 64-byte pieces from plain stores cost the launch 65 % more time.
+          const uint32_t gb = epi_base + half * 4 * kEpiStageS;
+          if (lane < 8) bulk_wait_read();                          // this thread's earlier rows have left the buffer
+          nbar_sync(G::kBarEpi0 + 2 * half, 128);
+          const uint32_t col = gb + (uint32_t)(q * 32 + lane) * 2;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            sts16(col + (2 * j) * 256, h[j]);
+            sts16(col + (2 * j + 1) * 256, h[j] >> 16);
+          }
+          fence_proxy_async_smem();
+          nbar_sync(G::kBarEpi0 + 2 * half + 1, 128);
+          if (lane < 8) {
+            const int row = q * 8 + lane, tk = ch * 32 + row;
+            const int n0  = ti.n_tile * kWT;
+            if (tk < ntok) {
+              __half* dst = reinterpret_cast<__half*>(pr->C) + (crow0 + tk) * ldc + n0;
+              bulk_store_row(dst, gb + row * 256, (uint32_t)min(kWT, N - n0) * 2u);
+            }
+            bulk_commit();
+          }
+          continue;
+        }
         // transpose through the warp's 2 KiB buffer: row = token pair (128 bytes = 32 channels x 2 tokens),
         // 16-byte slots XOR-swizzled by the row so that writes and reads are conflict-free
         __syncwarp();   // the previous chunk's reads of the buffer are done
@@ -618,6 +658,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane < 8) bulk_wait_all();   // rows handed to the copy engine have reached memory before the CTA ends
     if (blockIdx.x == 0 && warp == 2 && lane == 0) {
       status->prof[PROF_EPI_WAIT]  = w_epi;
       status->prof[PROF_EPI_STORE] = w_store;

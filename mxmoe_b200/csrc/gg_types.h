@@ -68,7 +68,8 @@ struct alignas(128) GGSwapProblemDev {
   int scheme, out_mode, ldc, sa_stride;
   const int* c_row0_dev;   // optional: rows of C start at *c_row0_dev instead of at row0
   int one_group;           // w4a16: one (scale, zero) pair per channel for the whole of K (per-channel scheme)
-  int pad[11];
+  int bulk_out;            // fp16 results leave as whole 256-byte rows through the copy engine (outputs in a peer's memory)
+  int pad[10];
 };
 static_assert(sizeof(GGSwapProblemDev) == 512, "GGSwapProblemDev layout");
 

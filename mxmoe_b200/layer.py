@@ -118,7 +118,12 @@ class ExpertCompute:
             self.row_ident = torch.arange(max(R, 1), dtype=torch.int64, device=dev)
 
         p1, p2 = [], []
-        for i, e in enumerate(self.seg_expert):
+        # Launch order: the segments of one expert next to each other.  The tiles of a launch are walked in problem
+        # order by all CTAs together, so an expert's weights are then read from HBM once however many segments
+        # (source ranks) it has, and outputs that go to different ranks (down_out) are in flight at the same time
+        # instead of one destination after the other.
+        for i in sorted(range(len(self.seg_expert)), key=lambda i: (self.seg_expert[i], i)):
+            e = self.seg_expert[i]
             m_ptr, r_ptr = seg_m.data_ptr() + 4 * i, seg_row0.data_ptr() + 4 * i
             w1: PackedWeight = gate_up[e]
             w2: PackedWeight = down[e]
