@@ -199,11 +199,12 @@ def ncu_traffic(workload_name: str):
     return sum(vals) / len(vals) if vals else None
 
 
-def problem_bytes(m: int, n: int, k: int, w) -> float:
+def problem_bytes(m: int, n: int, k: int, w, fused_silu: bool = False) -> float:
     """Algorithmic bytes of one problem: A at a_bits per value, the packed weight with its scales, fp16 C and the
-    per-token scales (activations of 4-bit schemes count half a byte per code, whatever the layer stores)."""
+    per-token scales (activations of 4-bit schemes count half a byte per code, whatever the layer stores).  A
+    gate_up problem with silu(gate) * up in its epilogue writes n / 2 columns."""
     a_bits = w.qparams[0]
-    return m * k * a_bits / 8 + w.nbytes() + m * n * 2 + (m * 2 if a_bits < 16 else 0)
+    return m * k * a_bits / 8 + w.nbytes() + m * (n // 2 if fused_silu else n) * 2 + (m * 2 if a_bits < 16 else 0)
 
 
 def class_pass(layer, spec, counts, peaks, reps: int = 10, only: str | None = None):
@@ -230,7 +231,7 @@ def class_pass(layer, spec, counts, peaks, reps: int = 10, only: str | None = No
                 a_bits = w.qparams[0]
                 peak = peaks["bf16_tflops"] * 1e12 * (2.0 if a_bits < 16 else 1.0)
                 fl = 2.0 * m * nn * kk
-                by = problem_bytes(m, nn, kk, w)
+                by = problem_bytes(m, nn, kk, w, gg is core.gg1 and e != E and getattr(core, "fused_silu", False))
                 cls = "compute" if fl / peak > by / bw else "memory"
                 mask[cls][e] = 1
                 out[cls]["flops"] += fl
@@ -319,7 +320,8 @@ def roofline_of(layer, spec, counts, d1, d2, peaks):
             fl_all += fl
             if w.qparams[0] < 16:
                 fl_i8 += fl
-            byts += problem_bytes(m, nn, kk, w)
+            byts += problem_bytes(m, nn, kk, w, block is layer.gate_up and e != spec.num_experts and
+                                  getattr(layer._core, "fused_silu", False))
     share_i8 = fl_i8 / fl_all if fl_all else 0.0
     peak = peaks["bf16_tflops"] * (1.0 + share_i8)
     achieved = flops_launch / (gemm_ms * 1e-3) / 1e12

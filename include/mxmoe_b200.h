@@ -50,6 +50,10 @@ typedef struct mxmoe_qparams {
  *                           (the reference's per-channel weight-only branch, cta_gemm.cuh:112-286; default kernel only)
  * C is fp16 [M,N] (row pitch ldc elements, 0 = N).  With out_mode 1 the raw
  * accumulators are stored instead (int32 for w8a8/w4a4, fp32 otherwise).
+ * With out_mode 2 (default kernel, not for w4a16) B is a gate_up weight [gate rows (I); up rows (I)], N = 2 I with
+ * I a multiple of 64, and C is fp16 [M, I] (ldc 0 = I): C = fp16(fp16(silu(gate)) * up) computed from the scaled
+ * fp16 results in the epilogue -- the bits mxmoe_silu_mul_then_quant makes of the [M, 2 I] rows of out_mode 0
+ * before it quantises (reference: the first half of silu_mul_then_quant_kernel, ref_bind.cu:701-716).
  *
  * Rows: the problem covers rows [row0, row0 + M) of A, scale_a and C.  `a_rows`
  * is the number of rows the A buffer holds (0 = row0 + M); it bounds what the
@@ -187,7 +191,8 @@ typedef struct mxmoe_act_args {
   void* q_store;              /* packed activations */
   void* s_store;              /* fp16 per-token scales */
   const int32_t* row_expert;  /* [rows_routed] */
-  const int64_t* row_token;   /* [rows_routed], quant_inp_act only */
+  const int64_t* row_token;   /* [rows_routed], quant_inp_act only; NULL (without rotation): row r of `in` is routed row r and
+                                 the shared rows are the rows of `in_shared` -- the quantiser alone, rows_dev honoured */
   const int32_t* exp_qtag;
   const int32_t* exp_row_start;
   const int32_t* exp_q_off;
@@ -201,7 +206,7 @@ typedef struct mxmoe_act_args {
   int32_t rotate;             /* quant_inp_act only: rotate rows by diag(signs) H_k / sqrt(k) first */
   int32_t rec_stride;         /* > 0: record layout (see below), in fp16 elements */
   int32_t rec_scale_off;      /* record layout: offset of the scale inside the record, or < 0 for s_store[row] */
-  const int32_t* rows_dev;    /* optional, silu_mul_then_quant without shared rows: live row count in device memory;
+  const int32_t* rows_dev;    /* optional, quant_act / silu_mul_then_quant without shared rows: live row count in device memory;
                                  rows at or beyond it are skipped (rows_routed == rows_total is then an upper bound) */
 } mxmoe_act_args;
 

@@ -385,7 +385,9 @@ __global__ void __launch_bounds__(kBlock) quant_act_kernel(ActArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_in_blk = warp / kWarps, w = warp % kWarps;
   const int row     = blockIdx.x * (8 / kWarps) + row_in_blk;
-  const bool row_ok = row < a.rows_total;
+  const int live    = a.rows_dev ? min(a.rows_total, __ldg(a.rows_dev)) : a.rows_total;
+  if (blockIdx.x * (8 / kWarps) >= live) return;   // the whole block lies beyond the live rows
+  const bool row_ok = row < live;
 
   RowInfo ri{0, 0, nullptr, nullptr};
   if (row_ok) ri = locate_row(a, row);
@@ -517,8 +519,10 @@ __global__ void __launch_bounds__(kBlock) gather_rows_kernel(ActArgs a, TokenQua
 // ---------------------------------------------------------------------------------------------
 // h = silu(gate) * up, then quantise; one pass per routed row.  Values are fp16 after the product,
 // so they are kept as half2 (32 registers per thread for 64 values).
-template <int kWarps>
-__global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
+// kSilu = false: the rows are h already ([rows, k] fp16, e.g. left by a GEMM epilogue that applied silu * up):
+// only the quantiser runs, on the same registers.
+template <int kWarps, bool kSilu>
+__device__ __forceinline__ void rows_quant_body(const ActArgs& a) {
   __shared__ float red[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_in_blk = warp / kWarps, w = warp % kWarps;
@@ -532,8 +536,9 @@ __global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
   const __half* src = nullptr;
   if (row_ok) {
     // gate_up rows: [gate (k) | up (k)]; routed rows first, shared-expert rows in their own buffer
-    if (row < a.rows_routed) src = a.in + (int64_t)row * 2 * a.k;
-    else                     src = a.in_shared + (int64_t)(row - a.rows_routed) * 2 * a.k_shared;
+    constexpr int kIn = kSilu ? 2 : 1;
+    if (row < a.rows_routed) src = a.in + (int64_t)row * kIn * a.k;
+    else                     src = a.in_shared + (int64_t)(row - a.rows_routed) * kIn * a.k_shared;
   }
   __half2 h[kJ][4];
   __half2 m2 = __float2half2_rn(0.f);
@@ -545,7 +550,7 @@ __global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
     const int ci = chunk_of<kWarps>(w, j, lane);
     if (row_ok && ci < nchunk) {
       gq[j] = __ldg(reinterpret_cast<const uint4*>(src) + ci);
-      uq[j] = __ldg(reinterpret_cast<const uint4*>(src + ri.k) + ci);
+      if (kSilu) uq[j] = __ldg(reinterpret_cast<const uint4*>(src + ri.k) + ci);
     }
   }
 #pragma unroll
@@ -558,11 +563,15 @@ __global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
       const __half2* uh = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 gf = __half22float2(gh[e]);
-        // silu in fp32, rounded to fp16; product rounded to fp16 (fp16 module semantics)
-        const float s0 = __fdividef(gf.x, 1.f + __expf(-gf.x));
-        const float s1 = __fdividef(gf.y, 1.f + __expf(-gf.y));
-        h[j][e] = __hmul2(__floats2half2_rn(s0, s1), uh[e]);
+        if (kSilu) {
+          const float2 gf = __half22float2(gh[e]);
+          // silu in fp32, rounded to fp16; product rounded to fp16 (fp16 module semantics)
+          const float s0 = __fdividef(gf.x, 1.f + __expf(-gf.x));
+          const float s1 = __fdividef(gf.y, 1.f + __expf(-gf.y));
+          h[j][e] = __hmul2(__floats2half2_rn(s0, s1), uh[e]);
+        } else {
+          h[j][e] = gh[e];
+        }
         m2 = __hmax2(m2, __habs2(h[j][e]));
       }
     } else {
@@ -615,6 +624,11 @@ __global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
   }
 }
 
+template <int kWarps>
+__global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) { rows_quant_body<kWarps, true>(a); }
+template <int kWarps>
+__global__ void __launch_bounds__(kBlock, 3) rows_quant_kernel(ActArgs a) { rows_quant_body<kWarps, false>(a); }
+
 #define MXB_DISPATCH_WARPS(kmax, rows, KERNEL, ...)                                                   \
   do {                                                                                                \
     if ((kmax) <= 2048)      KERNEL<1><<<((rows) + 7) / 8, kBlock, 0, stream>>>(__VA_ARGS__);          \
@@ -628,7 +642,12 @@ __global__ void __launch_bounds__(kBlock, 3) silu_mul_quant_kernel(ActArgs a) {
 cudaError_t launch_quant_act(const ActArgs& a, cudaStream_t stream) {
   if (a.rows_total <= 0) return cudaSuccess;
   const int kmax = a.k > a.k_shared ? a.k : a.k_shared;
-  MXB_DISPATCH_WARPS(kmax, a.rows_total, quant_act_kernel, a);
+  if (!a.rotate && !a.row_token) {
+    // rows in place, no rotation: the quantiser alone (the second half of silu_mul_quant)
+    MXB_DISPATCH_WARPS(kmax, a.rows_total, rows_quant_kernel, a);
+  } else {
+    MXB_DISPATCH_WARPS(kmax, a.rows_total, quant_act_kernel, a);
+  }
   return cudaGetLastError();
 }
 

@@ -31,7 +31,7 @@ struct ActArgs {
   int rotate;                // 1: apply y = (x .* signs) H / sqrt(k) before quantising
   int rec_stride;            // > 0: record layout, row r at q_store + r * rec_stride (fp16 elements)
   int rec_scale_off;         // record layout: scale at this offset inside the record, or < 0: s_store[r]
-  const int* rows_dev;       // optional live row count in device memory (silu_mul_quant, no shared rows)
+  const int* rows_dev;       // optional live row count in device memory (quant_act, silu_mul_quant; no shared rows)
 };
 
 // Per-token quantisation into token-major stores; a store pointer that is null is not produced.

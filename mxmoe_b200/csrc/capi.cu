@@ -114,6 +114,35 @@ int encode_2d(EncodeTiledFn enc, CUtensorMap* out, const void* base, CUtensorMap
   return MXMOE_OK;
 }
 
+// Weight map of the kernel with swapped operands, always of rank 4 so that its producer has one form of load.
+// Plain: [rows][inner] with two unit dimensions, box = box_rows x box_inner.  `silu_inter` = I > 0: the matrix is
+// [gate rows (I); up rows (I)] and a box of 128 rows gathers, four times, 16 gate rows followed by the 16 up rows of
+// the same columns of C: dimensions (inner, 16 rows, gate|up, I / 16 groups), box (box_inner, 16, 2, 4).
+int encode_w(EncodeTiledFn enc, CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+             uint64_t inner_elems, uint64_t rows, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw,
+             int silu_inter, int idx) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+    return fail(MXMOE_ERR_INVALID, "problem %d: B pointer %p is not 16-byte aligned", idx, base);
+  const uint64_t pitch = inner_elems * (uint64_t)elem_bytes;
+  if (pitch % 16 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: B row pitch %llu B is not a multiple of 16", idx, (unsigned long long)pitch);
+  cuuint64_t gdim[4], gstride[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  if (silu_inter > 0) {
+    const uint64_t I = (uint64_t)silu_inter;
+    gdim[0] = inner_elems; gdim[1] = 16; gdim[2] = 2; gdim[3] = I / 16;
+    gstride[0] = pitch; gstride[1] = I * pitch; gstride[2] = 16 * pitch;
+    box[0] = box_inner; box[1] = 16; box[2] = 2; box[3] = box_rows / 32;
+  } else {
+    gdim[0] = inner_elems; gdim[1] = rows; gdim[2] = 1; gdim[3] = 1;
+    gstride[0] = pitch; gstride[1] = pitch * rows; gstride[2] = pitch * rows;
+    box[0] = box_inner; box[1] = box_rows; box[2] = 1; box[3] = 1;
+  }
+  CUresult r = enc(out, dt, 4, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MXMOE_ERR_CUDA, "problem %d: cuTensorMapEncodeTiled(B, rank 4) failed with CUresult %d", idx, (int)r);
+  return MXMOE_OK;
+}
+
 int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GGProblemDev* d) {
   int scheme = 0;
   int rc     = scheme_of(p.q, &scheme);
@@ -126,15 +155,21 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
   if (p.M < 0 || p.N <= 0 || p.K <= 0) return fail(MXMOE_ERR_INVALID, "problem %d: bad shape M=%d N=%d K=%d", idx, p.M, p.N, p.K);
   if (p.N % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: N=%d must be a multiple of 8", idx, p.N);
   if (p.row0 < 0) return fail(MXMOE_ERR_INVALID, "problem %d: negative row0", idx);
-  const int ldc = p.ldc > 0 ? p.ldc : p.N;
-  if (ldc < p.N || ldc % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: ldc=%d must be >= N and a multiple of 8", idx, ldc);
+  // OUT_SILU: C has one column per (gate, up) pair of weight rows
+  const int n_out = p.out_mode == mxb::OUT_SILU ? p.N / 2 : p.N;
+  const int ldc   = p.ldc > 0 ? p.ldc : n_out;
+  if (ldc < n_out || ldc % 8 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: ldc=%d must be >= the %d columns of C and a multiple of 8", idx, ldc, n_out);
+  if (p.out_mode == mxb::OUT_SILU) {
+    if (scheme == mxb::SCH_W4A16G128) return fail(MXMOE_ERR_UNSUPPORTED, "problem %d: out_mode 2 (silu(gate) * up) is not available for weights packed along N", idx);
+    if (p.N % 128 != 0) return fail(MXMOE_ERR_INVALID, "problem %d: out_mode 2 needs N = 2 I with I %% 64 == 0 (N=%d)", idx, p.N);
+  }
   if ((reinterpret_cast<uintptr_t>(p.C) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: C is not 16-byte aligned", idx);
   const bool wxax = scheme == mxb::SCH_W8A8 || scheme == mxb::SCH_W4A4 || scheme == mxb::SCH_W4A4_XA;
-  if (wxax && p.out_mode == mxb::OUT_FP16) {
+  if (wxax && p.out_mode != mxb::OUT_ACC) {
     if (!p.scale_a || !p.scale_b) return fail(MXMOE_ERR_INVALID, "problem %d: w%da%d needs scale_a and scale_b", idx, p.q.w_bits, p.q.a_bits);
     if ((reinterpret_cast<uintptr_t>(p.scale_b) & 15) != 0) return fail(MXMOE_ERR_INVALID, "problem %d: scale_b is not 16-byte aligned", idx);
   }
-  if (p.out_mode != mxb::OUT_FP16 && p.out_mode != mxb::OUT_ACC) return fail(MXMOE_ERR_INVALID, "problem %d: bad out_mode %d", idx, p.out_mode);
+  if (p.out_mode != mxb::OUT_FP16 && p.out_mode != mxb::OUT_ACC && p.out_mode != mxb::OUT_SILU) return fail(MXMOE_ERR_INVALID, "problem %d: bad out_mode %d", idx, p.out_mode);
   const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
   const uint64_t lda    = p.lda_bytes > 0 ? (uint64_t)p.lda_bytes : 0;
   if (!p.row0_dev && a_rows < (uint64_t)p.row0 + (uint64_t)p.M) return fail(MXMOE_ERR_INVALID, "problem %d: a_rows=%llu < row0+M", idx, (unsigned long long)a_rows);
@@ -206,21 +241,22 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   const auto f16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const auto u8  = CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const auto s128 = CU_TENSOR_MAP_SWIZZLE_128B;
+  const int silu = d.out_mode == mxb::OUT_SILU ? p.N / 2 : 0;
   switch (d.scheme) {
     case mxb::SCH_FP16:
-      if ((rc = encode_2d(enc, &o->tmW, p.B, f16, 2, K, N, 64, mxb::kWT, s128, "B", idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, f16, 2, K, N, 64, mxb::kWT, s128, silu, idx))) return rc;
       break;
     case mxb::SCH_W8A8:
-      if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K, N, 128, mxb::kWT, s128, "B", idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K, N, 128, mxb::kWT, s128, silu, idx))) return rc;
       break;
     case mxb::SCH_W4A4:
     case mxb::SCH_W4A4_XA:
       // packed rows of 64 bytes per stage; the 64-byte swizzle spreads the rows a converter warp reads over the banks
-      if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K / 2, N, 64, mxb::kWT, CU_TENSOR_MAP_SWIZZLE_64B, "B", idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K / 2, N, 64, mxb::kWT, CU_TENSOR_MAP_SWIZZLE_64B, silu, idx))) return rc;
       break;
     case mxb::SCH_W4A16G128:
       // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, 32 packed rows = 128 channels
-      if ((rc = encode_2d(enc, &o->tmW, p.B, u8, 1, K * 2, N / 4, 128, mxb::kWT / 4, s128, "B", idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K * 2, N / 4, 128, mxb::kWT / 4, s128, 0, idx))) return rc;
       break;
     default:
       break;
@@ -245,6 +281,7 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   // results addressed through c_row0_dev are the expert-parallel combine: they land in a peer's buffer
   const bool aligned = p.N % 8 == 0 && d.ldc % 8 == 0 && ((uintptr_t)d.C & 15) == 0;
   o->bulk_out = (d.out_mode == mxb::OUT_FP16 && aligned && (p.c_row0_dev != nullptr || bulk_everywhere)) ? 1 : 0;
+  o->silu_inter = silu;
   return MXMOE_OK;
 }
 
@@ -324,7 +361,8 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept], bulk_everywhere);
     if (rc) return rc;
     // redirected C rows and the per-channel 4-bit weight-only scheme exist in the SWAP kernel only
-    if (problems[i].c_row0_dev || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1)) redirect = true;
+    if (problems[i].c_row0_dev || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1) ||
+        problems[i].out_mode == mxb::OUT_SILU) redirect = true;
     if (problems[i].M > max_rows) max_rows = problems[i].M;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
     else if ((dev[kept].scheme == mxb::SCH_W4A4_XA || dev[kept].scheme == mxb::SCH_W4A16G128) && needs_cvt < 1) needs_cvt = 1;
@@ -479,13 +517,14 @@ static int to_act_args(const mxmoe_act_args* a, mxb::ActArgs* o, bool silu) {
   if (!a->in || !a->q_store || !a->exp_qtag || (!a->exp_row_start && a->rec_stride <= 0))
     return fail(MXMOE_ERR_INVALID, "null pointer in activation arguments");
   if (a->rows_routed > 0 && !a->row_expert) return fail(MXMOE_ERR_INVALID, "row_expert is required for routed rows");
-  if (!silu && a->rows_routed > 0 && !a->row_token) return fail(MXMOE_ERR_INVALID, "row_token is required for routed rows");
+  // quant_act without row_token: the rows of `in` (and of `in_shared`) are taken in place; no rotation then
+  if (!silu && a->rows_routed > 0 && !a->row_token && a->rotate) return fail(MXMOE_ERR_INVALID, "row_token is required for rotated rows");
   if (a->rows_routed < 0 || a->rows_total < a->rows_routed) return fail(MXMOE_ERR_INVALID, "bad row counts");
   const bool has_shared = a->rows_total > a->rows_routed;
   const int ks = has_shared ? a->k_shared : a->k;
   if (a->k <= 0 || a->k % 8 || ks <= 0 || ks % 8) return fail(MXMOE_ERR_INVALID, "row length must be a positive multiple of 8 (k=%d, k_shared=%d)", a->k, ks);
   if (a->k > 16384 || ks > 16384) return fail(MXMOE_ERR_UNSUPPORTED, "row length above 16384 is not supported");
-  if (silu && has_shared && !a->in_shared) return fail(MXMOE_ERR_INVALID, "in_shared is required for shared-expert rows");
+  if ((silu || !a->row_token) && has_shared && !a->in_shared) return fail(MXMOE_ERR_INVALID, "in_shared is required for shared-expert rows");
   if (!silu && a->rotate) {
     if ((a->k & (a->k - 1)) != 0 || a->k < 256) return fail(MXMOE_ERR_UNSUPPORTED, "rotation needs a power-of-two row length >= 256 (k=%d)", a->k);
     if (has_shared && ks != a->k) return fail(MXMOE_ERR_INVALID, "rotation needs k_shared == k");

@@ -394,6 +394,10 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         uint32_t wbytes;
         int wx_step, wy;
         weight_coords(ti.scheme, w_row, wbytes, wx_step, wy);
+        // silu(gate) * up problems: the box gathers 16 gate + 16 up rows four times; its origin is the tile's first
+        // group of 16 columns of C (the weight maps have rank 4, see encode_w)
+        int wz = 0;
+        if (pr->silu_inter) { wz = ti.n_tile * 4; wy = 0; }
         const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;   // (packed int4: see below)
         // this tile's K block for which the test hook (GGStatus::skip_stage) announces more weight bytes than will
         // arrive.  A select, not a branch: one more branch per stage in these loops cost the w4a4 layer 3.5 %, and the
@@ -410,7 +414,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             TRACE(TR_PROD_GOT, n_stage + kb);
             if (!got) { report_s(status, 1, t); ok = false; break; }
             mbar_expect_tx(wfull0 + 8 * stage, wbytes + (kb == skip_kb ? 16u : 0u));
-            tma_load_2d(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy);
+            tma_load_4d(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
             mbar_expect_tx(xfull0 + 8 * stage, xbytes);
             tma_load_2d(xslot(stage), &pr->tmX, xfull0 + 8 * stage, kb * xx_step, x_row);
             TRACE(TR_PROD_ISSUED, n_stage + kb);
@@ -427,13 +431,13 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             if (packed_x) {
               // packed activation rows (64 bytes of K each) go behind the packed weights; the converters expand them
               mbar_expect_tx(wbar, wbytes + xbytes);
-              tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+              tma_load_4d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, 0, wz);
               for (int b = 0; b < nbox; ++b)
                 tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, wbar, kb * 64, x_row + b * kXBoxSmall);
               mbar_arrive(bar);                     // no activation tile of its own: complete the phase
             } else {
               mbar_expect_tx(wbar, wbytes + (kb == skip_kb ? 16u : 0u));
-              tma_load_2d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy);
+              tma_load_4d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, 0, wz);
               mbar_expect_tx(bar, xbytes);
               if (big) {
                 tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
@@ -520,11 +524,13 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const int64_t crow0 = ti.c_row;   // its row in C
       const int N = pr->N, ldc = pr->ldc, out_mode = pr->out_mode;
       const bool bulk     = pr->bulk_out != 0;
+      const int silu      = pr->silu_inter;   // > 0: lanes 0-15 of the warp hold gate rows, lanes 16-31 the up rows of the same 16 columns of C
       const bool is_int   = is_int_scheme(ti.scheme);
       const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
-      const int n_ch      = ti.n_tile * kWT + q * 32 + lane;                                // this thread's channel
+      const int c_col     = ti.n_tile * (kWT / 2) + q * 16 + (lane & 15);                   // silu: this thread's column of C
+      const int n_ch      = silu ? (lane >> 4) * silu + c_col : ti.n_tile * kWT + q * 32 + lane;   // this thread's channel (weight row)
       __half2 sb2 = __float2half2_rn(0.f);
-      if (!dead && is_int && out_mode == OUT_FP16 && half * 32 < ntok) {
+      if (!dead && is_int && out_mode != OUT_ACC && half * 32 < ntok) {
         // everything that does not depend on the accumulator is fetched before waiting for it
         if (n_ch < N) sb2 = __half2half2(__ldg(pr->scale_b + n_ch));
         __syncwarp();
@@ -616,6 +622,30 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             __half2 r = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
             h[j]      = *reinterpret_cast<uint32_t*>(&r);
           }
+        }
+        if (silu) {
+          // h = fp16( fp16(silu(gate)) * up ) on the fp16 results, the arithmetic of the stand-alone silu-mul kernel.
+          // The gate lane keeps tokens 0-15 of the chunk and gets their up values; the up lane gets the gate values
+          // of tokens 16-31: eight exchanges, then each lane finishes 16 tokens of its column and stores them.
+          const bool up = lane >= 16;
+          uint32_t other[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, up ? h[i] : h[8 + i], 16);
+          __half* dst = reinterpret_cast<__half*>(pr->C) + (crow0 + ch * 32 + (up ? 16 : 0)) * ldc + c_col;
+          const int tk0 = ch * 32 + (up ? 16 : 0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t gw = up ? other[i] : h[i], uw = up ? h[8 + i] : other[i];
+            const float2 gf   = __half22float2(*reinterpret_cast<const __half2*>(&gw));
+            const float s0    = __fdividef(gf.x, 1.f + __expf(-gf.x));
+            const float s1    = __fdividef(gf.y, 1.f + __expf(-gf.y));
+            const __half2 r   = __hmul2(__floats2half2_rn(s0, s1), *reinterpret_cast<const __half2*>(&uw));
+            if (c_col < silu) {
+              if (tk0 + 2 * i < ntok) dst[(2 * i) * ldc] = __low2half(r);
+              if (tk0 + 2 * i + 1 < ntok) dst[(2 * i + 1) * ldc] = __high2half(r);
+            }
+          }
+          continue;
         }
         if (bulk) {
           // Row-wide stores: the four warps of a group (one per TMEM lane quarter) lay the chunk down as 32 token

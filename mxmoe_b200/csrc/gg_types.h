@@ -19,6 +19,7 @@ enum Scheme : int {
 enum OutMode : int {
   OUT_FP16 = 0,  // scaled fp16 result
   OUT_ACC  = 1,  // raw accumulators: int32 for w8a8 / w4a4, fp32 otherwise
+  OUT_SILU = 2,  // B = [gate rows; up rows] (N = 2 I): C[M, I] = fp16( fp16(silu(gate)) * up ) of the scaled fp16 results
 };
 
 constexpr int kMaxProblems = 256;
@@ -69,7 +70,8 @@ struct alignas(128) GGSwapProblemDev {
   const int* c_row0_dev;   // optional: rows of C start at *c_row0_dev instead of at row0
   int one_group;           // w4a16: one (scale, zero) pair per channel for the whole of K (per-channel scheme)
   int bulk_out;            // fp16 results leave as whole 256-byte rows through the copy engine (outputs in a peer's memory)
-  int pad[10];
+  int silu_inter;          // OUT_SILU: I (the weight tile interleaves 16 gate rows with 16 up rows, four times); else 0
+  int pad[9];
 };
 static_assert(sizeof(GGSwapProblemDev) == 512, "GGSwapProblemDev layout");
 

@@ -17,6 +17,7 @@ from . import _lib
 
 OUT_FP16 = 0
 OUT_ACC = 1
+OUT_SILU = 2   # B = [gate rows; up rows]: C[M, N/2] = fp16(fp16(silu(gate)) * up) of the scaled results
 
 
 def _ptr(t) -> int | None:

@@ -31,8 +31,14 @@ import os
 import torch
 
 from . import _lib
-from .gg import GroupedGemm, Problem, current_stream_ptr
+from .gg import OUT_FP16, OUT_SILU, GroupedGemm, Problem, current_stream_ptr
 from .weights import PackedWeight
+
+
+def default_fuse_silu() -> bool:
+    """Whether layers apply silu(gate) * up in the epilogue of the gate_up GEMM when nobody says otherwise
+    (environment variable MXMOE_FUSE_SILU = 1 | 0, read when a layer is built)."""
+    return os.environ.get("MXMOE_FUSE_SILU", "0") == "1"
 
 
 def tag_of(qp) -> int:
@@ -81,8 +87,9 @@ class ExpertCompute:
                  q1: torch.Tensor, rec1: int, scale1_ptr: int, scale1_stride: int, device,
                  shared: dict | None = None, shared_inter: int = 0, tag_fn=internal_tag,
                  down_out: list | None = None, rows_dev: torch.Tensor | None = None,
-                 online_had: torch.Tensor | None = None):
+                 online_had: torch.Tensor | None = None, fuse_silu: bool | None = None):
         self.E, self.H, self.I, self.Is = num_experts, hidden, inter, shared_inter
+        fuse_silu = default_fuse_silu() if fuse_silu is None else fuse_silu
         self.R, self.device = rows_cap, device
         self.gate_up, self.down = gate_up, down
         self.row_expert, self.seg_expert = row_expert, list(seg_expert)
@@ -112,10 +119,13 @@ class ExpertCompute:
         self.q2 = torch.zeros(max(R, 1) * self.rec2, **f16)    # down input records
         self.s2 = torch.zeros(max(R, 1), **f16)
         self.o2 = torch.zeros(max(R, 1) * H, **f16)            # down output rows [R, H]
-        if self.had_k is not None:
-            self.h16 = torch.zeros(max(R, 1), I, **f16)        # silu(gate) * up rows, rotated in place
+        # silu(gate) * up in the epilogue of the first GEMM (the 2 I wide fp16 rows never reach memory): available
+        # when every routed expert's gate_up weights are packed along K and I is a multiple of 64
+        self.fused_silu = bool(fuse_silu) and I % 64 == 0 and bool(local) and \
+            all(gate_up[e].qparams[1] != 4 or gate_up[e].qparams[0] != 16 for e in local)
+        if self.had_k is not None or self.fused_silu:
+            self.h16 = torch.zeros(max(R, 1), I, **f16)        # silu(gate) * up rows (rotated in place if had_k)
             self.tag0 = torch.zeros(num_experts + 1, dtype=torch.int32, device=dev)
-            self.row_ident = torch.arange(max(R, 1), dtype=torch.int64, device=dev)
 
         p1, p2 = [], []
         # Launch order: the segments of one expert next to each other.  The tiles of a launch are walked in problem
@@ -127,7 +137,8 @@ class ExpertCompute:
             m_ptr, r_ptr = seg_m.data_ptr() + 4 * i, seg_row0.data_ptr() + 4 * i
             w1: PackedWeight = gate_up[e]
             w2: PackedWeight = down[e]
-            p1.append(Problem(A=q1, B=w1.data, C=self.o1, M=R, N=2 * I, K=H, qparams=w1.qparams,
+            p1.append(Problem(A=q1, B=w1.data, C=self.h16 if self.fused_silu else self.o1, M=R, N=2 * I, K=H,
+                              qparams=w1.qparams, out_mode=OUT_SILU if self.fused_silu else OUT_FP16,
                               scale_a=scale1_ptr if self._tag1[e] else None, scale_b=w1.scale,
                               a_rows=R, lda_bytes=rec1 * 2, sa_stride=scale1_stride, m_dev=m_ptr, row0_dev=r_ptr,
                               a_expanded=1 if self._tag1[e] == 3 else 0))
@@ -168,7 +179,14 @@ class ExpertCompute:
         """``rows``: upper bound of the rows in use this step (sizes the silu launch)."""
         lib = _lib.lib()
         self.gg1.run()
-        if self.had_k is None:
+        if self.fused_silu and self.had_k is None:
+            # the first GEMM left h = silu(gate) * up as fp16 rows: quantise them per expert format
+            _act_call(lib.mxmoe_quant_act, inp=self.h16, in_shared=None, q_store=self.q2, s_store=self.s2,
+                      row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
+                      exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
+                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1,
+                      rows_dev=self.rows_dev)
+        elif self.had_k is None:
             _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.q2, s_store=self.s2,
                       row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
                       exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
@@ -177,16 +195,18 @@ class ExpertCompute:
         else:
             # h = silu(gate) * up as fp16 rows -> h (had_K (x) H_m) / sqrt(I) in place -> quantise per expert format
             from .hadamard import hadamard_kron
-            _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.h16, s_store=self.s2,
-                      row_expert=self.row_expert, row_token=None, exp_qtag=self.tag0, exp_row_start=None,
-                      exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
-                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.I, rec_scale_off=-1,
-                      rows_dev=self.rows_dev)
+            if not self.fused_silu:
+                _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1, in_shared=None, q_store=self.h16, s_store=self.s2,
+                          row_expert=self.row_expert, row_token=None, exp_qtag=self.tag0, exp_row_start=None,
+                          exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
+                          rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.I, rec_scale_off=-1,
+                          rows_dev=self.rows_dev)
             hadamard_kron(self.h16[:rows], self.had_k, out=self.h16[:rows])
             _act_call(lib.mxmoe_quant_act, inp=self.h16, in_shared=None, q_store=self.q2, s_store=self.s2,
-                      row_expert=self.row_expert, row_token=self.row_ident, exp_qtag=self.tag2, exp_row_start=None,
+                      row_expert=self.row_expert, row_token=None, exp_qtag=self.tag2, exp_row_start=None,
                       exp_q_off=None, exp_s_off=None, signs=None, k=self.I, k_shared=self.I, rows_routed=rows,
-                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1)
+                      rows_total=rows, num_experts=self.E, rotate=0, rec_stride=self.rec2, rec_scale_off=-1,
+                      rows_dev=self.rows_dev)
         if self.shared is not None:
             T = self.shared["tokens"]
             _act_call(lib.mxmoe_silu_mul_then_quant, inp=self.o1s, in_shared=self.o1s, q_store=self.q2s,
@@ -249,8 +269,9 @@ class MoELayer:
 
     def __init__(self, num_experts: int, topk: int, hidden: int, inter: int, gate_up: dict, down: dict,
                  max_tokens: int, shared_inter: int = 0, signs: torch.Tensor | None = None, rotate: bool = False,
-                 device=None, online_had: torch.Tensor | None = None):
+                 device=None, online_had: torch.Tensor | None = None, fuse_silu: bool | None = None):
         self.E, self.topk, self.H, self.I, self.Is = num_experts, topk, hidden, inter, shared_inter
+        self.fuse_silu = fuse_silu       # silu(gate) * up in the first GEMM's epilogue where the schemes allow it
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.T = max_tokens
         self.has_shared = shared_inter > 0 and num_experts in gate_up
@@ -303,7 +324,8 @@ class MoELayer:
         assert self._routed == list(range(len(self._routed))), "single-GPU layer owns experts 0..E-1"
         self._core = ExpertCompute(self.E, self.H, self.I, self.gate_up, self.down, self.R, self._routed, seg_m,
                                    seg_row0, self.row_expert, self.q1, self.rec1, self.s1.data_ptr(), 1, self.device,
-                                   shared=shared, shared_inter=self.Is, online_had=self.online_had)
+                                   shared=shared, shared_inter=self.Is, online_had=self.online_had,
+                                   fuse_silu=self.fuse_silu)
         self.gg1, self.gg2 = self._core.gg1, self._core.gg2
 
     # buffers of the compute core, exposed for tests and benchmarks

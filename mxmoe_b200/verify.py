@@ -74,32 +74,61 @@ def _rel_l2(x: torch.Tensor, ref: torch.Tensor) -> float:
     return float((x.double() - ref.double()).norm().item() / den) if den > 0 else float(x.double().norm().item())
 
 
-def check_problem(a_store, a_stride, a_scale, row0, m, k, tag, w, out_rows: torch.Tensor) -> dict:
-    """One (expert, block) problem: ``out_rows`` = the fp16 [m, N] rows the layer produced for it."""
-    a = decode_rows(a_store, a_stride, row0, m, k, tag)
-    b, sb = decode_weight(w)
-    res = {"rows": int(m), "scheme": w.scheme}
-    if tag == 0:
-        ref = (a.double() @ b.double().t())
-        res["rel_l2"] = _rel_l2(out_rows, ref)
-        res["ok"] = res["rel_l2"] <= REL_L2_FP
-        return res
-    acc = (a @ b.t())                                             # exact integers in fp64
-    dev = out_rows.device
-    # the same problem once more with raw accumulators (operand pointers moved to the first row: C starts at row 0)
-    c_acc = torch.empty((m, w.n), dtype=torch.int32, device=dev)
-    p = gg.Problem(A=a_store.data_ptr() + row0 * a_stride * 2, B=w.data, C=c_acc, M=m, N=w.n, K=k, qparams=w.qparams,
-                   scale_a=a_scale.data_ptr() + row0 * 2, scale_b=w.scale, out_mode=gg.OUT_ACC, lda_bytes=a_stride * 2,
-                   a_expanded=1 if tag == 3 else 0)
+def _rerun(a_store, a_stride, a_scale, row0, m, k, tag, w, out_mode, dtype, dev):
+    """The same problem once more on its own (operand pointers moved to the first row: C starts at row 0)."""
+    c = torch.empty((m, w.n), dtype=dtype, device=dev)
+    p = gg.Problem(A=a_store.data_ptr() + row0 * a_stride * 2, B=w.data, C=c, M=m, N=w.n, K=k, qparams=w.qparams,
+                   scale_a=None if a_scale is None else a_scale.data_ptr() + row0 * 2, scale_b=w.scale,
+                   out_mode=out_mode, lda_bytes=a_stride * 2, a_expanded=1 if tag == 3 else 0)
     g = gg.GroupedGemm([p], device=dev)
     g.run()
     g.check()
+    return c
+
+
+def _silu_rows(gate_up_rows: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` of fp16 rows [m, 2 I] by the stand-alone device kernel, as fp16 [m, I]."""
+    import ctypes as C
+    from . import _lib
+    from .layer import _act_call
+    m, n2 = gate_up_rows.shape
+    dev = gate_up_rows.device
+    h = torch.empty((m, n2 // 2), dtype=torch.float16, device=dev)
+    zeros = torch.zeros(max(m, 2), dtype=torch.int32, device=dev)
+    _act_call(_lib.lib().mxmoe_silu_mul_then_quant, inp=gate_up_rows.contiguous(), in_shared=None, q_store=h, s_store=h,
+              row_expert=zeros, row_token=None, exp_qtag=zeros, exp_row_start=None, exp_q_off=None, exp_s_off=None,
+              signs=None, k=n2 // 2, k_shared=n2 // 2, rows_routed=m, rows_total=m, num_experts=1, rotate=0,
+              rec_stride=n2 // 2, rec_scale_off=-1)
+    return h
+
+
+def check_problem(a_store, a_stride, a_scale, row0, m, k, tag, w, out_rows: torch.Tensor | None,
+                  silu_rows: torch.Tensor | None = None) -> dict:
+    """One (expert, block) problem: ``out_rows`` = the fp16 [m, N] rows the layer produced for it.  A layer that
+    applies silu(gate) * up in the GEMM's epilogue has no such rows: pass ``silu_rows`` = its fp16 [m, N/2] rows
+    instead; the scaled results are then produced by a launch of the same problem on its own, and the layer's rows
+    must equal, bit for bit, what the stand-alone silu-mul kernel makes of them."""
+    a = decode_rows(a_store, a_stride, row0, m, k, tag)
+    b, sb = decode_weight(w)
+    res = {"rows": int(m), "scheme": w.scheme}
+    if out_rows is None:
+        out_rows = _rerun(a_store, a_stride, a_scale, row0, m, k, tag, w, gg.OUT_FP16, torch.float16, silu_rows.device)
+        res["silu_mismatch"] = int((_silu_rows(out_rows).view(torch.int16) != silu_rows.view(torch.int16)).sum().item())
+    if tag == 0:
+        ref = (a.double() @ b.double().t())
+        res["rel_l2"] = _rel_l2(out_rows, ref)
+        res["ok"] = res["rel_l2"] <= REL_L2_FP and res.get("silu_mismatch", 0) == 0
+        return res
+    acc = (a @ b.t())                                             # exact integers in fp64
+    dev = out_rows.device
+    # the same problem once more with raw accumulators
+    c_acc = _rerun(a_store, a_stride, a_scale, row0, m, k, tag, w, gg.OUT_ACC, torch.int32, dev)
     res["acc_mismatch"] = int((c_acc.double() != acc).sum().item())
     sa = a_scale[row0: row0 + m].float().reshape(m, 1)
     prod = (sa * sb.float().reshape(1, -1)).half().float()        # exact product, one rounding to fp16
     ref16 = (acc.float() * prod).half()
     res["out_mismatch"] = int((out_rows.view(torch.int16) != ref16.view(torch.int16)).sum().item())
-    res["ok"] = res["acc_mismatch"] == 0 and res["out_mismatch"] == 0
+    res["ok"] = res["acc_mismatch"] == 0 and res["out_mismatch"] == 0 and res.get("silu_mismatch", 0) == 0
     return res
 
 
@@ -125,11 +154,13 @@ def check_layer(layer, experts: list[int] | None = None, include_shared: bool = 
     H, I = layer.H, layer.I
     o1 = core.o1.view(-1, 2 * I)
     o2 = core.o2.view(-1, H)
+    fused = getattr(core, "fused_silu", False)
     for e in experts:
         m, r0 = counts[e], starts[e]
         if m == 0:
             continue
-        r = check_problem(layer.q1, layer.rec1, layer.s1, r0, m, H, layer._tag1[e], layer.gate_up[e], o1[r0:r0 + m])
+        r = check_problem(layer.q1, layer.rec1, layer.s1, r0, m, H, layer._tag1[e], layer.gate_up[e],
+                          None if fused else o1[r0:r0 + m], silu_rows=core.h16[r0:r0 + m] if fused else None)
         r.update(expert=e, block="gate_up")
         out.append(r)
         r = check_problem(core.q2, core.rec2, core.s2, r0, m, I, core._tag2[e], layer.down[e], o2[r0:r0 + m])

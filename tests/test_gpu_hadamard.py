@@ -51,9 +51,15 @@ def test_layer_with_online_rotation_of_the_down_input(cuda_device):
     ids, wts = workload.make_routing(spec)
     gate_up, down, signs, (gu_s, dn_s) = workload.build_layer_weights(spec, device=cuda_device, online_had=had)
     lay = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens, signs=signs,
-                   rotate=True, device=cuda_device, online_had=had)
+                   rotate=True, device=cuda_device, online_had=had, fuse_silu=False)
     lay.forward(hidden.to(cuda_device), ids.to(cuda_device), wts.to(cuda_device))
     lay.check()
+    # the same layer with silu(gate) * up in the first GEMM's epilogue: the rows that are rotated are the same bits
+    lay_f = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens, signs=signs,
+                     rotate=True, device=cuda_device, online_had=had, fuse_silu=True)
+    lay_f.forward(hidden.to(cuda_device), ids.to(cuda_device), wts.to(cuda_device))
+    lay_f.check()
+    assert lay_f._core.fused_silu and torch.equal(lay_f.o2.view(torch.int16), lay.o2.view(torch.int16))
     R = spec.tokens * spec.topk
     g1 = lay.o1.view(-1, 2 * spec.inter)[:R].cpu()
     rows = lay.o2.view(-1, spec.hidden)[:R].cpu()

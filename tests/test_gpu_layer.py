@@ -64,8 +64,9 @@ def test_layer_matches_fake_quant_loop(cuda_device, scheme, shared, rotate):
     hidden = workload.make_hidden(spec)
     ids, wts = workload.make_routing(spec)
     gate_up, down, signs, (gu_s, dn_s) = workload.build_layer_weights(spec, device=cuda_device)
+    # fuse_silu=False: this test reads the gate_up rows, which the fused epilogue never stores
     lay = MoELayer(spec.num_experts, spec.topk, spec.hidden, spec.inter, gate_up, down, spec.tokens,
-                   shared_inter=spec.shared_inter, signs=signs, rotate=rotate, device=cuda_device)
+                   shared_inter=spec.shared_inter, signs=signs, rotate=rotate, device=cuda_device, fuse_silu=False)
     out = lay.forward(hidden.to(cuda_device), ids.to(cuda_device), wts.to(cuda_device))
     lay.check()
     R = spec.tokens * spec.topk
