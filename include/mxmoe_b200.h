@@ -133,8 +133,11 @@ enum mxmoe_gg_kernel {
   MXMOE_GG_KERNEL_DEFAULT = 0,
   MXMOE_GG_KERNEL_SINGLE = 1, /* one CTA per tile of 128 rows x 256 channels, both operands from shared memory */
   MXMOE_GG_KERNEL_PAIR = 2,   /* tcgen05 cta_group::2, 256 x 256 tiles on clusters of two CTAs */
-  MXMOE_GG_KERNEL_SWAP = 3    /* swapped operands: 128 channels x up to 176 tokens per tile (128 when a problem has
+  MXMOE_GG_KERNEL_SWAP = 3,   /* swapped operands: 128 channels x up to 176 tokens per tile (128 when a problem has
                                  packed 4-bit activations), 4-bit weights converted into tensor memory */
+  MXMOE_GG_KERNEL_SWAP2 = 4   /* the same on CTA pairs (tcgen05 cta_group::2): 256 channels x up to 176 tokens, each CTA
+                                 loads half of the token tile; falls back to SWAP for launches with 32-token tiles or
+                                 packed 4-bit activations */
 };
 int mxmoe_gg_run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_ctas, void* stream);
 

@@ -264,14 +264,17 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   if (d.scheme == mxb::SCH_FP16 || d.scheme == mxb::SCH_W4A16G128) {
     if ((rc = encode_2d(enc, &o->tmX, p.A, f16, 2, K, a_rows, 64, mxb::kTT, s128, "A", idx, lda))) return rc;
     if ((rc = encode_2d(enc, &o->tmXs, p.A, f16, 2, K, a_rows, 64, mxb::kXBoxSmall, s128, "A", idx, lda))) return rc;
+    if ((rc = encode_2d(enc, &o->tmXh, p.A, f16, 2, K, a_rows, 64, mxb::kTT / 2, s128, "A", idx, lda))) return rc;
   } else if (d.scheme == mxb::SCH_W4A4) {
     // packed rows: 64 bytes of K per stage, unswizzled (the converters expand them in shared memory); token tiles
     // of such launches have at most 128 rows, loaded as 32-row boxes
     if ((rc = encode_2d(enc, &o->tmXs, p.A, u8, 1, K / 2, a_rows, 64, mxb::kXBoxSmall, CU_TENSOR_MAP_SWIZZLE_NONE, "A", idx, lda))) return rc;
     o->tmX = o->tmXs;
+    o->tmXh = o->tmXs;
   } else if (d.scheme == mxb::SCH_W8A8 || d.scheme == mxb::SCH_W4A4_XA) {
     if ((rc = encode_2d(enc, &o->tmX, p.A, u8, 1, K, a_rows, 128, mxb::kTT, s128, "A", idx, lda))) return rc;
     if ((rc = encode_2d(enc, &o->tmXs, p.A, u8, 1, K, a_rows, 128, mxb::kXBoxSmall, s128, "A", idx, lda))) return rc;
+    if ((rc = encode_2d(enc, &o->tmXh, p.A, u8, 1, K, a_rows, 128, mxb::kTT / 2, s128, "A", idx, lda))) return rc;
   }
   o->scale_a = d.scale_a; o->scale_b = d.scale_b; o->C = d.C; o->m_dev = d.m_dev; o->row0_dev = d.row0_dev;
   o->M = d.M; o->N = d.N; o->K = d.K; o->row0 = d.row0;
@@ -285,7 +288,7 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   return MXMOE_OK;
 }
 
-enum GGKernel { GGK_DEFAULT = 0, GGK_SINGLE = 1, GGK_PAIR = 2, GGK_SWAP = 3 };
+enum GGKernel { GGK_DEFAULT = 0, GGK_SINGLE = 1, GGK_PAIR = 2, GGK_SWAP = 3, GGK_SWAP2 = 4 };
 
 // which kernel a launch that does not name one uses: MXMOE_GG_KERNEL = swap | single | pair, read when a workspace
 // is prepared (never on the launch path) and kept in the plan
@@ -294,6 +297,7 @@ int default_kernel() {
   if (e && !strcmp(e, "pair")) return GGK_PAIR;
   if (e && !strcmp(e, "single")) return GGK_SINGLE;
   if (e && !strcmp(e, "swap")) return GGK_SWAP;
+  if (e && !strcmp(e, "swap2")) return GGK_SWAP2;
   return GGK_SWAP;
 }
 
@@ -401,14 +405,17 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   auto* probs  = reinterpret_cast<const mxb::GGProblemDev*>(base);
   auto* swp    = reinterpret_cast<const mxb::GGSwapProblemDev*>(base + sizeof(mxb::GGProblemDev) * (size_t)count);
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (kernel == GGK_DEFAULT) kernel = (plan->kernel >= GGK_SINGLE && plan->kernel <= GGK_SWAP) ? plan->kernel : GGK_SWAP;
+  if (kernel == GGK_DEFAULT) kernel = (plan->kernel >= GGK_SINGLE && plan->kernel <= GGK_SWAP2) ? plan->kernel : GGK_SWAP;
   if (plan->flags & 1) {
-    if (kernel != GGK_SWAP) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows or use w4a16_g-1_asym run on the SWAP kernel only");
+    if (kernel != GGK_SWAP && kernel != GGK_SWAP2) return fail(MXMOE_ERR_UNSUPPORTED, "problems that redirect their C rows or use w4a16_g-1_asym run on the SWAP kernel only");
   }
   int n = num_ctas;
   if (n <= 0 || n > st->sm_count) n = st->sm_count;
   if (kernel == GGK_PAIR && n < 2) kernel = GGK_SINGLE;
-  if (kernel == GGK_PAIR)       CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
+  // CTA pairs of the kernel with swapped operands: large token tiles and activations in their final form only
+  if (kernel == GGK_SWAP2 && (n < 2 || (plan->flags & 2) || needs_cvt == 2)) kernel = GGK_SWAP;
+  if (kernel == GGK_SWAP2)      mxb::gg_launch_swap_pair(swp, count, status, needs_cvt, n & ~1, cs);
+  else if (kernel == GGK_PAIR)  CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
   else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, (plan->flags & 2) != 0, n, cs);
   else                          mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
   CUDA_TRY(cudaGetLastError());
@@ -423,7 +430,7 @@ int mxmoe_gg_run(void* workspace, const mxmoe_gg_plan* plan, int num_ctas, void*
 }
 
 int mxmoe_gg_run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_ctas, void* stream) {
-  if (kernel < GGK_DEFAULT || kernel > GGK_SWAP) return fail(MXMOE_ERR_INVALID, "unknown kernel id %d", kernel);
+  if (kernel < GGK_DEFAULT || kernel > GGK_SWAP2) return fail(MXMOE_ERR_INVALID, "unknown kernel id %d", kernel);
   return run_kernel(workspace, plan, kernel, num_ctas < 0 ? -num_ctas : num_ctas, stream);
 }
 

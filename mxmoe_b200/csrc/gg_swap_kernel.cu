@@ -95,11 +95,12 @@ struct Geo {
 constexpr int kFirstCvtWarp = 11;
 constexpr int kAccBarThreads = kEpiWarps * 32 + 32;   // "accumulator drained": epilogue warps arrive, MMA warp syncs
 
-template <int kMode>
+template <int kMode, bool kPair = false>
 struct CfgS {
   static constexpr int kThreads = kFirstCvtWarp * 32 + (kMode ? kCvtWarps * 32 : 0);
-  // threads that meet at a "stage s is ready" named barrier: MMA warp + watcher (+ one converter group)
-  static constexpr int kStageBarThreads = 64 + (kMode ? kCvtGroup * 32 : 0);
+  // threads that meet at a "stage s is ready" named barrier: MMA warp + watcher (+ one converter group; in a CTA
+  // pair the converters of both CTAs report to an mbarrier of the leader that its watcher forwards)
+  static constexpr int kStageBarThreads = 64 + ((kMode && !kPair) ? kCvtGroup * 32 : 0);
 };
 
 // What every role needs to know about one tile, precomputed once per CTA: looking a tile up in the
@@ -123,6 +124,8 @@ struct CtrlS {
   uint64_t xfull[G::kStages];
   uint64_t empty[G::kStages];
   uint64_t tfull[2];
+  uint64_t cvtdone[G::kStages];   // CTA pairs, leader's instance: the converters of both CTAs have filled A slot s
+  uint64_t tempty[2];             // CTA pairs, leader's instance: both CTAs have drained accumulator b
   uint32_t tmem_base;
   int abort_flag;
   int pad[2];
@@ -155,14 +158,17 @@ __device__ __forceinline__ long long tick(bool) { return 0ll; }
 
 // bytes per stage of a weight tile and its coordinates (x step per K block, y) in the weight tensor map
 __device__ __forceinline__ void weight_coords(int scheme, int w_row, uint32_t& wbytes, int& wx_step, int& wy) {
-  if (scheme == SCH_W8A8)         { wbytes = kWSlotBytes;     wx_step = 128; wy = w_row; }
-  else if (scheme == SCH_FP16)    { wbytes = kWSlotBytes;     wx_step = 64;  wy = w_row; }
-  else if (scheme == SCH_W4A4_XA || scheme == SCH_W4A4) { wbytes = kWSlotBytes / 2; wx_step = 64;  wy = w_row; }   // 64 packed bytes per row
-  else                            { wbytes = kWSlotBytes / 4; wx_step = 128; wy = w_row / 4; }   // w4a16: 32 packed rows x 128 B
+  constexpr uint32_t kFull = kWT * kRowBytes;   // 128 channels x 128 bytes of K
+  if (scheme == SCH_W8A8)         { wbytes = kFull;     wx_step = 128; wy = w_row; }
+  else if (scheme == SCH_FP16)    { wbytes = kFull;     wx_step = 64;  wy = w_row; }
+  else if (scheme == SCH_W4A4_XA || scheme == SCH_W4A4) { wbytes = kFull / 2; wx_step = 64;  wy = w_row; }   // 64 packed bytes per row
+  else                            { wbytes = kFull / 4; wx_step = 128; wy = w_row / 4; }   // w4a16: 32 packed rows x 128 B
 }
 
-__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, int tok, int tok_packed) {
-  const Tile ti      = find_tile(sc, count, t);
+// `pair_rank` >= 0: the schedule counts channel tiles of 256 (a CTA pair); this CTA takes the pair_rank-th half
+__device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, int tok, int tok_packed, int pair_rank = -1) {
+  Tile ti            = find_tile(sc, count, t);
+  if (pair_rank >= 0) ti.n_tile = 2 * ti.n_tile + pair_rank;
   const int tile_tok = ti.scheme == SCH_W4A4 ? tok_packed : tok;   // problems with packed activations: shorter tiles
   TileRec r;
   r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12);
@@ -261,13 +267,66 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
       : "r"(d_tmem), "r"(a_tmem), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar)            \
       : "memory")
 
-template <int kV>
+// The same for a CTA pair: one M = 256 MMA over both CTAs' weights and token halves, and a commit that arrives at
+// the "stage may be refilled" barrier of both CTAs.
+#define MXB_MMA_STAGE_SS2(KIND)                                                                             \
+  asm volatile(                                                                                             \
+      "{\n\t"                                                                                               \
+      ".reg .pred p, t;\n\t"                                                                                \
+      ".reg .b64 w0, w1, w2, w3, x0, x1, x2, x3;\n\t"                                                       \
+      ".reg .b32 a1, a2, a3, b1, b2, b3;\n\t"                                                               \
+      "setp.ne.b32 p, %5, 0;\n\t"                                                                           \
+      "setp.eq.b32 t, 0, 0;\n\t"                                                                            \
+      "add.u32 a1, %1, 2;  add.u32 a2, %1, 4;  add.u32 a3, %1, 6;\n\t"                                      \
+      "add.u32 b1, %2, 2;  add.u32 b2, %2, 4;  add.u32 b3, %2, 6;\n\t"                                      \
+      "mov.b64 w0, {%1, %3}; mov.b64 w1, {a1, %3}; mov.b64 w2, {a2, %3}; mov.b64 w3, {a3, %3};\n\t"         \
+      "mov.b64 x0, {%2, %3}; mov.b64 x1, {b1, %3}; mov.b64 x2, {b2, %3}; mov.b64 x3, {b3, %3};\n\t"         \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], w0, x0, %4, p;\n\t"                                    \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], w1, x1, %4, t;\n\t"                                    \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], w2, x2, %4, t;\n\t"                                    \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], w3, x3, %4, t;\n\t"                                    \
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], %7;\n\t" \
+      "}"                                                                                                   \
+      :                                                                                                     \
+      : "r"(d_tmem), "r"(wlo), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar),              \
+        "h"((unsigned short)3)                                                                              \
+      : "memory")
+#define MXB_MMA_STAGE_TS2(KIND)                                                                             \
+  asm volatile(                                                                                             \
+      "{\n\t"                                                                                               \
+      ".reg .pred p, t;\n\t"                                                                                \
+      ".reg .b64 x0, x1, x2, x3;\n\t"                                                                       \
+      ".reg .b32 a1, a2, a3, b1, b2, b3;\n\t"                                                               \
+      "setp.ne.b32 p, %5, 0;\n\t"                                                                           \
+      "setp.eq.b32 t, 0, 0;\n\t"                                                                            \
+      "add.u32 a1, %1, 8;  add.u32 a2, %1, 16;  add.u32 a3, %1, 24;\n\t"                                    \
+      "add.u32 b1, %2, 2;  add.u32 b2, %2, 4;  add.u32 b3, %2, 6;\n\t"                                      \
+      "mov.b64 x0, {%2, %3}; mov.b64 x1, {b1, %3}; mov.b64 x2, {b2, %3}; mov.b64 x3, {b3, %3};\n\t"         \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [%1], x0, %4, p;\n\t"                                  \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [a1], x1, %4, t;\n\t"                                  \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [a2], x2, %4, t;\n\t"                                  \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [a3], x3, %4, t;\n\t"                                  \
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], %7;\n\t" \
+      "}"                                                                                                   \
+      :                                                                                                     \
+      : "r"(d_tmem), "r"(a_tmem), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar),           \
+        "h"((unsigned short)3)                                                                              \
+      : "memory")
+
+template <int kV, bool kPair>
 __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t wlo, uint32_t a_tmem, uint32_t xlo, uint32_t desc_hi,
                                           uint32_t idesc, uint32_t first, uint32_t empty_bar) {
-  if (kV == 0)      { MXB_MMA_STAGE_SS("i8"); }
-  else if (kV == 1) { MXB_MMA_STAGE_SS("f16"); }
-  else if (kV == 2) { MXB_MMA_STAGE_TS("i8"); }
-  else              { MXB_MMA_STAGE_TS("f16"); }
+  if (kPair) {
+    if (kV == 0)      { MXB_MMA_STAGE_SS2("i8"); }
+    else if (kV == 1) { MXB_MMA_STAGE_SS2("f16"); }
+    else if (kV == 2) { MXB_MMA_STAGE_TS2("i8"); }
+    else              { MXB_MMA_STAGE_TS2("f16"); }
+  } else {
+    if (kV == 0)      { MXB_MMA_STAGE_SS("i8"); }
+    else if (kV == 1) { MXB_MMA_STAGE_SS("f16"); }
+    else if (kV == 2) { MXB_MMA_STAGE_TS("i8"); }
+    else              { MXB_MMA_STAGE_TS("f16"); }
+  }
 }
 
 // The MMA warp's main loop over the K blocks of one tile, specialised on the operand kind and on where
@@ -280,7 +339,7 @@ struct MmaCursor {
   int stage;
   uint32_t wlo, xlo, a_tmem, ebar;
 };
-template <int kV, typename G, int kBarThreads>
+template <int kV, typename G, int kBarThreads, bool kPair>
 __device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCursor& c0, int lane, uint32_t d_tmem,
                                               uint32_t idesc, uint32_t desc_hi, int& sidx) {
   for (int kb = 0; kb < nkb; ++kb) {
@@ -288,7 +347,7 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCu
     if (lane == 0) TRACE(TR_MMA_GOT, sidx);
     if (elect_one_sync()) {
       tc_fence_after_sync();
-      mma_stage<kV>(d_tmem, c.wlo, c.a_tmem, c.xlo, desc_hi, idesc, kb > 0 ? 1u : 0u, c.ebar);
+      mma_stage<kV, kPair>(d_tmem, c.wlo, c.a_tmem, c.xlo, desc_hi, idesc, kb > 0 ? 1u : 0u, c.ebar);
     }
     __syncwarp();
     if (lane == 0) TRACE(TR_MMA_ISSUED, sidx);
@@ -301,11 +360,23 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCu
   }
 }
 
-template <int kMode, bool kSmall>
+// kPair: two CTAs of a cluster work on 256 channels x one token tile.  Each loads (and converts) its own 128 weight
+// rows and HALF of the token tile by its own plain TMA loads, the leader (cluster rank 0) issues one M = 256 MMA
+// for both (tcgen05 cta_group::2), each drains its own accumulator: per MAC a CTA writes and reads half as many
+// activation bytes in shared memory, which is what bounds the single-CTA form.  Cross-CTA signals: the token
+// halves complete on the leader's xfull (the cta_group::2 form of the load only redirects the byte count),
+// converters and epilogue warps of both CTAs arrive at the leader's cvtdone / tempty, the leader's commits arrive
+// at empty / tfull of both CTAs.
+template <int kMode, bool kSmall, bool kPair = false>
 __global__ void __launch_bounds__(CfgS<kMode>::kThreads, 1)
 gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatus* __restrict__ status) {
   using G = Geo<kSmall>;
   constexpr bool kCvt = kMode != 0;
+  static_assert(!kPair || (!kSmall && kMode != 2), "CTA pairs: large tiles, activations in their final form");
+  constexpr int kStageBar = CfgS<kMode, kPair>::kStageBarThreads;
+  const int rank  = kPair ? (int)cluster_ctarank() : 0;                      // 0 = the CTA that issues the MMAs
+  const int cta   = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;       // this walker (CTA or CTA pair) ...
+  const int nctas = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;         // ... of so many
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
   uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -332,9 +403,11 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       mbar_init(smem_u32(&ctrl->wfull[s]), 1);
       mbar_init(smem_u32(&ctrl->xfull[s]), 1);
       mbar_init(smem_u32(&ctrl->empty[s]), 1 + (kCvt ? kCvtGroup : 0));
+      mbar_init(smem_u32(&ctrl->cvtdone[s]), 2 * kCvtGroup);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tfull[b]), 1);
+      mbar_init(smem_u32(&ctrl->tempty[b]), 2 * kEpiWarps);
     }
     ctrl->abort_flag = 0;
     fence_mbar_init();
@@ -342,21 +415,28 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   // problems with packed 4-bit activations use token tiles of at most 128 rows: the packed rows of a stage
   // (128 x 64 B) then fit behind the packed weights in the stage's weight slot
   constexpr int kTokPacked = G::kTok > 128 ? 128 : G::kTok;
-  build_sched(sc, problems, count, G::kTok, kWT, kTokPacked);
+  build_sched(sc, problems, count, G::kTok, kPair ? 2 * kWT : kWT, kTokPacked);
   const int total_tiles = sc->total_tiles;
-  const int my_tiles    = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int my_tiles    = total_tiles > cta ? (total_tiles - cta + nctas - 1) / nctas : 0;
+  const int pair_rank   = kPair ? rank : -1;
   for (int i = tid; i < my_tiles && i < kMaxRecs; i += blockDim.x)
-    ctrl->recs[i] = make_rec(sc, count, blockIdx.x + i * gridDim.x, G::kTok, kTokPacked);
+    ctrl->recs[i] = make_rec(sc, count, cta + i * nctas, G::kTok, kTokPacked, pair_rank);
   auto tile_rec = [&](int i) -> TileRec {
     if (i < kMaxRecs) return ctrl->recs[i];
-    return make_rec(sc, count, blockIdx.x + i * gridDim.x, G::kTok, kTokPacked);
+    return make_rec(sc, count, cta + i * nctas, G::kTok, kTokPacked, pair_rank);
   };
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc2(smem_u32(&ctrl->tmem_base), 512);
+      tmem_relinquish2();
+    } else {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // both CTAs' barriers exist before either signals the other's
   tc_fence_after_sync();
 
   const bool prof_on = status->prof_on != 0;   // per-role cycle counters wanted (costs a few percent)
@@ -377,7 +457,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const uint32_t empty0 = smem_u32(&ctrl->empty[0]), wfull0 = smem_u32(&ctrl->wfull[0]), xfull0 = smem_u32(&ctrl->xfull[0]);
       TileRec nrec = tile_rec(0);
       for (int i = 0; ok && i < my_tiles; ++i) {
-        const int t    = blockIdx.x + i * gridDim.x;
+        const int t    = cta + i * nctas;
         const TileS ti = decode_rec(nrec);
         if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
         const GGSwapProblemDev* pr = problems + ti.p;
@@ -405,7 +485,26 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         // measured too and is no faster than one lean loop.
         const int skip_kb = (skip_stage >= n_stage && skip_stage < n_stage + ti.nkb) ? skip_stage - n_stage : -1;
         const bool packed_x = kMode == 2 && ti.scheme == SCH_W4A4;
-        if (big && !packed_x) {
+        if (kPair) {
+          // this CTA's weights and its half of the token tile: rows [rank * npad / 2, +88) of the tile, one box.
+          // The token halves of both CTAs complete on the leader's barrier, which the leader arms for both.
+          constexpr uint32_t kXHalf = (uint32_t)(kTT / 2) * kRowBytes;
+          const int xr = x_row + rank * (((ntok + 15) & ~15) >> 1);
+          for (int kb = 0; kb < ti.nkb; ++kb) {
+            const bool got = wait_bar(empty0 + 8 * stage, phase ^ 1u, abort_flag, 0, tmo);
+            if (!got) { report_s(status, 1, t); ok = false; break; }
+            if (kCvt) {
+              mbar_expect_tx(wfull0 + 8 * stage, wbytes);
+              tma_load_4d(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
+              if (rank == 0) mbar_expect_tx(xfull0 + 8 * stage, 2 * kXHalf);
+            } else {
+              if (rank == 0) mbar_expect_tx(xfull0 + 8 * stage, 2 * (wbytes + kXHalf));
+              tma_load_4d_pair(wslot(stage), &pr->tmW, xfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
+            }
+            tma_load_2d_pair(xslot(stage), &pr->tmXh, xfull0 + 8 * stage, kb * xx_step, xr);
+            if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
+          }
+        } else if (big && !packed_x) {
           // the common case (a full token tile), straight-line: wait, announce, two loads
           for (int kb = 0; kb < ti.nkb; ++kb) {
             const long long c0 = tick(prof_on);
@@ -457,7 +556,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         status->prof[PROF_STAGES]    = n_stage;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 && rank == 0) {
     // ===== MMA issuer (all lanes walk the loop and meet the named barriers, the elected lane issues) =====
     int acc = 0;
     long long w_oper = 0, w_acc = 0, w_issue = 0;
@@ -478,29 +577,45 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
       const long long ca = tick(prof_on);
-      if (i >= 2) nbar_sync(G::kBarAcc0 + acc, kAccBarThreads);     // the epilogue has drained this accumulator (tile i - 2)
+      // the epilogue has drained this accumulator (tile i - 2); in a CTA pair both CTAs' epilogues have
+      if (kPair) {
+        if (i >= 2 && !warp_wait_bar(smem_u32(&ctrl->tempty[acc]), (uint32_t)((i >> 1) - 1) & 1u, abort_flag, lane, tmo)) {
+          if (lane == 0) report_s(status, 2, cta + i * nctas);
+          break;
+        }
+        tc_fence_after_sync();
+      } else if (i >= 2) {
+        nbar_sync(G::kBarAcc0 + acc, kAccBarThreads);
+      }
       w_acc += tick(prof_on) - ca;
       const int npad        = (ti.ntok + 15) & ~15;
       const uint32_t d_tmem = tmem_base + acc * G::kAccCols;
       const bool is_int     = is_int_scheme(ti.scheme);
       const bool from_tmem  = kCvt && is_cvt_scheme(ti.scheme);
-      const uint32_t idesc  = is_int ? idesc_i8(kWT, npad) : idesc_f16(kWT, npad);
+      constexpr int kMmaM   = kPair ? 2 * kWT : kWT;
+      const uint32_t idesc  = is_int ? idesc_i8(kMmaM, npad) : idesc_f16(kMmaM, npad);
       const int variant     = (from_tmem ? 2 : 0) + (is_int ? 0 : 1);
-      if (variant == 0)      mma_tile_loop<0, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      else if (variant == 1) mma_tile_loop<1, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      else if (variant == 2) mma_tile_loop<2, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      else                   mma_tile_loop<3, G, CfgS<kMode>::kStageBarThreads>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      if (elect_one_sync()) mma_commit(smem_u32(&ctrl->tfull[acc]));
+      if (variant == 0)      mma_tile_loop<0, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else if (variant == 1) mma_tile_loop<1, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else if (variant == 2) mma_tile_loop<2, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else                   mma_tile_loop<3, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      if (elect_one_sync()) {
+        if (kPair) mma_commit2(smem_u32(&ctrl->tfull[acc]), 3);
+        else       mma_commit(smem_u32(&ctrl->tfull[acc]));
+      }
       __syncwarp();
       acc ^= 1;
     }
     // consume the "drained" arrivals of the last two tiles, so that no named barrier is left half-way
-    for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(G::kBarAcc0 + (i & 1), kAccBarThreads);
+    if (!kPair)
+      for (int i = max(my_tiles - 2, 0); i < my_tiles; ++i) nbar_sync(G::kBarAcc0 + (i & 1), kAccBarThreads);
     if (blockIdx.x == 0 && lane == 0) {
       status->prof[PROF_MMA_WAIT_OPER] = w_oper;
       status->prof[PROF_MMA_WAIT_ACC]  = w_acc;
       status->prof[PROF_MMA_ISSUE]     = w_issue;
     }
+  } else if (warp == 1) {
+    // (the second CTA of a pair issues nothing)
   } else if (warp < 6 || (warp > 6 && warp < kFirstCvtWarp)) {
     // ===== epilogue (TMEM lane quarter = warp % 4; lane = output channel, columns = tokens) =====
     // warps 2-5 take the even 32-token chunks of a tile, warps 7-10 the odd ones
@@ -515,7 +630,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     bool dead = false;   // a wait ran out: walk the remaining tiles without waiting or working
     TileRec nrec = tile_rec(0);
     for (int i = 0; i < my_tiles; ++i) {
-      const int t    = blockIdx.x + i * gridDim.x;
+      const int t    = cta + i * nctas;
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);   // issued now, needed at the next tile
       const GGSwapProblemDev* pr = problems + ti.p;
@@ -548,7 +663,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       }
       if (dead) {
         // keep the MMA warp's bar.sync on this accumulator balanced, do nothing else
-        nbar_arrive(G::kBarAcc0 + acc, kAccBarThreads);
+        if (kPair) { if (lane == 0) mbar_arrive_leader_relaxed(smem_u32(&ctrl->tempty[acc])); }
+        else nbar_arrive(G::kBarAcc0 + acc, kAccBarThreads);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
         continue;
@@ -683,7 +799,12 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         store_chunk(stg, ch);
       }
       tc_fence_before_sync();
-      nbar_arrive(G::kBarAcc0 + acc, kAccBarThreads);
+      if (kPair) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_leader_relaxed(smem_u32(&ctrl->tempty[acc]));
+      } else {
+        nbar_arrive(G::kBarAcc0 + acc, kAccBarThreads);
+      }
       w_store += tick(prof_on) - c1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -693,6 +814,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       status->prof[PROF_EPI_WAIT]  = w_epi;
       status->prof[PROF_EPI_STORE] = w_store;
     }
+  } else if (warp == 6 && rank != 0) {
+    // (the leader's watcher serves the pair)
   } else if (warp == 6) {
     // ===== watcher: forwards "stage ready" from the mbarriers to the MMA warp's named barriers =====
     int stage = 0;
@@ -701,7 +824,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     int wit = 0;   // stages forwarded so far (timeline tracing only)
     TileRec nrec = tile_rec(0);
     for (int i = 0; i < my_tiles; ++i) {
-      const int t    = blockIdx.x + i * gridDim.x;
+      const int t    = cta + i * nctas;
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);
       for (int kb = 0; kb < ti.nkb; ++kb) {
@@ -709,7 +832,11 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           // with converter warps in the CTA the stage's converter group waits for the weights (and arrives at the
           // named barrier itself); without them this warp does
           bool ok = warp_wait_bar(smem_u32(&ctrl->xfull[stage]), phase, abort_flag, lane, tmo);
-          if (ok && !kCvt) ok = warp_wait_bar(smem_u32(&ctrl->wfull[stage]), phase, abort_flag, lane, tmo);
+          if (ok && !kCvt && !kPair) ok = warp_wait_bar(smem_u32(&ctrl->wfull[stage]), phase, abort_flag, lane, tmo);
+          if (ok && kCvt && kPair) {   // the converter groups of both CTAs have filled their A slots
+            ok = warp_wait_bar(smem_u32(&ctrl->cvtdone[stage]), phase, abort_flag, lane, tmo);
+            tc_fence_after_sync();
+          }
           if (!ok) {
             if (lane == 0) report_s(status, 3, t);
             dead = true;
@@ -717,7 +844,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         }
         if (lane == 0) TRACE(TR_WATCH, wit);
         ++wit;
-        nbar_arrive(G::kBarStage0 + stage, CfgS<kMode>::kStageBarThreads);   // always: the MMA warp's bar.sync must complete
+        nbar_arrive(G::kBarStage0 + stage, kStageBar);   // always: the MMA warp's bar.sync must complete
         if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -738,7 +865,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     long long w_cwait = 0, w_cwork = 0;
     TileRec nrec = tile_rec(0);
     for (int i = 0; i < my_tiles; ++i) {
-      const int t    = blockIdx.x + i * gridDim.x;
+      const int t    = cta + i * nctas;
       const TileS ti = decode_rec(nrec);
       if (i + 1 < my_tiles) nrec = tile_rec(i + 1);
       const GGSwapProblemDev* pr = problems + ti.p;
@@ -772,7 +899,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           }
         }
         if (dead) {
-          nbar_arrive(G::kBarStage0 + s_cur, CfgS<kMode>::kStageBarThreads);   // the MMA warp's bar.sync must complete
+          // the MMA warp's bar.sync (the leader's wait, in a pair) must complete
+          if (kPair) { if (lane == 0) mbar_arrive_leader_relaxed(smem_u32(&ctrl->cvtdone[s_cur])); }
+          else nbar_arrive(G::kBarStage0 + s_cur, kStageBar);
           continue;
         }
         const long long c1 = tick(prof_on);
@@ -833,7 +962,12 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
           w_cwork += tick(prof_on) - c1;
         }
         if (q == 0 && lane == 0) TRACE(TR_CVT_DONE, (int)it);
-        nbar_arrive(G::kBarStage0 + s_cur, CfgS<kMode>::kStageBarThreads);
+        if (kPair) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive_leader_relaxed(smem_u32(&ctrl->cvtdone[s_cur]));
+        } else {
+          nbar_arrive(G::kBarStage0 + s_cur, kStageBar);
+        }
       }
     }
     if (blockIdx.x == 0 && warp == kFirstCvtWarp && lane == 0) {
@@ -851,10 +985,12 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  if (kPair) cluster_sync_all();   // the other CTA may still signal this CTA's barriers or read its shared memory
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    if (kPair) tmem_dealloc2(tmem_base, 512);
+    else       tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -867,6 +1003,22 @@ cudaError_t configure_one() {
 template <int kMode, bool kSmall>
 void launch_one(const GGSwapProblemDev* problems, int count, GGStatus* status, int num_ctas, cudaStream_t stream) {
   gg_swap_kernel<kMode, kSmall><<<num_ctas, CfgS<kMode>::kThreads, smem_bytes_swap<Geo<kSmall>>(), stream>>>(problems, count, status);
+}
+template <int kMode>
+void launch_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int num_ctas, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3((unsigned)(num_ctas & ~1), 1, 1);
+  cfg.blockDim           = dim3(CfgS<kMode>::kThreads, 1, 1);
+  cfg.dynamicSmemBytes   = smem_bytes_swap<Geo<false>>();
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs    = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, gg_swap_kernel<kMode, false, true>, problems, count, status);
 }
 }  // namespace
 
@@ -883,7 +1035,18 @@ cudaError_t gg_configure_swap() {
   if ((e = configure_one<2, false>()) != cudaSuccess) return e;
   if ((e = configure_one<0, true>()) != cudaSuccess) return e;
   if ((e = configure_one<1, true>()) != cudaSuccess) return e;
-  return configure_one<2, true>();
+  if ((e = configure_one<2, true>()) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gg_swap_kernel<0, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                smem_bytes_swap<Geo<false>>())) != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gg_swap_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              smem_bytes_swap<Geo<false>>());
+}
+
+// CTA pairs (cta_group::2): large token tiles, activations in their final form (cvt_mode 0 or 1)
+void gg_launch_swap_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
+                         cudaStream_t stream) {
+  if (cvt_mode) launch_pair<1>(problems, count, status, num_ctas, stream);
+  else          launch_pair<0>(problems, count, status, num_ctas, stream);
 }
 
 void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles,

@@ -60,6 +60,7 @@ struct alignas(128) GGSwapProblemDev {
   CUtensorMap tmW;    // weights: 128 channels x one stage of K (packed for the 4-bit schemes)
   CUtensorMap tmX;    // activations: kTT rows x 128 bytes of K
   CUtensorMap tmXs;   // activations: kXBoxSmall rows x 128 bytes of K
+  CUtensorMap tmXh;   // activations: kTT / 2 rows x 128 bytes of K (each CTA of a pair loads half of the token tile)
   const __half* scale_a;
   const __half* scale_b;
   void* C;
@@ -73,7 +74,7 @@ struct alignas(128) GGSwapProblemDev {
   int silu_inter;          // OUT_SILU: I (the weight tile interleaves 16 gate rows with 16 up rows, four times); else 0
   int pad[9];
 };
-static_assert(sizeof(GGSwapProblemDev) == 512, "GGSwapProblemDev layout");
+static_assert(sizeof(GGSwapProblemDev) == 640, "GGSwapProblemDev layout");
 
 // Workspace: [GGStatus (256 B)] [GGProblemDev x count] [GGSwapProblemDev x count]
 struct alignas(256) GGStatus {
@@ -122,6 +123,8 @@ cudaError_t gg_configure_pair();
 // kernel with swapped operands (gg_swap_kernel.cu): weights from tensor memory / shared memory as the M side,
 // token tiles of up to 176 rows (ring of 5 stages) or, with `small_tiles`, of up to 32 rows (ring of 10 stages)
 // as the N side
+void gg_launch_swap_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
+                         cudaStream_t stream);
 void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles,
                     int num_ctas, cudaStream_t stream);
 cudaError_t gg_configure_swap();

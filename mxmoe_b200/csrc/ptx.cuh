@@ -227,6 +227,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kLeaderMask) : "memory");
 }
+// The same without release semantics, for signals whose payload is not in generic memory (tensor-memory stores
+// ordered by tcgen05.wait::st + tcgen05.fence::before_thread_sync, operands written by TMA): a release at cluster
+// scope costs the arriving warp about 2 500 cycles, per pipeline stage.
+__device__ __forceinline__ void mbar_arrive_leader_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kLeaderMask) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_all() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }
@@ -236,6 +242,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* 
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       :
       : "r"(dst_smem), "l"(tmap), "r"(bar & kLeaderMask), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst_smem, const void* tmap, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst_smem), "l"(tmap), "r"(bar & kLeaderMask), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {

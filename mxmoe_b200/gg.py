@@ -146,7 +146,7 @@ class GroupedGemm:
             _lib.check(_lib.lib().mxmoe_gg_debug(self._ws, timeout_ms, skip_stage, current_stream_ptr()))
 
 
-KERNELS = {"default": 0, "single": 1, "pair": 2, "swap": 3}
+KERNELS = {"default": 0, "single": 1, "pair": 2, "swap": 3, "swap2": 4}
 
 PROF_NAMES = ("total", "producer_wait", "mma_wait_operands", "mma_wait_accumulator", "mma_issue", "epilogue_wait",
               "epilogue_store", "converter_wait", "converter_work", "tiles", "stages", "mma_gap")

@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 REL_L2 = 1e-3
 
 
-@pytest.fixture(autouse=True, params=["swap", "swap-small", "pair", "single"])
+@pytest.fixture(autouse=True, params=["swap", "swap-small", "swap2", "pair", "single"])
 def gg_kernel(request, monkeypatch):
     """Every test of this file runs once per kernel: swapped operands (128 channels x up to 176 tokens, 4-bit
     weights through tensor memory; "swap-small" forces its geometry for few rows - 32-token tiles, ring of 10 stages -
@@ -262,7 +262,7 @@ def test_redirected_c_rows(cuda_device, gg_kernel):
                                 c_row0_dev=cst.data_ptr() + 4 * e))
     g = gg.GroupedGemm(probs)
     assert g._plan.flags & 1
-    if gg_kernel != "swap":
+    if gg_kernel not in ("swap", "swap2"):
         with pytest.raises(MxMoEError):
             g.run()
         return

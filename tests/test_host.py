@@ -46,7 +46,7 @@ def test_no_device_is_an_error_not_a_fallback():
     p = (_lib.GGProblem * 1)()
     rc = lib.mxmoe_gg_prepare(ctypes.byref(p), 1, 256, 4096, None, ctypes.byref(plan))
     assert rc == 6 and b"no CUDA device" in lib.mxmoe_last_error()
-    assert lib.mxmoe_gg_workspace_bytes(10) == 256 + 10 * (384 + 512)
+    assert lib.mxmoe_gg_workspace_bytes(10) == 256 + 10 * (384 + 640)
 
 
 def test_argument_validation_without_device():
