@@ -284,7 +284,14 @@ typedef struct mxmoe_route_args {
   int32_t* slot_row;       /* [T * topk]; -1 where the expert id is out of range */
   int32_t* workspace;      /* mxmoe_route_workspace_bytes() bytes */
   size_t workspace_bytes;
-  int32_t num_tokens, topk, num_experts, reserved_;
+  int32_t num_tokens, topk, num_experts;
+  int32_t num_ids;         /* with id_map: the ids in topk_ids lie in [0, num_ids); 0 = num_experts */
+  /* Optional renumbering, applied to every id as it is read (NULL = none): id -> id_map[v] with
+   * v = rep_base ? rep_base[id] + token % rep_count[id] : id.  An expert-parallel layer deals the rows of an expert
+   * that is replicated on several ranks to its copies by token index and numbers the copies rank-major. */
+  const int32_t* id_map;
+  const int32_t* rep_base;
+  const int32_t* rep_count;
 } mxmoe_route_args;
 
 size_t mxmoe_route_workspace_bytes(int num_tokens, int topk, int num_experts);

@@ -99,7 +99,8 @@ class RouteArgs(C.Structure):
         ("topk_ids", C.c_void_p), ("counts", C.c_void_p), ("row_start", C.c_void_p), ("row_expert", C.c_void_p),
         ("row_token", C.c_void_p), ("slot_row", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
-        ("num_tokens", C.c_int32), ("topk", C.c_int32), ("num_experts", C.c_int32), ("reserved_", C.c_int32),
+        ("num_tokens", C.c_int32), ("topk", C.c_int32), ("num_experts", C.c_int32), ("num_ids", C.c_int32),
+        ("id_map", C.c_void_p), ("rep_base", C.c_void_p), ("rep_count", C.c_void_p),
     ]
 
 

@@ -674,7 +674,10 @@ int mxmoe_route_topk(const mxmoe_route_args* a, void* stream) {
   r.topk_ids = a->topk_ids; r.counts = a->counts; r.row_start = a->row_start; r.row_expert = a->row_expert;
   r.row_token = a->row_token; r.slot_row = a->slot_row; r.workspace = a->workspace;
   r.workspace_bytes = a->workspace_bytes;
-  r.num_tokens = a->num_tokens; r.topk = a->topk; r.num_experts = a->num_experts; r.reserved = 0;
+  r.num_tokens = a->num_tokens; r.topk = a->topk; r.num_experts = a->num_experts;
+  r.num_ids = a->num_ids > 0 ? a->num_ids : a->num_experts;
+  r.id_map = a->id_map; r.rep_base = a->rep_base; r.rep_count = a->rep_count;
+  if (r.rep_base && (!r.id_map || !r.rep_count)) return fail(MXMOE_ERR_INVALID, "rep_base needs id_map and rep_count");
   CUDA_TRY(mxb::launch_route(r, static_cast<cudaStream_t>(stream)));
   return MXMOE_OK;
 }
@@ -699,7 +702,10 @@ int mxmoe_route_topk_static(const mxmoe_route_args* a, void* stream) {
   r.topk_ids = a->topk_ids; r.counts = a->counts; r.row_start = a->row_start; r.row_expert = a->row_expert;
   r.row_token = a->row_token; r.slot_row = a->slot_row; r.workspace = scratch;
   r.workspace_bytes = mxb::route_static_scratch_ints() * sizeof(int);
-  r.num_tokens = a->num_tokens; r.topk = a->topk; r.num_experts = a->num_experts; r.reserved = 0;
+  r.num_tokens = a->num_tokens; r.topk = a->topk; r.num_experts = a->num_experts;
+  r.num_ids = a->num_ids > 0 ? a->num_ids : a->num_experts;
+  r.id_map = a->id_map; r.rep_base = a->rep_base; r.rep_count = a->rep_count;
+  if (r.rep_base && (!r.id_map || !r.rep_count)) return fail(MXMOE_ERR_INVALID, "rep_base needs id_map and rep_count");
   CUDA_TRY(mxb::launch_route(r, static_cast<cudaStream_t>(stream)));
   return MXMOE_OK;
 }

@@ -21,6 +21,17 @@ constexpr int kChunk   = 1024;  // (token, slot) pairs per block
 constexpr int kThreads = 256;
 constexpr int kMaxE    = 512;
 
+// expert of pair `idx` = (token, slot), renumbered if the caller gave a map; -1 for an id out of range
+__device__ __forceinline__ int read_id(const RouteArgs& a, int idx) {
+  int e = a.topk_ids[idx];
+  if (a.id_map) {
+    if (e < 0 || e >= a.num_ids) return -1;
+    if (a.rep_base) e = a.rep_base[e] + (idx / a.topk) % a.rep_count[e];
+    e = a.id_map[e];
+  }
+  return (e < 0 || e >= a.num_experts) ? -1 : e;
+}
+
 __global__ void __launch_bounds__(kThreads) route_count_kernel(RouteArgs a) {
   __shared__ int hist[kMaxE];
   const int n = a.num_tokens * a.topk;
@@ -30,8 +41,8 @@ __global__ void __launch_bounds__(kThreads) route_count_kernel(RouteArgs a) {
   for (int i = threadIdx.x; i < kChunk; i += kThreads) {
     const int idx = base + i;
     if (idx < n) {
-      const int e = a.topk_ids[idx];
-      if (e >= 0 && e < a.num_experts) atomicAdd(&hist[e], 1);
+      const int e = read_id(a, idx);
+      if (e >= 0) atomicAdd(&hist[e], 1);
     }
   }
   __syncthreads();
@@ -106,7 +117,7 @@ __global__ void __launch_bounds__(kThreads) route_scatter_kernel(RouteArgs a) {
   for (int p = 0; p < kPerWarp; p += 32) {
     const int idx = wstart + p + lane;
     int e = -1;
-    if (idx < n) { e = a.topk_ids[idx]; if (e < 0 || e >= E) e = -1; }
+    if (idx < n) e = read_id(a, idx);
     const unsigned m = __match_any_sync(0xffffffffu, e);
     if (e >= 0 && (m & ((1u << lane) - 1)) == 0) wbase[warp][e] += __popc(m);
     __syncwarp();
@@ -149,7 +160,7 @@ __global__ void __launch_bounds__(kThreads) route_scatter_kernel(RouteArgs a) {
   for (int p = 0; p < kPerWarp; p += 32) {
     const int idx = wstart + p + lane;
     int e = -1;
-    if (idx < n) { e = a.topk_ids[idx]; if (e < 0 || e >= E) e = -1; }
+    if (idx < n) e = read_id(a, idx);
     const unsigned m  = __match_any_sync(0xffffffffu, e);
     const unsigned lt = m & ((1u << lane) - 1);
     if (e >= 0) {

@@ -15,7 +15,14 @@ struct RouteArgs {
   int* slot_row;         // [T*topk] sorted row of every (token, slot); -1 for an invalid expert id
   int* workspace;        // per-block histograms
   size_t workspace_bytes;
-  int num_tokens, topk, num_experts, reserved;
+  int num_tokens, topk, num_experts;
+  int num_ids;           // range of the ids in topk_ids when id_map is given (0: num_experts)
+  // optional renumbering applied to every id as it is read: id -> id_map[ rep_base ? rep_base[id] + token % rep_count[id] : id ]
+  // (expert-parallel layers: an expert replicated on several ranks is dealt to its copies by token index, then the
+  // copies are renumbered rank-major)
+  const int* id_map;
+  const int* rep_base;
+  const int* rep_count;
 };
 
 size_t route_workspace_bytes(int num_tokens, int topk, int num_experts);

@@ -174,7 +174,6 @@ class EPMoELayer:
             vbase[e] = vbase[e - 1] + reps[e - 1]
         self.vbase = torch.tensor(vbase, **i32)                       # original expert -> its first virtual expert
         self.vrep = torch.tensor(reps, **i32)
-        self.slot_token = torch.arange(T, **i32).repeat_interleave(k)  # token of every (token, slot) pair
 
         # weights of the local experts, keyed by their NEW ids (the shared expert keeps key E)
         local_orig = [self.vorig[inverse[n]] for n in range(lo, hi)]
@@ -199,6 +198,10 @@ class EPMoELayer:
         f.slot_row = torch.zeros(T * k, **i32)
         f.route_ws = torch.zeros(_lib.lib().mxmoe_route_workspace_bytes(T * k, 1, E) // 4 + 1, **i32)
         f.tag1 = torch.tensor(self._tag1, **i32)
+        # the routing kernels renumber the ids as they read them: original expert -> one of its copies (by token
+        # index) -> the copy's rank-major id
+        f.id_map, f.num_ids = self.remap, E0
+        f.rep_base, f.rep_count = (self.vbase, self.vrep) if self.replicated else (None, None)
         used = set(self._tag1[:E]) | ({self._tag1[E]} if self.has_shared else set())
         self.tq = TokenQuant(T, H, used, spec.rotate, signs, dev)
 
@@ -245,7 +248,6 @@ class EPMoELayer:
         # all ranks' per-expert row counts: the payload slots of the sync block (p2p) or an all-gather buffer (nccl)
         self.counts_all = self.sync[128:] if self.transport == "p2p" else torch.zeros(self.world * E, **i32)
         self.counts_host = torch.zeros(self.world, E, dtype=torch.int32).pin_memory()
-        self.ids_new = torch.zeros(T, k, **i32)
         # device-side plan of the p2p transport
         self.range_lo = torch.tensor([r[0] for r in self.ranges] + [E], **i32)
         self.seg_src_row0 = torch.zeros(max(nseg, 1), **i32)
@@ -283,15 +285,6 @@ class EPMoELayer:
             ev.record()
             marks.append((name, ev))
 
-    def _renumber(self, topk_ids: torch.Tensor) -> None:
-        """Original expert ids -> new ids (virtual expert chosen by token index, then the rank-major numbering)."""
-        flat = topk_ids.reshape(-1)
-        if not self.replicated:
-            torch.index_select(self.remap, 0, flat, out=self.ids_new.view(-1))
-            return
-        virt = torch.index_select(self.vbase, 0, flat) + torch.remainder(self.slot_token, torch.index_select(self.vrep, 0, flat))
-        torch.index_select(self.remap, 0, virt, out=self.ids_new.view(-1))
-
     def _sync(self, payload: torch.Tensor | None = None):
         """Every rank's earlier kernels on this stream (their peer stores included) are complete before any
         rank's later kernels start: flags in peer-mapped memory, ordered on the stream, no host involvement and
@@ -313,8 +306,7 @@ class EPMoELayer:
             if self._core is None:
                 self._build_core(hidden)
             self._mark(marks, "start")
-            self._renumber(topk_ids)
-            f.route(self.ids_new)
+            f.route(topk_ids)
             t = self.tq.run(hidden)
             self._mark(marks, "route+quant")
             self._sync(payload=f.counts)
@@ -362,8 +354,7 @@ class EPMoELayer:
             if self._core is None:
                 self._build_core(hidden)
             self._mark(marks, "start")
-            self._renumber(topk_ids)
-            f.route(self.ids_new)
+            f.route(topk_ids)
             t = self.tq.run(hidden)
             f.gather(t, T * k, self.send.view(-1), self.rec, None, rec_scale_off=self.P)
             self._mark(marks, "route+quant+gather")

@@ -354,6 +354,11 @@ class MoELayer:
                                                  self.slot_row.data_ptr())
         a.workspace, a.workspace_bytes = self.route_ws.data_ptr(), self.route_ws.numel() * 4
         a.num_tokens, a.topk, a.num_experts = T, k, self.E
+        id_map = getattr(self, "id_map", None)          # expert-parallel front end: renumbering inside the routing kernels
+        if id_map is not None:
+            a.id_map, a.num_ids = id_map.data_ptr(), self.num_ids
+            if self.rep_base is not None:
+                a.rep_base, a.rep_count = self.rep_base.data_ptr(), self.rep_count.data_ptr()
         _lib.check(_lib.lib().mxmoe_route_topk(C.byref(a), current_stream_ptr()))
 
     def _row_args(self, rows: int, q_store: torch.Tensor, rec_stride: int, s_store: torch.Tensor | None,

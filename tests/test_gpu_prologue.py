@@ -180,6 +180,42 @@ def test_device_routing_matches_stable_sort(cuda_device, t, e, k):
     assert torch.equal(lay.slot_row.cpu().long(), inv)
 
 
+@pytest.mark.parametrize("replicated", [False, True])
+def test_device_routing_renumbers_ids_as_it_reads_them(cuda_device, replicated):
+    """The optional map of the routing arguments: original expert -> (a copy chosen by token index ->) new id.  The
+    result must be the stable sort of the ids a host-side renumbering gives."""
+    from mxmoe_b200 import _lib
+    from mxmoe_b200.layer import MoELayer
+    rng = np.random.default_rng(11)
+    t, e0, k = 777, 12, 3
+    dev = cuda_device
+    ids = _routing(rng, t, e0, k)
+    reps = rng.integers(1, 4, e0) if replicated else np.ones(e0, dtype=np.int64)
+    base = np.concatenate([[0], np.cumsum(reps)[:-1]])
+    e = int(reps.sum())
+    perm = rng.permutation(e)
+    tok = torch.arange(t).repeat_interleave(k)
+    flat = ids.reshape(-1).long()
+    virt = torch.from_numpy(base)[flat] + tok % torch.from_numpy(reps)[flat]
+    new = torch.from_numpy(perm)[virt]
+    lay = MoELayer.__new__(MoELayer)
+    lay.E, lay.R = e, t * k
+    i32 = dict(dtype=torch.int32, device=dev)
+    lay.counts, lay.row_start = torch.zeros(e, **i32), torch.zeros(e + 1, **i32)
+    lay.row_expert, lay.slot_row = torch.zeros(t * k, **i32), torch.zeros(t * k, **i32)
+    lay.row_token = torch.zeros(t * k, dtype=torch.int64, device=dev)
+    lay.route_ws = torch.zeros(_lib.lib().mxmoe_route_workspace_bytes(t * k, 1, e) // 4 + 1, **i32)
+    lay.id_map, lay.num_ids = torch.from_numpy(perm.astype(np.int32)).to(dev), e0
+    lay.rep_base = torch.from_numpy(base.astype(np.int32)).to(dev) if replicated else None
+    lay.rep_count = torch.from_numpy(reps.astype(np.int32)).to(dev) if replicated else None
+    lay.route(ids.to(dev))
+    torch.cuda.synchronize()
+    srt, order = torch.sort(new, stable=True)
+    assert torch.equal(lay.counts.cpu().long(), torch.bincount(srt, minlength=e))
+    assert torch.equal(lay.row_expert.cpu().long(), srt)
+    assert torch.equal(lay.row_token.cpu(), order // k)
+
+
 def test_combine(cuda_device):
     from mxmoe_b200 import _lib
     from mxmoe_b200.gg import current_stream_ptr

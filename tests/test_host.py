@@ -33,7 +33,7 @@ def test_struct_layouts_match_header():
     assert ctypes.sizeof(_lib.EpPlanArgs) == 9 * 8 + 6 * 4
     assert ctypes.sizeof(_lib.EpDispatchArgs) == 7 * 8 + 6 * 4
     assert ctypes.sizeof(_lib.ActArgs) == 12 * 8 + 8 * 4
-    assert ctypes.sizeof(_lib.RouteArgs) == 8 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.RouteArgs) == 11 * 8 + 4 * 4
     assert ctypes.sizeof(_lib.TokenQuantArgs) == 8 * 8 + 4 * 4
 
 
