@@ -86,6 +86,11 @@ typedef struct mxmoe_gg_problem {
                                 row0).  Lets an expert-parallel rank store a segment's results straight into the
                                 buffer of the rank the rows came from, at their place in that rank's order; C may
                                 then be peer memory (plain stores). */
+  const int64_t* c_row_ptrs; /* optional (default kernel, fp16 results, N and ldc multiples of 8): device table indexed
+                                like the rows of A; row r of the result is stored at the ADDRESS c_row_ptrs[r] (+ the
+                                column offset) instead of into C.  The rows of one problem may then go to different
+                                buffers, e.g. to the ranks its rows came from; each row leaves in 256-byte pieces
+                                through the copy engine.  Addresses must be 16-byte aligned. */
 } mxmoe_gg_problem;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -337,14 +342,23 @@ typedef struct mxmoe_ep_plan_args {
   const int32_t* counts_all; /* [world][num_experts] */
   const int32_t* range_lo;   /* [world + 1] */
   int32_t world, rank, num_experts, experts_local, recv_capacity;
-  int32_t reserved_;
-  int32_t* seg_m;           /* [world * experts_local] rows of segment (source rank, local expert), source-major */
+  int32_t layout;           /* order of the rows in a receive store: 0 = (source rank, expert), 1 = (expert, source rank) */
+  int32_t* seg_m;           /* [world * experts_local] rows of segment (source rank, local expert), indexed source-major */
   int32_t* seg_row0;        /* first row of the segment in this rank's receive store */
   int32_t* seg_src_row0;    /* first row of the same rows in the source rank's expert-sorted order */
   int32_t* recv_row_expert; /* [recv_capacity] expert of every received row */
   int32_t* total_recv;      /* [0] rows received (clamped), [1] rows wanted when that exceeded the capacity */
   int32_t* dst_row0;        /* [num_experts] first row of this rank's rows for expert e in its owner's store */
   int32_t* exp_owner;       /* [num_experts] */
+  /* layout 1, optional (all or none): with an expert's rows contiguous whatever rank sent them, the grouped GEMMs
+   * take ONE problem per local expert (m_dev = exp_m + j, row0_dev = exp_row0 + j) instead of one per (source rank,
+   * expert), and the down projection finds the destination of every row in row_dst (mxmoe_gg_problem.c_row_ptrs). */
+  int32_t* exp_m;           /* [experts_local] */
+  int32_t* exp_row0;        /* [experts_local] */
+  int64_t* row_dst;         /* [recv_capacity] address of the row's result in the home-coming buffer of its source rank */
+  const uint64_t* peer_ret; /* [world] device array: home-coming buffer of every rank as mapped here */
+  int32_t ret_row_bytes;
+  int32_t reserved_;
 } mxmoe_ep_plan_args;
 
 typedef struct mxmoe_ep_dispatch_args {

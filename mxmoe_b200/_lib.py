@@ -41,7 +41,7 @@ class GGProblem(C.Structure):
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
         ("a_rows", C.c_int32), ("row0", C.c_int32), ("ldc", C.c_int32),
         ("q", QParams), ("out_mode", C.c_int32), ("lda_bytes", C.c_int32), ("sa_stride", C.c_int32),
-        ("a_expanded", C.c_int32), ("reserved_", C.c_int32), ("c_row0_dev", C.c_void_p),
+        ("a_expanded", C.c_int32), ("reserved_", C.c_int32), ("c_row0_dev", C.c_void_p), ("c_row_ptrs", C.c_void_p),
     ]
 
 
@@ -53,9 +53,11 @@ class EpPlanArgs(C.Structure):
     _fields_ = [
         ("counts_all", C.c_void_p), ("range_lo", C.c_void_p),
         ("world", C.c_int32), ("rank", C.c_int32), ("num_experts", C.c_int32), ("experts_local", C.c_int32),
-        ("recv_capacity", C.c_int32), ("reserved_", C.c_int32),
+        ("recv_capacity", C.c_int32), ("layout", C.c_int32),
         ("seg_m", C.c_void_p), ("seg_row0", C.c_void_p), ("seg_src_row0", C.c_void_p), ("recv_row_expert", C.c_void_p),
         ("total_recv", C.c_void_p), ("dst_row0", C.c_void_p), ("exp_owner", C.c_void_p),
+        ("exp_m", C.c_void_p), ("exp_row0", C.c_void_p), ("row_dst", C.c_void_p), ("peer_ret", C.c_void_p),
+        ("ret_row_bytes", C.c_int32), ("reserved_", C.c_int32),
     ]
 
 

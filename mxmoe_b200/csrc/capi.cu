@@ -281,9 +281,13 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   o->scheme = d.scheme; o->out_mode = d.out_mode; o->ldc = d.ldc; o->sa_stride = d.sa_stride;
   o->c_row0_dev = p.c_row0_dev;
   o->one_group  = (d.scheme == mxb::SCH_W4A16G128 && p.q.gsize == -1) ? 1 : 0;
+  o->c_row_ptrs = p.c_row_ptrs;
   // results addressed through c_row0_dev are the expert-parallel combine: they land in a peer's buffer
   const bool aligned = p.N % 8 == 0 && d.ldc % 8 == 0 && ((uintptr_t)d.C & 15) == 0;
-  o->bulk_out = (d.out_mode == mxb::OUT_FP16 && aligned && (p.c_row0_dev != nullptr || bulk_everywhere)) ? 1 : 0;
+  o->bulk_out = (d.out_mode == mxb::OUT_FP16 && aligned && (p.c_row0_dev != nullptr || p.c_row_ptrs != nullptr || bulk_everywhere)) ? 1 : 0;
+  if (p.c_row_ptrs && !o->bulk_out)
+    return fail(MXMOE_ERR_INVALID, "problem %d: c_row_ptrs needs fp16 results with N and ldc multiples of 8", idx);
+  if (p.c_row_ptrs && p.c_row0_dev) return fail(MXMOE_ERR_INVALID, "problem %d: c_row_ptrs and c_row0_dev exclude each other", idx);
   o->silu_inter = silu;
   return MXMOE_OK;
 }
@@ -365,7 +369,7 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept], bulk_everywhere);
     if (rc) return rc;
     // redirected C rows and the per-channel 4-bit weight-only scheme exist in the SWAP kernel only
-    if (problems[i].c_row0_dev || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1) ||
+    if (problems[i].c_row0_dev || problems[i].c_row_ptrs || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1) ||
         problems[i].out_mode == mxb::OUT_SILU) redirect = true;
     if (problems[i].M > max_rows) max_rows = problems[i].M;
     if (dev[kept].scheme == mxb::SCH_W4A4) needs_cvt = 2;
@@ -753,6 +757,10 @@ int mxmoe_ep_plan(const mxmoe_ep_plan_args* a, void* stream) {
   if (!a->counts_all || !a->range_lo || !a->seg_m || !a->seg_row0 || !a->seg_src_row0 || !a->recv_row_expert ||
       !a->total_recv || !a->dst_row0 || !a->exp_owner)
     return fail(MXMOE_ERR_INVALID, "null table");
+  if (a->layout != 0 && a->layout != 1) return fail(MXMOE_ERR_INVALID, "unknown receive-store layout %d", a->layout);
+  const int n_opt = (a->exp_m != nullptr) + (a->exp_row0 != nullptr) + (a->row_dst != nullptr) + (a->peer_ret != nullptr);
+  if (n_opt != 0 && (n_opt != 4 || a->layout != 1 || a->ret_row_bytes <= 0 || a->ret_row_bytes % 16))
+    return fail(MXMOE_ERR_INVALID, "exp_m, exp_row0, row_dst and peer_ret go together, with layout 1 and a row size that is a multiple of 16");
   static_assert(sizeof(mxmoe_ep_plan_args) == sizeof(mxb::EpPlanArgs), "plan args layout");
   mxb::EpPlanArgs k;
   std::memcpy(&k, a, sizeof(k));

@@ -29,9 +29,16 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
     const int d   = owner_of(a.range_lo, G, e);
     const int dlo = a.range_lo[d], dhi = a.range_lo[d + 1];
     int off = 0;
-    for (int s = 0; s < me; ++s)
-      for (int j = dlo; j < dhi; ++j) off += a.counts_all[s * E + j];
-    for (int j = dlo; j < e; ++j) off += a.counts_all[me * E + j];
+    if (a.layout == 0) {
+      for (int s = 0; s < me; ++s)
+        for (int j = dlo; j < dhi; ++j) off += a.counts_all[s * E + j];
+      for (int j = dlo; j < e; ++j) off += a.counts_all[me * E + j];
+    } else {
+      // (expert, source rank): behind all rows of the owner's earlier experts and the lower ranks' rows for e
+      for (int s = 0; s < G; ++s)
+        for (int j = dlo; j < e; ++j) off += a.counts_all[s * E + j];
+      for (int s = 0; s < me; ++s) off += a.counts_all[s * E + e];
+    }
     a.dst_row0[e]  = off;
     a.exp_owner[e] = d;
   }
@@ -40,9 +47,15 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
   for (int i = tid; i < nseg; i += kPlanThreads) {
     const int s = i / el, j = i - s * el;
     int row0 = 0;
-    for (int s2 = 0; s2 < s; ++s2)
-      for (int j2 = lo; j2 < hi; ++j2) row0 += a.counts_all[s2 * E + j2];
-    for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s * E + j2];
+    if (a.layout == 0) {
+      for (int s2 = 0; s2 < s; ++s2)
+        for (int j2 = lo; j2 < hi; ++j2) row0 += a.counts_all[s2 * E + j2];
+      for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s * E + j2];
+    } else {
+      for (int s2 = 0; s2 < G; ++s2)
+        for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s2 * E + j2];
+      for (int s2 = 0; s2 < s; ++s2) row0 += a.counts_all[s2 * E + lo + j];
+    }
     int src0 = 0;   // the same rows in rank s's expert-sorted order
     for (int e2 = 0; e2 < lo + j; ++e2) src0 += a.counts_all[s * E + e2];
     int m = a.counts_all[s * E + lo + j];
@@ -52,6 +65,19 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
     a.seg_m[i]        = m;
     a.seg_row0[i]     = row0;
     a.seg_src_row0[i] = src0;
+  }
+  if (a.exp_m) {
+    for (int j = tid; j < el; j += kPlanThreads) {
+      int row0 = 0, m = 0;
+      for (int s = 0; s < G; ++s) {
+        for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s * E + j2];
+        m += a.counts_all[s * E + lo + j];
+      }
+      if (row0 >= a.recv_capacity) m = 0;
+      else if (row0 + m > a.recv_capacity) m = a.recv_capacity - row0;
+      a.exp_m[j]    = m;
+      a.exp_row0[j] = row0;
+    }
   }
   if (tid == 0) {
     int total = 0;
@@ -118,6 +144,10 @@ __global__ void ep_fill_row_expert_kernel(EpPlanArgs a) {
   const int e = lo + (i % el);
   const int row0 = a.seg_row0[i], m = a.seg_m[i];
   for (int r = threadIdx.x; r < m; r += blockDim.x) a.recv_row_expert[row0 + r] = e;
+  if (a.row_dst) {
+    const int64_t base = (int64_t)a.peer_ret[i / el] + (int64_t)a.seg_src_row0[i] * a.ret_row_bytes;
+    for (int r = threadIdx.x; r < m; r += blockDim.x) a.row_dst[row0 + r] = base + (int64_t)r * a.ret_row_bytes;
+  }
 }
 
 // One warp per expert-sorted row of this rank: packed row + its scale -> record in the owner's receive store.

@@ -13,7 +13,7 @@ struct EpPlanArgs {
   const int* counts_all;   // [world][num_experts] rows rank s routes to expert e (all-gathered)
   const int* range_lo;     // [world + 1]
   int world, rank, num_experts, experts_local, recv_capacity;
-  int pad_;
+  int layout;              // order of the receive store: 0 = (source rank, expert), 1 = (expert, source rank)
   // receive side of this rank: segment i = (source rank i / experts_local, local expert i % experts_local)
   int* seg_m;              // [world * experts_local] rows of the segment
   int* seg_row0;           // first row of the segment in this rank's receive store
@@ -23,6 +23,14 @@ struct EpPlanArgs {
   // send side of this rank
   int* dst_row0;           // [num_experts] first row of this rank's rows for expert e in the owner's receive store
   int* exp_owner;          // [num_experts] rank that owns expert e
+  // layout 1 (optional, all four or none): an expert's rows are contiguous whatever rank they came from
+  int* exp_m;              // [experts_local] rows of local expert j
+  int* exp_row0;           // [experts_local] its first row in the receive store
+  int64_t* row_dst;        // [recv_capacity] where the result of received row r goes: address of its row in the
+                           // home-coming buffer of the rank it came from
+  const uint64_t* peer_ret;   // [world] home-coming buffer of every rank as mapped into this process
+  int ret_row_bytes;       // bytes of one row of those buffers
+  int pad_;
 };
 
 struct EpDispatchArgs {

@@ -639,6 +639,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const int64_t crow0 = ti.c_row;   // its row in C
       const int N = pr->N, ldc = pr->ldc, out_mode = pr->out_mode;
       const bool bulk     = pr->bulk_out != 0;
+      const int64_t* row_ptrs = pr->c_row_ptrs;
       const int silu      = pr->silu_inter;   // > 0: lanes 0-15 of the warp hold gate rows, lanes 16-31 the up rows of the same 16 columns of C
       const bool is_int   = is_int_scheme(ti.scheme);
       const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
@@ -698,6 +699,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       };
 #pragma unroll 1
       for (int ch = half; ch < nchunk; ch += 2) {
+        // row-wide stores to per-row addresses: this lane's row of the chunk, fetched before the accumulator load
+        int64_t row_ptr = 0;
+        if (row_ptrs && lane < 8 && ch * 32 + q * 8 + lane < ntok) row_ptr = __ldg(row_ptrs + crow0 + ch * 32 + q * 8 + lane);
         uint32_t v[32];
         tmem_ld_32x32(taddr + ch * 32, v);
         tmem_ld_wait();
@@ -783,7 +787,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             const int row = q * 8 + lane, tk = ch * 32 + row;
             const int n0  = ti.n_tile * kWT;
             if (tk < ntok) {
-              __half* dst = reinterpret_cast<__half*>(pr->C) + (crow0 + tk) * ldc + n0;
+              // the row's place: in C, or wherever the problem's table of row addresses says
+              __half* dst = row_ptrs ? reinterpret_cast<__half*>(row_ptr) + n0
+                                     : reinterpret_cast<__half*>(pr->C) + (crow0 + tk) * ldc + n0;
               bulk_store_row(dst, gb + row * 256, (uint32_t)min(kWT, N - n0) * 2u);
             }
             bulk_commit();

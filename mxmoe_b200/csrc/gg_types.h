@@ -68,11 +68,12 @@ struct alignas(128) GGSwapProblemDev {
   const int* row0_dev;
   int M, N, K, row0;
   int scheme, out_mode, ldc, sa_stride;
+  const int64_t* c_row_ptrs;   // optional: result row r goes to the ADDRESS c_row_ptrs[r] (rows numbered like A's)
   const int* c_row0_dev;   // optional: rows of C start at *c_row0_dev instead of at row0
   int one_group;           // w4a16: one (scale, zero) pair per channel for the whole of K (per-channel scheme)
   int bulk_out;            // fp16 results leave as whole 256-byte rows through the copy engine (outputs in a peer's memory)
   int silu_inter;          // OUT_SILU: I (the weight tile interleaves 16 gate rows with 16 up rows, four times); else 0
-  int pad[9];
+  int pad[7];
 };
 static_assert(sizeof(GGSwapProblemDev) == 640, "GGSwapProblemDev layout");
 

@@ -225,6 +225,7 @@ class EPMoELayer:
             self._h_ret = symm.rendezvous(self.ret, grp)
             self.peer_recv = torch.tensor([int(p) for p in self._h_recv.buffer_ptrs], dtype=torch.int64, device=dev)
             self.peer_ret = [int(p) for p in self._h_ret.buffer_ptrs]
+            self.peer_ret_dev = torch.tensor(self.peer_ret, dtype=torch.int64, device=dev)
             self.send = None
             # sync block: arrival flags, error word, epoch, and one payload slot per rank that receives the ranks'
             # per-expert row counts (see mxmoe_ep_sync)
@@ -240,7 +241,12 @@ class EPMoELayer:
             self.ret = torch.zeros(self.R_send, H, **f16)        # expert outputs coming home
 
         nseg = self.world * (hi - lo)
-        self.seg_expert = [e for _ in range(self.world) for e in range(lo, hi)]
+        # p2p: the receive store is ordered (expert, source rank), so the grouped GEMMs take one problem per local
+        # expert; nccl (all-to-all): (source rank, expert), one problem per segment
+        self.expert_major = self.transport == "p2p"
+        self.seg_expert = list(range(lo, hi)) if self.expert_major else [e for _ in range(self.world) for e in range(lo, hi)]
+        self.exp_tab = torch.zeros(2, max(hi - lo, 1), **i32)                   # [rows; first row] of every local expert
+        self.row_dst = torch.zeros(self.R_recv, dtype=torch.int64, device=dev)  # where every received row's result goes
         self.seg_tab = torch.zeros(2, max(nseg, 1), **i32)                      # [m; row0]
         self.seg_tab_host = torch.zeros(2, max(nseg, 1), dtype=torch.int32).pin_memory()
         self.seg_expert_dev = torch.tensor(self.seg_expert or [0], **i32)
@@ -266,18 +272,16 @@ class EPMoELayer:
         if self.has_shared:
             a_ptr, sa_ptr = self.tq.rows_of(self._tag1[self.E], hidden)
             shared = {"tokens": spec.tokens, "a_ptr": a_ptr, "sa_ptr": sa_ptr}
-        down_out = None
-        if self.transport == "p2p":
-            # segment i = (source rank s, local expert j): its results go to rank s's home-coming buffer, at the rows
-            # the segment has in rank s's expert-sorted order
-            el = self.ranges[self.rank][1] - self.ranges[self.rank][0]
-            down_out = [(self.peer_ret[i // el], self.seg_src_row0.data_ptr() + 4 * i) for i in range(self.world * el)]
+        p2p = self.transport == "p2p"
+        # p2p: one problem per local expert over the rows of all source ranks; every result row goes to the address
+        # the plan put into row_dst (its row in the home-coming buffer of the rank it came from)
+        tab = self.exp_tab if p2p else self.seg_tab
         self._core = ExpertCompute(
             self.E, spec.hidden, spec.inter, self._gate_up, self._down, self.R_recv, self.seg_expert,
-            self.seg_tab[0], self.seg_tab[1], self.recv_row_expert, self.recv.view(-1), self.rec,
+            tab[0], tab[1], self.recv_row_expert, self.recv.view(-1), self.rec,
             self.recv.data_ptr() + self.P * 2, self.rec, self.device, shared=shared, shared_inter=spec.shared_inter,
             tag_fn=self._tag_fn,
-            down_out=down_out, rows_dev=self.total_recv if self.transport == "p2p" else None)
+            down_row_ptrs=self.row_dst if p2p else None, rows_dev=self.total_recv if p2p else None)
 
     def _mark(self, marks, name):
         if self.profile:
@@ -318,6 +322,9 @@ class EPMoELayer:
             pa.seg_m, pa.seg_row0 = self.seg_tab[0].data_ptr(), self.seg_tab[1].data_ptr()
             pa.seg_src_row0, pa.recv_row_expert = self.seg_src_row0.data_ptr(), self.recv_row_expert.data_ptr()
             pa.total_recv, pa.dst_row0, pa.exp_owner = self.total_recv.data_ptr(), self.dst_row0.data_ptr(), self.exp_owner.data_ptr()
+            pa.layout = 1
+            pa.exp_m, pa.exp_row0, pa.row_dst = self.exp_tab[0].data_ptr(), self.exp_tab[1].data_ptr(), self.row_dst.data_ptr()
+            pa.peer_ret, pa.ret_row_bytes = self.peer_ret_dev.data_ptr(), H * 2
             _lib.check(lib.mxmoe_ep_plan(C.byref(pa), current_stream_ptr()))
             da = _lib.EpDispatchArgs()
             da.peer_base, da.row_expert, da.row_token = self.peer_recv.data_ptr(), f.row_expert.data_ptr(), f.row_token.data_ptr()

@@ -54,6 +54,7 @@ class Problem:
     sa_stride: int = 0        # distance between per-token scales in elements (0 = contiguous)
     a_expanded: int = 0       # w4a4: activations stored as one byte 16*q per code
     c_row0_dev: object = None  # device pointer (int) to the first row of C, when it differs from the rows of A
+    c_row_ptrs: object = None  # int64 device table: address of every result row (indexed like the rows of A)
 
     def fill(self, c: _lib.GGProblem) -> None:
         a_bits, w_bits, gsize, sym = self.qparams
@@ -68,6 +69,7 @@ class Problem:
         c.sa_stride = int(self.sa_stride)
         c.a_expanded = int(self.a_expanded)
         c.c_row0_dev = _ptr(self.c_row0_dev)
+        c.c_row_ptrs = _ptr(self.c_row_ptrs)
 
     def flops(self) -> int:
         return 2 * self.M * self.N * self.K

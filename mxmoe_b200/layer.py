@@ -87,7 +87,8 @@ class ExpertCompute:
                  q1: torch.Tensor, rec1: int, scale1_ptr: int, scale1_stride: int, device,
                  shared: dict | None = None, shared_inter: int = 0, tag_fn=internal_tag,
                  down_out: list | None = None, rows_dev: torch.Tensor | None = None,
-                 online_had: torch.Tensor | None = None, fuse_silu: bool | None = None):
+                 online_had: torch.Tensor | None = None, fuse_silu: bool | None = None,
+                 down_row_ptrs: torch.Tensor | None = None):
         self.E, self.H, self.I, self.Is = num_experts, hidden, inter, shared_inter
         fuse_silu = default_fuse_silu() if fuse_silu is None else fuse_silu
         self.R, self.device = rows_cap, device
@@ -96,6 +97,8 @@ class ExpertCompute:
         self.shared = shared
         # down_out[i] = (C pointer, pointer to the first C row) of segment i: the down projection then stores the
         # segment's rows there (e.g. straight into the buffer of the rank they came from) instead of into o2.
+        # down_row_ptrs: int64 device table with the address of every row's result (rows of one segment may then go
+        # to different buffers); excludes down_out.
         # rows_dev: live row count on the device (sizes the work of the second quantiser)
         self.rows_dev = rows_dev
         dev, R, H, I = device, rows_cap, hidden, inter
@@ -146,7 +149,7 @@ class ExpertCompute:
             p2.append(Problem(A=self.q2, B=w2.data, C=c_out, M=R, N=H, K=I, qparams=w2.qparams,
                               scale_a=self.s2 if self._tag2[e] else None, scale_b=w2.scale,
                               a_rows=R, lda_bytes=self.rec2 * 2, m_dev=m_ptr, row0_dev=r_ptr,
-                              a_expanded=1 if self._tag2[e] == 3 else 0, c_row0_dev=c_row0))
+                              a_expanded=1 if self._tag2[e] == 3 else 0, c_row0_dev=c_row0, c_row_ptrs=down_row_ptrs))
         if shared is not None:
             T, Is, E = shared["tokens"], shared_inter, num_experts
             w1, w2 = gate_up[E], down[E]

@@ -234,6 +234,34 @@ def test_bad_arguments_raise(cuda_device):
         gg.GroupedGemm([p])
 
 
+def test_result_rows_at_given_addresses(cuda_device, gg_kernel):
+    """c_row_ptrs: every result row is stored at the address its table entry gives (here: a permutation of the rows
+    of one buffer and a second buffer for every third row), whole rows through the copy engine."""
+    if gg_kernel not in ("swap", "swap2"):
+        pytest.skip("per-row destinations exist in the kernel with swapped operands")
+    rng = np.random.default_rng(77)
+    for bits, (m, n, k) in ((8, (300, 384, 256)), (4, (177, 2048, 1408)), (8, (5, 256, 128))):
+        c = util.WxAxCase(rng, m, n, k, bits, expanded=(bits == 4))
+        p = c.problem(cuda_device)
+        buf0 = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda_device)
+        buf1 = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda_device)
+        perm = rng.permutation(m)
+        which = (np.arange(m) % 3 == 0)
+        ptrs = np.where(which, buf1.data_ptr(), buf0.data_ptr()).astype(np.int64) + perm.astype(np.int64) * n * 2
+        table = torch.from_numpy(ptrs).to(cuda_device)
+        p.c_row_ptrs = table
+        util.run([p])
+        got0, got1 = buf0.cpu().numpy(), buf1.cpu().numpy()
+        for r in range(m):
+            got = (got1 if which[r] else got0)[perm[r]]
+            assert np.array_equal(got.view(np.uint16), c.ref[r].view(np.uint16)), (bits, r)
+        assert np.isnan(c.C.cpu().numpy()).all()          # C itself is not written
+        rows_written = np.zeros(m, dtype=int)
+        rows_written[perm[~which]] += 1
+        assert np.array_equal(~np.isnan(got0).any(axis=1), rows_written == 1)
+
+
+
 def test_redirected_c_rows(cuda_device, gg_kernel):
     """c_row0_dev: the rows of C start somewhere else than the rows of A (what lets an expert-parallel rank store
     a segment straight into another rank's buffer).  Only the kernel with swapped operands offers it."""

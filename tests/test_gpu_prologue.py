@@ -303,3 +303,64 @@ def test_gate_topk_matches_torch(cuda_device, t, e, k, dtype, renorm):
         want_w = want_w / want_w.sum(dim=-1, keepdim=True)
     assert torch.equal(ids.cpu().long(), want_i), "expert ids differ from torch.topk"
     assert torch.allclose(wts.cpu(), want_w, rtol=2e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("world,rank", [(1, 0), (3, 1), (4, 3)])
+def test_device_exchange_plan_expert_major(cuda_device, world, rank):
+    """Layout 1 of mxmoe_ep_plan: the receive store is ordered (expert, source rank).  Segment tables, the per-expert
+    tables, the senders' first rows, the expert of every received row and the address of every row's result against
+    plain numpy on made-up counts."""
+    import ctypes as C
+    from mxmoe_b200 import _lib
+    from mxmoe_b200.ep import expert_ranges
+    from mxmoe_b200.gg import current_stream_ptr
+    rng = np.random.default_rng(17 + world)
+    E, row_bytes = 13, 64
+    counts = rng.integers(0, 40, (world, E)).astype(np.int64)
+    counts[:, 2] = 0
+    ranges = expert_ranges(E, world)
+    lo, hi = ranges[rank]
+    el = hi - lo
+    total = int(counts[:, lo:hi].sum())
+    cap = total + 5
+    i32 = dict(dtype=torch.int32, device=cuda_device)
+    bases = [1 << 40 | (s << 30) for s in range(world)]              # made-up buffer addresses, never dereferenced
+    t = {
+        "counts_all": torch.tensor(counts.reshape(-1), **i32), "range_lo": torch.tensor([r[0] for r in ranges] + [E], **i32),
+        "seg_m": torch.zeros(max(world * el, 1), **i32), "seg_row0": torch.zeros(max(world * el, 1), **i32),
+        "seg_src_row0": torch.zeros(max(world * el, 1), **i32), "recv_row_expert": torch.full((cap,), -1, **i32),
+        "total_recv": torch.zeros(2, **i32), "dst_row0": torch.zeros(E, **i32), "exp_owner": torch.zeros(E, **i32),
+        "exp_m": torch.zeros(max(el, 1), **i32), "exp_row0": torch.zeros(max(el, 1), **i32),
+        "row_dst": torch.zeros(cap, dtype=torch.int64, device=cuda_device),
+        "peer_ret": torch.tensor(bases, dtype=torch.int64, device=cuda_device),
+    }
+    a = _lib.EpPlanArgs()
+    for name, ten in t.items():
+        setattr(a, name, ten.data_ptr())
+    a.world, a.rank, a.num_experts, a.experts_local, a.recv_capacity = world, rank, E, el, cap
+    a.layout, a.ret_row_bytes = 1, row_bytes
+    _lib.check(_lib.lib().mxmoe_ep_plan(C.byref(a), current_stream_ptr()))
+    torch.cuda.synchronize()
+    exp_m = [int(counts[:, lo + j].sum()) for j in range(el)]
+    exp_row0 = [int(counts[:, lo:lo + j].sum()) for j in range(el)]
+    assert t["exp_m"].tolist()[:el] == exp_m and t["exp_row0"].tolist()[:el] == exp_row0
+    seg_row0 = [exp_row0[j] + int(counts[:s, lo + j].sum()) for s in range(world) for j in range(el)]
+    seg_m = [int(counts[s, lo + j]) for s in range(world) for j in range(el)]
+    assert t["seg_row0"].tolist()[:world * el] == seg_row0 and t["seg_m"].tolist()[:world * el] == seg_m
+    assert t["total_recv"].tolist() == [total, 0]
+    owner = [next(r for r, (a0, b0) in enumerate(ranges) if a0 <= e < b0) for e in range(E)]
+    want_dst = []
+    for e in range(E):
+        dlo, _ = ranges[owner[e]]
+        want_dst.append(int(counts[:, dlo:e].sum() + counts[:rank, e].sum()))
+    assert t["dst_row0"].tolist() == want_dst
+    want_exp = np.full(cap, -1)
+    want_ptr = np.zeros(cap, dtype=np.int64)
+    for s in range(world):
+        for j in range(el):
+            r0, m = seg_row0[s * el + j], seg_m[s * el + j]
+            want_exp[r0:r0 + m] = lo + j
+            src0 = int(counts[s, :lo + j].sum())
+            want_ptr[r0:r0 + m] = bases[s] + (src0 + np.arange(m)) * row_bytes
+    assert np.array_equal(t["recv_row_expert"].cpu().numpy(), want_exp)
+    assert np.array_equal(t["row_dst"].cpu().numpy()[:total], want_ptr[:total])

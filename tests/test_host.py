@@ -28,9 +28,9 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layouts_match_header():
     assert ctypes.sizeof(_lib.QParams) == 16
-    assert ctypes.sizeof(_lib.GGProblem) == 128
+    assert ctypes.sizeof(_lib.GGProblem) == 136
     assert ctypes.sizeof(_lib.GGPlan) == 16
-    assert ctypes.sizeof(_lib.EpPlanArgs) == 9 * 8 + 6 * 4
+    assert ctypes.sizeof(_lib.EpPlanArgs) == 13 * 8 + 8 * 4
     assert ctypes.sizeof(_lib.EpDispatchArgs) == 7 * 8 + 6 * 4
     assert ctypes.sizeof(_lib.ActArgs) == 12 * 8 + 8 * 4
     assert ctypes.sizeof(_lib.RouteArgs) == 11 * 8 + 4 * 4
