@@ -18,9 +18,19 @@ __device__ __forceinline__ int owner_of(const int* range_lo, int world, int e) {
 
 // One block.  counts_all[s][e]: rows rank s routes to expert e; experts are numbered so that rank r owns
 // [range_lo[r], range_lo[r+1]).
+constexpr int kPlanSmemInts = 8192;   // counts of up to this many (rank, expert) pairs are staged in shared memory
+
 __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
+  __shared__ int s_counts[kPlanSmemInts];
   const int tid = threadIdx.x;
   const int E = a.num_experts, G = a.world, me = a.rank;
+  // every table below is a sum over a few hundred of the G x E counts: read them from HBM once
+  const int* counts = a.counts_all;
+  if (G * E <= kPlanSmemInts) {
+    for (int i = tid; i < G * E; i += kPlanThreads) s_counts[i] = a.counts_all[i];
+    __syncthreads();
+    counts = s_counts;
+  }
   const int lo = a.range_lo[me], hi = a.range_lo[me + 1];
   const int el = hi - lo;
   // where my rows for expert e start in the receive store of e's owner: behind the rows of the lower ranks
@@ -31,13 +41,13 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
     int off = 0;
     if (a.layout == 0) {
       for (int s = 0; s < me; ++s)
-        for (int j = dlo; j < dhi; ++j) off += a.counts_all[s * E + j];
-      for (int j = dlo; j < e; ++j) off += a.counts_all[me * E + j];
+        for (int j = dlo; j < dhi; ++j) off += counts[s * E + j];
+      for (int j = dlo; j < e; ++j) off += counts[me * E + j];
     } else {
       // (expert, source rank): behind all rows of the owner's earlier experts and the lower ranks' rows for e
       for (int s = 0; s < G; ++s)
-        for (int j = dlo; j < e; ++j) off += a.counts_all[s * E + j];
-      for (int s = 0; s < me; ++s) off += a.counts_all[s * E + e];
+        for (int j = dlo; j < e; ++j) off += counts[s * E + j];
+      for (int s = 0; s < me; ++s) off += counts[s * E + e];
     }
     a.dst_row0[e]  = off;
     a.exp_owner[e] = d;
@@ -49,16 +59,16 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
     int row0 = 0;
     if (a.layout == 0) {
       for (int s2 = 0; s2 < s; ++s2)
-        for (int j2 = lo; j2 < hi; ++j2) row0 += a.counts_all[s2 * E + j2];
-      for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s * E + j2];
+        for (int j2 = lo; j2 < hi; ++j2) row0 += counts[s2 * E + j2];
+      for (int j2 = lo; j2 < lo + j; ++j2) row0 += counts[s * E + j2];
     } else {
       for (int s2 = 0; s2 < G; ++s2)
-        for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s2 * E + j2];
-      for (int s2 = 0; s2 < s; ++s2) row0 += a.counts_all[s2 * E + lo + j];
+        for (int j2 = lo; j2 < lo + j; ++j2) row0 += counts[s2 * E + j2];
+      for (int s2 = 0; s2 < s; ++s2) row0 += counts[s2 * E + lo + j];
     }
     int src0 = 0;   // the same rows in rank s's expert-sorted order
-    for (int e2 = 0; e2 < lo + j; ++e2) src0 += a.counts_all[s * E + e2];
-    int m = a.counts_all[s * E + lo + j];
+    for (int e2 = 0; e2 < lo + j; ++e2) src0 += counts[s * E + e2];
+    int m = counts[s * E + lo + j];
     // never let a segment reach past the store: the rows beyond the capacity are dropped and reported
     if (row0 >= a.recv_capacity) m = 0;
     else if (row0 + m > a.recv_capacity) m = a.recv_capacity - row0;
@@ -70,8 +80,8 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
     for (int j = tid; j < el; j += kPlanThreads) {
       int row0 = 0, m = 0;
       for (int s = 0; s < G; ++s) {
-        for (int j2 = lo; j2 < lo + j; ++j2) row0 += a.counts_all[s * E + j2];
-        m += a.counts_all[s * E + lo + j];
+        for (int j2 = lo; j2 < lo + j; ++j2) row0 += counts[s * E + j2];
+        m += counts[s * E + lo + j];
       }
       if (row0 >= a.recv_capacity) m = 0;
       else if (row0 + m > a.recv_capacity) m = a.recv_capacity - row0;
@@ -82,7 +92,7 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(EpPlanArgs a) {
   if (tid == 0) {
     int total = 0;
     for (int s = 0; s < G; ++s)
-      for (int j = lo; j < hi; ++j) total += a.counts_all[s * E + j];
+      for (int j = lo; j < hi; ++j) total += counts[s * E + j];
     a.total_recv[0] = total < a.recv_capacity ? total : a.recv_capacity;
     if (total > a.recv_capacity) atomicExch(&a.total_recv[1], total);   // overflow: rows wanted
   }
@@ -167,7 +177,16 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs d, Toke
   unsigned char* rec = reinterpret_cast<unsigned char*>(d.peer_base[d.exp_owner[e]]) + (int64_t)dst_row * d.rec_bytes;
   uint4* dst        = reinterpret_cast<uint4*>(rec);
   const int n16     = (d.k / pack) >> 3;
-  for (int c = lane; c < n16; c += 32) dst[c] = __ldg(s + c);
+  // all loads of the record are issued before the first (peer) store
+  for (int c0 = 0; c0 < n16; c0 += 32 * 8) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j * 32 + lane < n16) v[j] = __ldg(s + c0 + j * 32 + lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j * 32 + lane < n16) dst[c0 + j * 32 + lane] = v[j];
+  }
   if (tag != 0 && lane == 0) *reinterpret_cast<__half*>(rec + d.scale_off_bytes) = (tag == 1 ? t.s8 : t.s4)[tok];
 }
 
