@@ -113,6 +113,8 @@ typedef struct mxmoe_gg_plan {
   int32_t count;     /* problems kept (empty ones are dropped) */
   int32_t needs_cvt; /* kernel variant: 0 no 4-bit operand, 1 4-bit weights only, 2 packed 4-bit activations too */
   int32_t flags;     /* bit 0: a problem redirects its C rows (c_row0_dev) or uses w4a16_g-1_asym: only the SWAP kernel can run it;
+                        bit 2: a problem uses an optional result form (out_mode 2, c_row0_dev, c_row_ptrs): the launch runs the
+                               kernel instance that has them, the weight tensor maps have rank 4;
                         bit 1: SWAP kernel with token tiles of 32 rows and a ring of 10 stages (set by prepare when no
                         problem has more than 32 rows; the caller may set or clear it before mxmoe_gg_run, e.g. set
                         it when the row counts come from device memory and are known to be small on average) */

@@ -120,7 +120,8 @@ int encode_2d(EncodeTiledFn enc, CUtensorMap* out, const void* base, CUtensorMap
 // the same columns of C: dimensions (inner, 16 rows, gate|up, I / 16 groups), box (box_inner, 16, 2, 4).
 int encode_w(EncodeTiledFn enc, CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
              uint64_t inner_elems, uint64_t rows, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw,
-             int silu_inter, int idx) {
+             int silu_inter, int idx, bool rank4) {
+  if (!rank4) return encode_2d(enc, out, base, dt, elem_bytes, inner_elems, rows, box_inner, box_rows, sw, "B", idx);
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
     return fail(MXMOE_ERR_INVALID, "problem %d: B pointer %p is not 16-byte aligned", idx, base);
   const uint64_t pitch = inner_elems * (uint64_t)elem_bytes;
@@ -232,8 +233,9 @@ int build_problem(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, mxb::GG
 
 // The same problem for the kernel with swapped operands: tensor maps with its boxes (weights: 128 channels per
 // box; activations: 176-row and 32-row boxes).  `d` has been validated by build_problem already.
+// `ext`: the launch runs the kernel instance with the optional result forms; its weight maps have rank 4
 int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, const mxb::GGProblemDev& d,
-                       mxb::GGSwapProblemDev* o, bool bulk_everywhere) {
+                       mxb::GGSwapProblemDev* o, bool bulk_everywhere, bool ext) {
   int rc;
   const uint64_t a_rows = p.a_rows > 0 ? (uint64_t)p.a_rows : (uint64_t)p.row0 + (uint64_t)p.M;
   const uint64_t lda    = p.lda_bytes > 0 ? (uint64_t)p.lda_bytes : 0;
@@ -244,19 +246,19 @@ int build_problem_swap(EncodeTiledFn enc, const mxmoe_gg_problem& p, int idx, co
   const int silu = d.out_mode == mxb::OUT_SILU ? p.N / 2 : 0;
   switch (d.scheme) {
     case mxb::SCH_FP16:
-      if ((rc = encode_w(enc, &o->tmW, p.B, f16, 2, K, N, 64, mxb::kWT, s128, silu, idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, f16, 2, K, N, 64, mxb::kWT, s128, silu, idx, ext))) return rc;
       break;
     case mxb::SCH_W8A8:
-      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K, N, 128, mxb::kWT, s128, silu, idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K, N, 128, mxb::kWT, s128, silu, idx, ext))) return rc;
       break;
     case mxb::SCH_W4A4:
     case mxb::SCH_W4A4_XA:
       // packed rows of 64 bytes per stage; the 64-byte swizzle spreads the rows a converter warp reads over the banks
-      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K / 2, N, 64, mxb::kWT, CU_TENSOR_MAP_SWIZZLE_64B, silu, idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K / 2, N, 64, mxb::kWT, CU_TENSOR_MAP_SWIZZLE_64B, silu, idx, ext))) return rc;
       break;
     case mxb::SCH_W4A16G128:
       // [N/4, K] uint16 words seen as bytes: 64 k = 128 bytes per stage, 32 packed rows = 128 channels
-      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K * 2, N / 4, 128, mxb::kWT / 4, s128, 0, idx))) return rc;
+      if ((rc = encode_w(enc, &o->tmW, p.B, u8, 1, K * 2, N / 4, 128, mxb::kWT / 4, s128, 0, idx, ext))) return rc;
       break;
     default:
       break;
@@ -361,12 +363,16 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
   // to a peer (read here, when the workspace is prepared)
   const char* stores_env     = getenv("MXMOE_GG_STORES");
   const bool bulk_everywhere = stores_env && !strcmp(stores_env, "rows");
+  // does any problem use an optional result form?  Then the launch runs the kernel instance that has them.
+  bool ext = bulk_everywhere;
+  for (int i = 0; i < problem_count; ++i)
+    if (problems[i].c_row0_dev || problems[i].c_row_ptrs || problems[i].out_mode == mxb::OUT_SILU) ext = true;
   int max_rows = 0;
   for (int i = 0; i < problem_count; ++i) {
     if (problems[i].M == 0 && !problems[i].m_dev) continue;  // empty expert (ref_bind.cu:345 skips them too)
     rc = build_problem(st->encode, problems[i], i, dev + kept);
     if (rc) return rc;
-    rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept], bulk_everywhere);
+    rc = build_problem_swap(st->encode, problems[i], i, dev[kept], &swp[kept], bulk_everywhere, ext);
     if (rc) return rc;
     // redirected C rows and the per-channel 4-bit weight-only scheme exist in the SWAP kernel only
     if (problems[i].c_row0_dev || problems[i].c_row_ptrs || (dev[kept].scheme == mxb::SCH_W4A16G128 && problems[i].q.gsize == -1) ||
@@ -389,7 +395,7 @@ int mxmoe_gg_prepare(const mxmoe_gg_problem* problems, int problem_count, void* 
     plan->count     = kept;
     plan->needs_cvt = needs_cvt;
     // few rows in every problem: token tiles of 32 rows and a deeper ring (more weight bytes in flight per SM)
-    plan->flags     = (redirect ? 1 : 0) | (small_tiles_at_prepare(max_rows <= 32) ? 2 : 0);
+    plan->flags     = (redirect ? 1 : 0) | (small_tiles_at_prepare(max_rows <= 32) ? 2 : 0) | (ext ? 4 : 0);
     plan->kernel    = default_kernel();
   }
   return MXMOE_OK;
@@ -418,9 +424,10 @@ int run_kernel(void* workspace, const mxmoe_gg_plan* plan, int kernel, int num_c
   if (kernel == GGK_PAIR && n < 2) kernel = GGK_SINGLE;
   // CTA pairs of the kernel with swapped operands: large token tiles and activations in their final form only
   if (kernel == GGK_SWAP2 && (n < 2 || (plan->flags & 2) || needs_cvt == 2)) kernel = GGK_SWAP;
-  if (kernel == GGK_SWAP2)      mxb::gg_launch_swap_pair(swp, count, status, needs_cvt, n & ~1, cs);
+  const bool ext = (plan->flags & 4) != 0;
+  if (kernel == GGK_SWAP2)      mxb::gg_launch_swap_pair(swp, count, status, needs_cvt, ext, n & ~1, cs);
   else if (kernel == GGK_PAIR)  CUDA_TRY(mxb::gg_launch_pair(probs, count, status, needs_cvt, n & ~1, cs));
-  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, (plan->flags & 2) != 0, n, cs);
+  else if (kernel == GGK_SWAP)  mxb::gg_launch_swap(swp, count, status, needs_cvt, (plan->flags & 2) != 0, ext, n, cs);
   else                          mxb::gg_launch_single(probs, count, status, needs_cvt, n, cs);
   CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;

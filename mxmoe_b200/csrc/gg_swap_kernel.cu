@@ -367,7 +367,10 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCu
 // halves complete on the leader's xfull (the cta_group::2 form of the load only redirects the byte count),
 // converters and epilogue warps of both CTAs arrive at the leader's cvtdone / tempty, the leader's commits arrive
 // at empty / tfull of both CTAs.
-template <int kMode, bool kSmall, bool kPair = false>
+// kExt: the launch holds problems with one of the optional result forms (silu(gate) * up, row-wide stores, rows at
+// given addresses); its weight tensor maps then have rank 4.  Launches without them run the instance in which all of
+// that is compiled out: the extra per-tile loads and per-chunk branches cost the plain launch 2-7 %.
+template <int kMode, bool kSmall, bool kPair = false, bool kExt = false>
 __global__ void __launch_bounds__(CfgS<kMode>::kThreads, 1)
 gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatus* __restrict__ status) {
   using G = Geo<kSmall>;
@@ -394,6 +397,10 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
     return;
   }
 
+  auto load_w = [&](uint32_t dst, const void* map, uint32_t bar, int x, int y, int z) {
+    if (kExt) tma_load_4d(dst, map, bar, x, y, 0, z);
+    else      tma_load_2d(dst, map, bar, x, y);
+  };
   auto wslot = [&](int s) { return smem_base + s * G::kStageBytes; };
   auto xslot = [&](int s) { return smem_base + s * G::kStageBytes + kWSlotBytes; };
 
@@ -477,7 +484,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         // silu(gate) * up problems: the box gathers 16 gate + 16 up rows four times; its origin is the tile's first
         // group of 16 columns of C (the weight maps have rank 4, see encode_w)
         int wz = 0;
-        if (pr->silu_inter) { wz = ti.n_tile * 4; wy = 0; }
+        if (kExt && pr->silu_inter) { wz = ti.n_tile * 4; wy = 0; }
         const int xx_step = (ti.scheme == SCH_FP16 || ti.scheme == SCH_W4A16G128) ? 64 : 128;   // (packed int4: see below)
         // this tile's K block for which the test hook (GGStatus::skip_stage) announces more weight bytes than will
         // arrive.  A select, not a branch: one more branch per stage in these loops cost the w4a4 layer 3.5 %, and the
@@ -495,11 +502,12 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             if (!got) { report_s(status, 1, t); ok = false; break; }
             if (kCvt) {
               mbar_expect_tx(wfull0 + 8 * stage, wbytes);
-              tma_load_4d(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
+              load_w(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy, wz);
               if (rank == 0) mbar_expect_tx(xfull0 + 8 * stage, 2 * kXHalf);
             } else {
               if (rank == 0) mbar_expect_tx(xfull0 + 8 * stage, 2 * (wbytes + kXHalf));
-              tma_load_4d_pair(wslot(stage), &pr->tmW, xfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
+              if (kExt) tma_load_4d_pair(wslot(stage), &pr->tmW, xfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
+              else      tma_load_2d_pair(wslot(stage), &pr->tmW, xfull0 + 8 * stage, kb * wx_step, wy);
             }
             tma_load_2d_pair(xslot(stage), &pr->tmXh, xfull0 + 8 * stage, kb * xx_step, xr);
             if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
@@ -513,7 +521,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             TRACE(TR_PROD_GOT, n_stage + kb);
             if (!got) { report_s(status, 1, t); ok = false; break; }
             mbar_expect_tx(wfull0 + 8 * stage, wbytes + (kb == skip_kb ? 16u : 0u));
-            tma_load_4d(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy, 0, wz);
+            load_w(wslot(stage), &pr->tmW, wfull0 + 8 * stage, kb * wx_step, wy, wz);
             mbar_expect_tx(xfull0 + 8 * stage, xbytes);
             tma_load_2d(xslot(stage), &pr->tmX, xfull0 + 8 * stage, kb * xx_step, x_row);
             TRACE(TR_PROD_ISSUED, n_stage + kb);
@@ -530,13 +538,13 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             if (packed_x) {
               // packed activation rows (64 bytes of K each) go behind the packed weights; the converters expand them
               mbar_expect_tx(wbar, wbytes + xbytes);
-              tma_load_4d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, 0, wz);
+              load_w(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, wz);
               for (int b = 0; b < nbox; ++b)
                 tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, wbar, kb * 64, x_row + b * kXBoxSmall);
               mbar_arrive(bar);                     // no activation tile of its own: complete the phase
             } else {
               mbar_expect_tx(wbar, wbytes + (kb == skip_kb ? 16u : 0u));
-              tma_load_4d(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, 0, wz);
+              load_w(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, wz);
               mbar_expect_tx(bar, xbytes);
               if (big) {
                 tma_load_2d(xslot(stage), &pr->tmX, bar, kb * xx_step, x_row);
@@ -638,9 +646,9 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const int64_t grow0 = ti.x_row;   // buffer row of token 0 of the tile (A, scale_a)
       const int64_t crow0 = ti.c_row;   // its row in C
       const int N = pr->N, ldc = pr->ldc, out_mode = pr->out_mode;
-      const bool bulk     = pr->bulk_out != 0;
-      const int64_t* row_ptrs = pr->c_row_ptrs;
-      const int silu      = pr->silu_inter;   // > 0: lanes 0-15 of the warp hold gate rows, lanes 16-31 the up rows of the same 16 columns of C
+      const bool bulk     = kExt && pr->bulk_out != 0;
+      const int64_t* row_ptrs = kExt ? pr->c_row_ptrs : nullptr;
+      const int silu      = kExt ? pr->silu_inter : 0;   // > 0: lanes 0-15 of the warp hold gate rows, lanes 16-31 the up rows of the same 16 columns of C
       const bool is_int   = is_int_scheme(ti.scheme);
       const int acc_shift = (ti.scheme == SCH_W4A4 || ti.scheme == SCH_W4A4_XA) ? 8 : 0;   // codes ride in the high nibbles
       const int c_col     = ti.n_tile * (kWT / 2) + q * 16 + (lane & 15);                   // silu: this thread's column of C
@@ -815,7 +823,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-    if (lane < 8) bulk_wait_all();   // rows handed to the copy engine have reached memory before the CTA ends
+    if (kExt && lane < 8) bulk_wait_all();   // rows handed to the copy engine have reached memory before the CTA ends
     if (blockIdx.x == 0 && warp == 2 && lane == 0) {
       status->prof[PROF_EPI_WAIT]  = w_epi;
       status->prof[PROF_EPI_STORE] = w_store;
@@ -1003,15 +1011,19 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
 namespace {
 template <int kMode, bool kSmall>
 cudaError_t configure_one() {
-  return cudaFuncSetAttribute(gg_swap_kernel<kMode, kSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(gg_swap_kernel<kMode, kSmall, false, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_swap<Geo<kSmall>>());
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gg_swap_kernel<kMode, kSmall, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               smem_bytes_swap<Geo<kSmall>>());
 }
 template <int kMode, bool kSmall>
-void launch_one(const GGSwapProblemDev* problems, int count, GGStatus* status, int num_ctas, cudaStream_t stream) {
-  gg_swap_kernel<kMode, kSmall><<<num_ctas, CfgS<kMode>::kThreads, smem_bytes_swap<Geo<kSmall>>(), stream>>>(problems, count, status);
+void launch_one(const GGSwapProblemDev* problems, int count, GGStatus* status, bool ext, int num_ctas, cudaStream_t stream) {
+  if (ext) gg_swap_kernel<kMode, kSmall, false, true><<<num_ctas, CfgS<kMode>::kThreads, smem_bytes_swap<Geo<kSmall>>(), stream>>>(problems, count, status);
+  else     gg_swap_kernel<kMode, kSmall, false, false><<<num_ctas, CfgS<kMode>::kThreads, smem_bytes_swap<Geo<kSmall>>(), stream>>>(problems, count, status);
 }
 template <int kMode>
-void launch_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int num_ctas, cudaStream_t stream) {
+void launch_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, bool ext, int num_ctas, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim            = dim3((unsigned)(num_ctas & ~1), 1, 1);
   cfg.blockDim           = dim3(CfgS<kMode>::kThreads, 1, 1);
@@ -1024,7 +1036,8 @@ void launch_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs    = attr;
   cfg.numAttrs = 1;
-  cudaLaunchKernelEx(&cfg, gg_swap_kernel<kMode, false, true>, problems, count, status);
+  if (ext) cudaLaunchKernelEx(&cfg, gg_swap_kernel<kMode, false, true, true>, problems, count, status);
+  else     cudaLaunchKernelEx(&cfg, gg_swap_kernel<kMode, false, true, false>, problems, count, status);
 }
 }  // namespace
 
@@ -1042,29 +1055,30 @@ cudaError_t gg_configure_swap() {
   if ((e = configure_one<0, true>()) != cudaSuccess) return e;
   if ((e = configure_one<1, true>()) != cudaSuccess) return e;
   if ((e = configure_one<2, true>()) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(gg_swap_kernel<0, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                smem_bytes_swap<Geo<false>>())) != cudaSuccess) return e;
-  return cudaFuncSetAttribute(gg_swap_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              smem_bytes_swap<Geo<false>>());
+  constexpr int kBytes = smem_bytes_swap<Geo<false>>();
+  if ((e = cudaFuncSetAttribute(gg_swap_kernel<0, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gg_swap_kernel<0, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gg_swap_kernel<1, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes)) != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gg_swap_kernel<1, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
 }
 
 // CTA pairs (cta_group::2): large token tiles, activations in their final form (cvt_mode 0 or 1)
-void gg_launch_swap_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
-                         cudaStream_t stream) {
-  if (cvt_mode) launch_pair<1>(problems, count, status, num_ctas, stream);
-  else          launch_pair<0>(problems, count, status, num_ctas, stream);
+void gg_launch_swap_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool ext,
+                         int num_ctas, cudaStream_t stream) {
+  if (cvt_mode) launch_pair<1>(problems, count, status, ext, num_ctas, stream);
+  else          launch_pair<0>(problems, count, status, ext, num_ctas, stream);
 }
 
 void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles,
-                    int num_ctas, cudaStream_t stream) {
+                    bool ext, int num_ctas, cudaStream_t stream) {
   if (small_tiles) {
-    if (cvt_mode == 2)  launch_one<2, true>(problems, count, status, num_ctas, stream);
-    else if (cvt_mode)  launch_one<1, true>(problems, count, status, num_ctas, stream);
-    else                launch_one<0, true>(problems, count, status, num_ctas, stream);
+    if (cvt_mode == 2)  launch_one<2, true>(problems, count, status, ext, num_ctas, stream);
+    else if (cvt_mode)  launch_one<1, true>(problems, count, status, ext, num_ctas, stream);
+    else                launch_one<0, true>(problems, count, status, ext, num_ctas, stream);
   } else {
-    if (cvt_mode == 2)  launch_one<2, false>(problems, count, status, num_ctas, stream);
-    else if (cvt_mode)  launch_one<1, false>(problems, count, status, num_ctas, stream);
-    else                launch_one<0, false>(problems, count, status, num_ctas, stream);
+    if (cvt_mode == 2)  launch_one<2, false>(problems, count, status, ext, num_ctas, stream);
+    else if (cvt_mode)  launch_one<1, false>(problems, count, status, ext, num_ctas, stream);
+    else                launch_one<0, false>(problems, count, status, ext, num_ctas, stream);
   }
 }
 

@@ -124,9 +124,10 @@ cudaError_t gg_configure_pair();
 // kernel with swapped operands (gg_swap_kernel.cu): weights from tensor memory / shared memory as the M side,
 // token tiles of up to 176 rows (ring of 5 stages) or, with `small_tiles`, of up to 32 rows (ring of 10 stages)
 // as the N side
-void gg_launch_swap_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, int num_ctas,
-                         cudaStream_t stream);
-void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles,
+// `ext`: the launch holds problems with an optional result form (weight maps of rank 4), see gg_swap_kernel
+void gg_launch_swap_pair(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool ext,
+                         int num_ctas, cudaStream_t stream);
+void gg_launch_swap(const GGSwapProblemDev* problems, int count, GGStatus* status, int cvt_mode, bool small_tiles, bool ext,
                     int num_ctas, cudaStream_t stream);
 cudaError_t gg_configure_swap();
 
