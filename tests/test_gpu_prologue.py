@@ -150,7 +150,9 @@ def test_silu_mul_then_quant(cuda_device, n, ns):
             row += m
 
 
-@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (37, 60, 4), (1000, 64, 6), (8192, 60, 4), (300, 8, 2)])
+# decode batch (one block does everything), layer sizes, many experts, many pairs
+@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (37, 60, 4), (1000, 64, 6), (8192, 60, 4), (300, 8, 2), (600, 256, 2),
+                                   (700, 300, 3), (70000, 16, 4), (513, 2, 2)])
 def test_device_routing_matches_stable_sort(cuda_device, t, e, k):
     from mxmoe_b200.layer import MoELayer
     rng = np.random.default_rng(t)
