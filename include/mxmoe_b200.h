@@ -115,7 +115,7 @@ typedef struct mxmoe_gg_plan {
   int32_t flags;     /* bit 0: a problem redirects its C rows (c_row0_dev) or uses w4a16_g-1_asym: only the SWAP kernel can run it;
                         bit 2: a problem uses an optional result form (out_mode 2, c_row0_dev, c_row_ptrs): the launch runs the
                                kernel instance that has them, the weight tensor maps have rank 4;
-                        bit 1: SWAP kernel with token tiles of 32 rows and a ring of 10 stages (set by prepare when no
+                        bit 1: SWAP kernel with token tiles of 32 rows and a ring of 10 stages, 7 of two K blocks with 4-bit weights (set by prepare when no
                         problem has more than 32 rows; the caller may set or clear it before mxmoe_gg_run, e.g. set
                         it when the row counts come from device memory and are known to be small on average) */
   int32_t kernel;    /* the kernel mxmoe_gg_run launches (an mxmoe_gg_kernel value): chosen by mxmoe_gg_prepare from the

@@ -53,6 +53,7 @@ struct Sched {
 
 struct Tile {
   int p, m_tile, n_tile, scheme, nkb;
+  int odd;   // stages of two K blocks: the last stage of the tile holds one
 };
 
 // Fill the tables (all threads of the CTA; contains two __syncthreads).  `rows_per_tile` x `cols_per_tile`
@@ -65,9 +66,11 @@ __device__ __forceinline__ int c_shift_of(const GGSwapProblemDev& pr, int r0) {
 }
 
 // `packed_rows_per_tile` (> 0) replaces rows_per_tile for problems with packed 4-bit activations
+// `two_kblocks`: a pipeline stage holds TWO K blocks of a problem whose weights are 4-bit (the 32-token geometry
+// of the kernel with swapped operands); nkb then counts stages and bit 31 of meta says that the last one holds one
 template <typename Problem>
 __device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, int count, int rows_per_tile,
-                                            int cols_per_tile = kBN, int packed_rows_per_tile = 0) {
+                                            int cols_per_tile = kBN, int packed_rows_per_tile = 0, bool two_kblocks = false) {
   const int tid = threadIdx.x, lane = tid & 31;
   for (int p = tid; p < count; p += blockDim.x) {
     const Problem& pr = problems[p];
@@ -76,12 +79,17 @@ __device__ __forceinline__ void build_sched(Sched* sc, const Problem* problems, 
     const int r0     = pr.row0_dev ? *pr.row0_dev : pr.row0;
     const int nt     = (pr.N + cols_per_tile - 1) / cols_per_tile;
     const int kelems = (pr.scheme == SCH_FP16 || pr.scheme == SCH_W4A16G128) ? 64 : 128;
-    const int nkb    = (pr.K + kelems - 1) / kelems;
+    int nkb          = (pr.K + kelems - 1) / kelems;
+    unsigned odd     = 0;
+    if (two_kblocks && (pr.scheme == SCH_W4A4_XA || pr.scheme == SCH_W4A16G128)) {
+      odd = (unsigned)(nkb & 1);
+      nkb = (nkb + 1) >> 1;
+    }
     const int rpt   = (packed_rows_per_tile > 0 && pr.scheme == SCH_W4A4) ? packed_rows_per_tile : rows_per_tile;
     sc->tile_end[p] = ((m + rpt - 1) / rpt) * nt;
     sc->m_eff[p]    = m;
     sc->row0[p]     = r0;
-    sc->meta[p]     = (nt << 16) | (nkb << 4) | pr.scheme;
+    sc->meta[p]     = (int)((odd << 31) | ((unsigned)nt << 16) | ((unsigned)nkb << 4) | (unsigned)pr.scheme);
     sc->c_shift[p]  = c_shift_of(pr, r0);
   }
   __syncthreads();
@@ -112,7 +120,7 @@ __device__ __forceinline__ Tile find_tile(const Sched* c, int count, int t) {
   }
   const int start = lo ? c->tile_end[lo - 1] : 0;
   const int meta  = c->meta[lo];
-  const int nt    = meta >> 16;
+  const int nt    = (meta >> 16) & 0x7FFF;
   const int idx   = t - start;
   Tile r;
   r.p      = lo;
@@ -120,6 +128,7 @@ __device__ __forceinline__ Tile find_tile(const Sched* c, int count, int t) {
   r.n_tile = idx - r.m_tile * nt;
   r.scheme = meta & 15;
   r.nkb    = (meta >> 4) & 0xFFF;
+  r.odd    = (int)((unsigned)meta >> 31);
   return r;
 }
 

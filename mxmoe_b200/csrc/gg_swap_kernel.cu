@@ -65,7 +65,7 @@ constexpr int kEpiStageS   = 2048;              // per epilogue warp: 16 token p
 // 8- and 16-bit tiles of a launch that also holds 4-bit weights lose 4-7 % per group that is present.
 constexpr int kCvtWarps    = 8;
 constexpr int kCvtGroups   = kCvtWarps / 4;
-constexpr uint32_t kASlotCols = 32;             // TMEM columns of one A slot (128 bytes of K per channel)
+constexpr uint32_t kASlotCols = 32;             // TMEM columns of one converted K block (128 bytes of K per channel)
 constexpr int kCvtGroup    = 4;                 // warps per converter group (one per TMEM lane quarter)
 constexpr int kEpiWarps    = 8;                 // two per TMEM lane quarter (warps 2-5 and 7-10)
 
@@ -73,12 +73,18 @@ constexpr int kEpiWarps    = 8;                 // two per TMEM lane quarter (wa
 // with compute-bound problems.  Small: token tiles of up to 32 rows, ring of 10 stages - for launches whose
 // problems all have few rows (decode): what matters there is how many weight bytes are in flight per SM, and a
 // stage of such a tile carries only 4-16 KiB of weights.
-template <bool kSmall>
+// kTwo (32-token tiles of launches with 4-bit weights): a stage holds TWO K blocks of a problem with 4-bit weights
+// (16 KiB of packed w4a4 weights, 8 KiB of w4a16, 8 KiB of activations), ring of 7 stages: the hand-offs of a stage
+// cost the same 500-600 cycles whatever it carries, and a 32-token tile has nothing else to pay them with.
+template <bool kSmall, bool kTwo = false>
 struct Geo {
+  static_assert(!kTwo || kSmall, "two K blocks per stage: 32-token tiles only");
   static constexpr int kTok        = kSmall ? 32 : kTT;          // tokens per tile (tcgen05 N, any multiple of 16 up to this)
-  static constexpr int kStages     = kSmall ? 10 : 5;
+  static constexpr int kStages     = kSmall ? (kTwo ? 7 : 10) : 5;
+  static constexpr int kKbPerStage = kTwo ? 2 : 1;
+  static constexpr uint32_t kASlotStride = kASlotCols * kKbPerStage;   // TMEM columns of the A slot of one stage
   static constexpr int kEpiBufs    = kSmall ? 4 : kEpiWarps;     // transpose buffers: a 32-token tile has one chunk, the second warp of a quarter never stores
-  static constexpr int kXSlotBytes = kTok * kRowBytes;           // 22 KiB / 4 KiB
+  static constexpr int kXSlotBytes = kTok * kRowBytes * kKbPerStage;   // 22 KiB / 4 KiB / 8 KiB
   static constexpr int kStageBytes = kWSlotBytes + kXSlotBytes;
   static constexpr int kRingBytes  = kStages * kStageBytes;      // 190 KiB / 200 KiB
   static constexpr uint32_t kAccCols   = kTok;                   // TMEM columns per accumulator
@@ -87,7 +93,7 @@ struct Geo {
   static constexpr int kBarAcc0   = 1 + kStages;                 // two more: accumulator b is drained
   static constexpr int kBarEpi0   = 3 + kStages;                 // two per group of four epilogue warps (row-wide stores)
   static constexpr int kEpiGroups = kEpiBufs / 4;
-  static_assert(kASlotCol0 + kStages * kASlotCols <= 512, "tensor memory budget");
+  static_assert(kASlotCol0 + kStages * kASlotStride <= 512, "tensor memory budget");
   static_assert(kBarEpi0 + 2 * kEpiGroups - 1 <= 15, "named barrier budget");
   static_assert((kTok + 32) % 8 == 0, "sa_stage rows must stay 16-byte aligned");
 };
@@ -116,6 +122,7 @@ constexpr int kMaxRecs = 512;   // tiles per CTA kept in the table; later ones a
 
 struct TileS {
   int p, scheme, nkb, x_row, n_tile, ntok, c_row;
+  int odd;   // stages of two K blocks: the last stage holds one
 };
 
 template <typename G>
@@ -137,7 +144,8 @@ struct CtrlS {
 template <typename G>
 constexpr int smem_bytes_swap() { return 1024 + G::kRingBytes + G::kEpiBufs * kEpiStageS + (int)sizeof(CtrlS<G>); }
 
-static_assert(smem_bytes_swap<Geo<false>>() <= 232448 && smem_bytes_swap<Geo<true>>() <= 232448,
+static_assert(smem_bytes_swap<Geo<false>>() <= 232448 && smem_bytes_swap<Geo<true>>() <= 232448 &&
+                  smem_bytes_swap<Geo<true, true>>() <= 232448,
               "dynamic shared memory of one CTA (227 KiB)");
 
 __device__ __forceinline__ void report_s(GGStatus* status, int role, int tile) {
@@ -171,7 +179,7 @@ __device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, i
   if (pair_rank >= 0) ti.n_tile = 2 * ti.n_tile + pair_rank;
   const int tile_tok = ti.scheme == SCH_W4A4 ? tok_packed : tok;   // problems with packed activations: shorter tiles
   TileRec r;
-  r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12);
+  r.pk     = ti.p | (ti.scheme << 8) | (ti.nkb << 12) | (ti.odd << 30);
   r.x_row  = sc->row0[ti.p] + ti.m_tile * tile_tok;
   r.nt     = ti.n_tile | (min(tile_tok, sc->m_eff[ti.p] - ti.m_tile * tile_tok) << 16);
   r.c_row  = r.x_row + sc->c_shift[ti.p];
@@ -179,7 +187,7 @@ __device__ __forceinline__ TileRec make_rec(const Sched* sc, int count, int t, i
 }
 __device__ __forceinline__ TileS decode_rec(const TileRec& r) {
   TileS t;
-  t.p = r.pk & 0xff; t.scheme = (r.pk >> 8) & 15; t.nkb = r.pk >> 12;
+  t.p = r.pk & 0xff; t.scheme = (r.pk >> 8) & 15; t.nkb = (r.pk >> 12) & 0x3FFFF; t.odd = (r.pk >> 30) & 1;
   t.x_row = r.x_row; t.n_tile = r.nt & 0xffff; t.ntok = r.nt >> 16; t.c_row = r.c_row;
   return t;
 }
@@ -225,6 +233,7 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
 // TMEM lane quarter, so every instruction it does not need (a predicate set-up per MMA, descriptor arithmetic
 // recomputed per stage) delays the issue of the next stage.  `first` == 0: the first MMA overwrites D.
 //   kV 0 int8 / weights from shared memory, 1 fp16 / shared memory, 2 int8 / tensor memory, 3 fp16 / tensor memory.
+#define MXB_COMMIT1 "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
 #define MXB_MMA_STAGE_SS(KIND)                                                                              \
   asm volatile(                                                                                             \
       "{\n\t"                                                                                               \
@@ -246,7 +255,7 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
       :                                                                                                     \
       : "r"(d_tmem), "r"(wlo), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar)               \
       : "memory")
-#define MXB_MMA_STAGE_TS(KIND)                                                                              \
+#define MXB_MMA_STAGE_TS(KIND, COMMIT)                                                                      \
   asm volatile(                                                                                             \
       "{\n\t"                                                                                               \
       ".reg .pred p, t;\n\t"                                                                                \
@@ -261,7 +270,7 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
       "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [a1], x1, %4, t;\n\t"                                  \
       "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [a2], x2, %4, t;\n\t"                                  \
       "tcgen05.mma.cta_group::1.kind::" KIND " [%0], [a3], x3, %4, t;\n\t"                                  \
-      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"                     \
+      COMMIT                                                                                                \
       "}"                                                                                                   \
       :                                                                                                     \
       : "r"(d_tmem), "r"(a_tmem), "r"(xlo), "r"(desc_hi), "r"(idesc), "r"(first), "r"(empty_bar)            \
@@ -313,7 +322,8 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
         "h"((unsigned short)3)                                                                              \
       : "memory")
 
-template <int kV, bool kPair>
+// kCommit = false (weights from tensor memory, single CTAs): the first K block of a stage that holds two
+template <int kV, bool kPair, bool kCommit = true>
 __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t wlo, uint32_t a_tmem, uint32_t xlo, uint32_t desc_hi,
                                           uint32_t idesc, uint32_t first, uint32_t empty_bar) {
   if (kPair) {
@@ -324,8 +334,8 @@ __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t wlo, uint32_
   } else {
     if (kV == 0)      { MXB_MMA_STAGE_SS("i8"); }
     else if (kV == 1) { MXB_MMA_STAGE_SS("f16"); }
-    else if (kV == 2) { MXB_MMA_STAGE_TS("i8"); }
-    else              { MXB_MMA_STAGE_TS("f16"); }
+    else if (kV == 2) { if (kCommit) { MXB_MMA_STAGE_TS("i8", MXB_COMMIT1); } else { MXB_MMA_STAGE_TS("i8", ""); } }
+    else              { if (kCommit) { MXB_MMA_STAGE_TS("f16", MXB_COMMIT1); } else { MXB_MMA_STAGE_TS("f16", ""); } }
   }
 }
 
@@ -339,15 +349,24 @@ struct MmaCursor {
   int stage;
   uint32_t wlo, xlo, a_tmem, ebar;
 };
+// `last_nb`: K blocks in the last stage of the tile (stages of two K blocks, weights from tensor memory: 1 or 2;
+// otherwise 1): every other stage of such a tile holds two, issued as 4 + 4 MMAs and one commit.
 template <int kV, typename G, int kBarThreads, bool kPair>
-__device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCursor& c0, int lane, uint32_t d_tmem,
-                                              uint32_t idesc, uint32_t desc_hi, int& sidx) {
+__device__ __forceinline__ void mma_tile_loop(int nkb, int last_nb, MmaCursor& c, const MmaCursor& c0, int lane,
+                                              uint32_t d_tmem, uint32_t idesc, uint32_t desc_hi, int& sidx) {
+  constexpr bool kTwo = G::kKbPerStage == 2 && kV >= 2;
   for (int kb = 0; kb < nkb; ++kb) {
     nbar_sync(G::kBarStage0 + c.stage, kBarThreads);   // operands of this stage are in place
     if (lane == 0) TRACE(TR_MMA_GOT, sidx);
     if (elect_one_sync()) {
       tc_fence_after_sync();
-      mma_stage<kV, kPair>(d_tmem, c.wlo, c.a_tmem, c.xlo, desc_hi, idesc, kb > 0 ? 1u : 0u, c.ebar);
+      if (kTwo && (kb + 1 < nkb || last_nb == 2)) {
+        mma_stage<kV, kPair, false>(d_tmem, c.wlo, c.a_tmem, c.xlo, desc_hi, idesc, kb > 0 ? 1u : 0u, c.ebar);
+        mma_stage<kV, kPair>(d_tmem, c.wlo, c.a_tmem + kASlotCols, c.xlo + ((G::kTok * kRowBytes) >> 4), desc_hi, idesc,
+                             1u, c.ebar);
+      } else {
+        mma_stage<kV, kPair>(d_tmem, c.wlo, c.a_tmem, c.xlo, desc_hi, idesc, kb > 0 ? 1u : 0u, c.ebar);
+      }
     }
     __syncwarp();
     if (lane == 0) TRACE(TR_MMA_ISSUED, sidx);
@@ -355,7 +374,7 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCu
     if (++c.stage == G::kStages) {
       c = c0;
     } else {
-      c.wlo += G::kStageBytes >> 4; c.xlo += G::kStageBytes >> 4; c.a_tmem += kASlotCols; c.ebar += 8;
+      c.wlo += G::kStageBytes >> 4; c.xlo += G::kStageBytes >> 4; c.a_tmem += G::kASlotStride; c.ebar += 8;
     }
   }
 }
@@ -373,7 +392,8 @@ __device__ __forceinline__ void mma_tile_loop(int nkb, MmaCursor& c, const MmaCu
 template <int kMode, bool kSmall, bool kPair = false, bool kExt = false>
 __global__ void __launch_bounds__(CfgS<kMode>::kThreads, 1)
 gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatus* __restrict__ status) {
-  using G = Geo<kSmall>;
+  constexpr bool kTwo = kSmall && kMode == 1;   // stages of two K blocks for problems with 4-bit weights
+  using G = Geo<kSmall, kTwo>;
   constexpr bool kCvt = kMode != 0;
   static_assert(!kPair || (!kSmall && kMode != 2), "CTA pairs: large tiles, activations in their final form");
   constexpr int kStageBar = CfgS<kMode, kPair>::kStageBarThreads;
@@ -422,7 +442,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
   // problems with packed 4-bit activations use token tiles of at most 128 rows: the packed rows of a stage
   // (128 x 64 B) then fit behind the packed weights in the stage's weight slot
   constexpr int kTokPacked = G::kTok > 128 ? 128 : G::kTok;
-  build_sched(sc, problems, count, G::kTok, kPair ? 2 * kWT : kWT, kTokPacked);
+  build_sched(sc, problems, count, G::kTok, kPair ? 2 * kWT : kWT, kTokPacked, kTwo);
   const int total_tiles = sc->total_tiles;
   const int my_tiles    = total_tiles > cta ? (total_tiles - cta + nctas - 1) / nctas : 0;
   const int pair_rank   = kPair ? rank : -1;
@@ -542,6 +562,17 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
               for (int b = 0; b < nbox; ++b)
                 tma_load_2d(wslot(stage) + kWSlotBytes / 2 + b * kXBoxSmall * 64, &pr->tmXs, wbar, kb * 64, x_row + b * kXBoxSmall);
               mbar_arrive(bar);                     // no activation tile of its own: complete the phase
+            } else if (kTwo) {
+              // stages of two K blocks for problems with 4-bit weights: K block 2 kb (+ 1 unless the tile's K ends
+              // there), weights back to back in the weight slot, activations as [K block][32 rows][128 bytes]
+              const int nb = (is_cvt_scheme(ti.scheme) && !(ti.odd && kb + 1 == ti.nkb)) ? 2 : 1;
+              const int k0 = is_cvt_scheme(ti.scheme) ? 2 * kb : kb;
+              mbar_expect_tx(wbar, wbytes * nb + (kb == skip_kb ? 16u : 0u));
+              mbar_expect_tx(bar, xbytes * nb);
+              for (int b = 0; b < nb; ++b) {
+                load_w(wslot(stage) + b * wbytes, &pr->tmW, wbar, (k0 + b) * wx_step, wy, wz);
+                tma_load_2d(xslot(stage) + b * G::kTok * kRowBytes, &pr->tmXs, bar, (k0 + b) * xx_step, x_row);
+              }
             } else {
               mbar_expect_tx(wbar, wbytes + (kb == skip_kb ? 16u : 0u));
               load_w(wslot(stage), &pr->tmW, wbar, kb * wx_step, wy, wz);
@@ -603,10 +634,11 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       constexpr int kMmaM   = kPair ? 2 * kWT : kWT;
       const uint32_t idesc  = is_int ? idesc_i8(kMmaM, npad) : idesc_f16(kMmaM, npad);
       const int variant     = (from_tmem ? 2 : 0) + (is_int ? 0 : 1);
-      if (variant == 0)      mma_tile_loop<0, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      else if (variant == 1) mma_tile_loop<1, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      else if (variant == 2) mma_tile_loop<2, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
-      else                   mma_tile_loop<3, G, kStageBar, kPair>(ti.nkb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      const int last_nb     = (kTwo && from_tmem && !ti.odd) ? 2 : 1;
+      if (variant == 0)      mma_tile_loop<0, G, kStageBar, kPair>(ti.nkb, last_nb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else if (variant == 1) mma_tile_loop<1, G, kStageBar, kPair>(ti.nkb, last_nb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else if (variant == 2) mma_tile_loop<2, G, kStageBar, kPair>(ti.nkb, last_nb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
+      else                   mma_tile_loop<3, G, kStageBar, kPair>(ti.nkb, last_nb, cur, cur0, lane, d_tmem, idesc, desc_hi, sidx);
       if (elect_one_sync()) {
         if (kPair) mma_commit2(smem_u32(&ctrl->tfull[acc]), 3);
         else       mma_commit(smem_u32(&ctrl->tfull[acc]));
@@ -893,7 +925,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       const __half2* szp  = reinterpret_cast<const __half2*>(pr->scale_b) + gn;
       // K blocks per (scale, zero) group as a shift: 1 for groups of 128 (two 64-k stages); the per-channel scheme
       // (cta_gemm.cuh:112-286) has one group for the whole of K
-      const int gsh       = pr->one_group ? 30 : 1;
+      // (with stages of two K blocks a stage IS a group of 128)
+      const int gsh       = pr->one_group ? 30 : (kTwo ? 0 : 1);
       const int kb_first  = (int)(((uint32_t)group + kCvtGroups - it % kCvtGroups) % kCvtGroups);   // first K block of this tile the group handles
       __half2 sz_next = __float2half2_rn(0.f);
       if (has_sz && kb_first < ti.nkb) sz_next = __ldg(szp + (int64_t)(kb_first >> gsh) * N);
@@ -923,12 +956,17 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
         if (q == 0 && lane == 0) TRACE(TR_CVT_GOT, (int)it);
         if (convert) {
           tc_fence_after_sync();
+          // stages of two K blocks: the second block's packed weights lie behind the first's, its converted form
+          // goes to the upper 32 columns of the stage's A slot
+          const int nb = (kTwo && !(ti.odd && kb + 1 == ti.nkb)) ? 2 : 1;
+#pragma unroll 1
+          for (int b = 0; b < nb; ++b) {
           uint32_t o[32];
           if (ti.scheme == SCH_W4A4_XA || ti.scheme == SCH_W4A4) {
             // packed row: 64 bytes, 16-byte chunks swizzled by (row >> 1) & 3 (64-byte swizzle of the tensor map).
             // Chunk c becomes 32 int8 bytes: its high nibbles, then its low nibbles, each moved to the top of a
             // byte (code q -> byte 16*q; the accumulator is shifted back in the epilogue).
-            const uint32_t src = wslot(s_cur) + row * 64;
+            const uint32_t src = wslot(s_cur) + b * (kWSlotBytes / 2) + row * 64;
             const int sw       = (row >> 1) & 3;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -943,7 +981,7 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
             // stage is the 16-byte chunk 2*kb16 + (f >> 1) (128-byte swizzle: XOR r), nibble 2*(f & 1) + c of
             // word d holds k = 16*kb16 + 8*c + d.
             const int f = lane >> 3, r = lane & 7;
-            const uint32_t src = wslot(s_cur) + (8 * q + r) * 128;
+            const uint32_t src = wslot(s_cur) + b * (kWSlotBytes / 4) + (8 * q + r) * 128;
             const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
 #pragma unroll
             for (int kb16 = 0; kb16 < 4; ++kb16) {
@@ -958,7 +996,8 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
               }
             }
           }
-          tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + G::kASlotCol0 + s_cur * kASlotCols, o);
+          tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + G::kASlotCol0 + s_cur * G::kASlotStride + b * kASlotCols, o);
+          }
           if (kMode == 2 && ti.scheme == SCH_W4A4) {
             // packed activation rows -> int8 rows of the swizzled operand tile (the same nibble -> byte 16*q map)
             const int rows32 = (ti.ntok + 31) & ~31;
