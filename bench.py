@@ -515,7 +515,7 @@ def main():
     # neighbouring steps overlap the compute on their own streams
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(3, min(args.steps, 50))
+    e2e_steps = max(3, min(args.steps, 200))
     from mxmoe_b200.layer import HostPipeline
     pipe = HostPipeline(layer, T, spec.hidden, spec.topk, device=dev, use_graph=use_graph,
                         inputs=(hidden, ids_d, wts_d))
