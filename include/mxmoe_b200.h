@@ -334,6 +334,14 @@ int mxmoe_gate_topk(const void* logits, int logits_fp16, int num_tokens, int num
 int mxmoe_combine_topk(const void* y, const int32_t* slot_row, const float* topk_weights, const void* y_shared,
                        void* out, int num_tokens, int topk, int hidden, void* stream);
 
+/* Small host -> device transfer done by a KERNEL that reads page-locked (mapped) host memory, for serving loops
+ * whose copy engines are busy with large transfers: a 131 KB routing table queued as a DMA copy behind a 33 MB
+ * one held the copy-in stream of the 8192-token layer for 50 us (measured).  `src` must be page-locked host memory
+ * that the device can address (cudaHostAlloc / cudaHostRegister; what torch's pin_memory() returns) and must stay
+ * unchanged until the stream reaches the call; dst, src and bytes are multiples of 16.  Anything else is handed to
+ * cudaMemcpyAsync.  No counterpart in the reference. */
+int mxmoe_fetch_host(void* dst, const void* src, size_t bytes, void* stream);
+
 /* ---- expert parallel ----------------------------------------------------------
  * No reference counterpart: the reference has no distributed code.  One process per GPU; experts are
  * numbered so that rank r owns the contiguous range [range_lo[r], range_lo[r+1]).  mxmoe_ep_plan turns the

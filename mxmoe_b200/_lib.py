@@ -17,7 +17,7 @@ EXPORTS = (
     "mxmoe_gg_workspace_bytes", "mxmoe_gg_prepare", "mxmoe_gg_run", "mxmoe_gg_run_kernel", "mxmoe_ep_plan", "mxmoe_ep_sync", "mxmoe_ep_dispatch_rows", "mxmoe_gate_topk", "mxmoe_gg_launch", "mxmoe_gg_check", "mxmoe_gg_profile", "mxmoe_gg_debug",
     "mxmoe_groupgemm_hz_fused", "mxmoe_quant_act", "mxmoe_quant_tokens", "mxmoe_gather_rows", "mxmoe_quant_tokens_scatter",
     "mxmoe_silu_mul_then_quant", "mxmoe_hadamard_kron",
-    "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk",
+    "mxmoe_route_workspace_bytes", "mxmoe_route_topk", "mxmoe_route_topk_static", "mxmoe_combine_topk", "mxmoe_fetch_host",
 )
 
 
@@ -145,6 +145,7 @@ def lib() -> C.CDLL:
         l.mxmoe_route_topk_static.argtypes = [C.c_void_p, C.c_void_p]
         l.mxmoe_combine_topk.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int, C.c_int, C.c_int, C.c_void_p]
+        l.mxmoe_fetch_host.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         _lib = l
     return _lib
 

@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -718,6 +719,32 @@ int mxmoe_route_topk_static(const mxmoe_route_args* a, void* stream) {
   r.id_map = a->id_map; r.rep_base = a->rep_base; r.rep_count = a->rep_count;
   if (r.rep_base && (!r.id_map || !r.rep_count)) return fail(MXMOE_ERR_INVALID, "rep_base needs id_map and rep_count");
   CUDA_TRY(mxb::launch_route(r, static_cast<cudaStream_t>(stream)));
+  return MXMOE_OK;
+}
+
+namespace {
+__global__ void fetch_host_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n16) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+}  // namespace
+
+int mxmoe_fetch_host(void* dst, const void* src, size_t bytes, void* stream) {
+  if (bytes == 0) return MXMOE_OK;
+  if (!dst || !src) return fail(MXMOE_ERR_INVALID, "null pointer");
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  cudaPointerAttributes at;
+  const bool mapped = cudaPointerGetAttributes(&at, src) == cudaSuccess && at.type == cudaMemoryTypeHost &&
+                      at.devicePointer != nullptr;
+  if (!mapped) cudaGetLastError();   // an unregistered pointer leaves an error behind on older runtimes
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | bytes) & 15) == 0;
+  if (!mapped || !aligned || bytes > (size_t)(4 << 20)) {
+    CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, cs));
+    return MXMOE_OK;
+  }
+  const size_t n16 = bytes / 16;
+  const int blocks = (int)std::min<size_t>(64, (n16 + 255) / 256);
+  fetch_host_kernel<<<blocks, 256, 0, cs>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(at.devicePointer), n16);
+  CUDA_TRY(cudaGetLastError());
   return MXMOE_OK;
 }
 

@@ -468,6 +468,10 @@ class HostPipeline:
         for hidden_host, ids_host, wts_host, out_host in batches:     # pinned host tensors
             pipe.submit(hidden_host, ids_host, wts_host, out_host)
         pipe.drain()                                                  # out_host of every submitted step is complete
+
+    The host tensors of a step (int32 ids, fp32 weights, fp16 hidden states; contiguous, page-locked) must stay
+    unchanged until the step has run: the routing tables are read from them by a kernel when the step's compute
+    starts, the hidden states by the copy engine before that.
     """
 
     def __init__(self, layer, tokens: int, hidden: int, topk: int, device=None, use_graph: bool = True,
@@ -477,8 +481,6 @@ class HostPipeline:
         dev = self.device
         self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         self.bufs = [dict(hidden=torch.empty(tokens, hidden, dtype=torch.float16, device=dev),
-                          ids=torch.empty(tokens, topk, dtype=torch.int32, device=dev),
-                          wts=torch.empty(tokens, topk, dtype=torch.float32, device=dev),
                           out=torch.empty(tokens, hidden, dtype=torch.float16, device=dev),
                           ev_in=torch.cuda.Event(), ev_comp=torch.cuda.Event(), ev_out=torch.cuda.Event())
                      for _ in range(2)]
@@ -501,15 +503,19 @@ class HostPipeline:
             if self.step >= 2:
                 self.s_in.wait_event(b["ev_comp"])          # step - 2 no longer reads this input set
             b["hidden"].copy_(hidden_host, non_blocking=True)
-            b["ids"].copy_(ids_host, non_blocking=True)
-            b["wts"].copy_(wts_host, non_blocking=True)
             b["ev_in"].record(self.s_in)
         comp.wait_event(b["ev_in"])
         if self.step >= 2:
             comp.wait_event(b["ev_out"])                    # step - 2's result has left this output buffer
         self.x.copy_(b["hidden"], non_blocking=True)
-        self.i.copy_(b["ids"], non_blocking=True)
-        self.w.copy_(b["wts"], non_blocking=True)
+        # the routing tables (131 KB each) are read from the page-locked host tensors by a kernel on the compute
+        # stream: as DMA copies behind the hidden states they cost the copy-in stream 0.11 ms per step (0.83 -> 0.72)
+        assert ids_host.dtype == self.i.dtype and wts_host.dtype == self.w.dtype and ids_host.is_contiguous() \
+            and wts_host.is_contiguous() and ids_host.numel() == self.i.numel() and wts_host.numel() == self.w.numel()
+        stream = current_stream_ptr()
+        lib = _lib.lib()
+        _lib.check(lib.mxmoe_fetch_host(self.i.data_ptr(), ids_host.data_ptr(), ids_host.numel() * ids_host.element_size(), stream))
+        _lib.check(lib.mxmoe_fetch_host(self.w.data_ptr(), wts_host.data_ptr(), wts_host.numel() * wts_host.element_size(), stream))
         fwd = self.layer.forward_graph if self.use_graph else self.layer.forward
         b["out"].copy_(fwd(self.x, self.i, self.w), non_blocking=True)
         b["ev_comp"].record(comp)

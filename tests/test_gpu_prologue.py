@@ -366,3 +366,19 @@ def test_device_exchange_plan_expert_major(cuda_device, world, rank):
             want_ptr[r0:r0 + m] = bases[s] + (src0 + np.arange(m)) * row_bytes
     assert np.array_equal(t["recv_row_expert"].cpu().numpy(), want_exp)
     assert np.array_equal(t["row_dst"].cpu().numpy()[:total], want_ptr[:total])
+
+
+def test_fetch_host_reads_page_locked_memory_with_a_kernel(cuda_device):
+    """mxmoe_fetch_host: page-locked source (kernel path), pageable source and odd sizes (copy-engine path)."""
+    from mxmoe_b200 import _lib
+    from mxmoe_b200.gg import current_stream_ptr
+    lib = _lib.lib()
+    rng = np.random.default_rng(3)
+    for n, pinned in ((8192 * 4, True), (1000, True), (8192 * 4, False), (37, True)):
+        src = torch.from_numpy(rng.integers(-2**31, 2**31 - 1, n, dtype=np.int64).astype(np.int32))
+        if pinned:
+            src = src.pin_memory()
+        dst = torch.zeros(n, dtype=torch.int32, device=cuda_device)
+        _lib.check(lib.mxmoe_fetch_host(dst.data_ptr(), src.data_ptr(), n * 4, current_stream_ptr()))
+        torch.cuda.synchronize()
+        assert torch.equal(dst.cpu(), src)
