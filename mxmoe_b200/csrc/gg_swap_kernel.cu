@@ -696,9 +696,17 @@ gg_swap_kernel(const GGSwapProblemDev* __restrict__ problems, int count, GGStatu
       }
       const long long c0 = tick(prof_on);
       if (!dead) {
-        const bool ok = warp_wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag, lane, tmo);
+        // ONE epilogue warp polls the accumulator's mbarrier, the other seven wait for it at a named barrier (a
+        // tile keeps them waiting for thousands of cycles; eight polling warps are eight streams of try_wait)
+        if (ew == 0) {
+          const bool ok = warp_wait_bar(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag, lane, tmo);
+          if (lane == 0) ctrl->pad[0] = ok ? 1 : 0;
+          __syncwarp();
+        }
+        nbar_sync(15, kEpiWarps * 32);
+        const bool ok = *reinterpret_cast<volatile int*>(&ctrl->pad[0]) != 0;
         if (!ok) {
-          if (lane == 0) report_s(status, 4, t);
+          if (lane == 0 && ew == 0) report_s(status, 4, t);
           dead = true;
         }
       }
