@@ -415,7 +415,7 @@ class MoELayer:
     def forward_graph(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor | None = None):
         """Same as :meth:`forward`, replayed from a CUDA graph.
 
-        The step launches nine kernels and never returns to the host, so it is captured once per set
+        The step launches eight kernels (nine with a shared expert) and never returns to the host, so it is captured once per set
         of argument buffers (their addresses are baked into the graph: refill the same tensors for
         the next step) and replayed with a single launch.
         """
